@@ -1,0 +1,108 @@
+/* wave_b200 — C ABI of the B200 (sm_100a) MXFP4 scaled-GEMM library.
+ *
+ * This is the boundary a binding of the reference would call instead of its own launch shim.
+ * In the reference, a compiled kernel is launched by the C++ extension `wave_runtime`
+ * (wave_lang/kernel/wave/runtime/runtime.cpp:123-203 `launch`, :231-240 `load_binary`), driven
+ * from Python by `invoke_with_wave_runtime` (wave_lang/kernel/wave/utils/run_utils.py:62-134):
+ * raw device pointers, problem sizes and the caller's stream go in, the launch is asynchronous
+ * and nothing is returned but an error. The entry points below keep that contract: plain
+ * pointers and sizes, an explicit stream, no allocation of caller-visible memory, no implicit
+ * synchronisation, an int status with a thread-local message.
+ *
+ * Tensor contract (wave_lang/kernel/wave/templates/gemm.py:171-175):
+ *   a        uint8 [M, K/2]   packed E2M1, two codes per byte, even k in the low nibble
+ *   a_scale  uint8 [M, K/32]  E8M0, one per 32 K elements
+ *   b        uint8 [N, K/2]   (N-major: the kernel computes a * b^T)
+ *   b_scale  uint8 [N, K/32]
+ *   c        f32 or bf16 [M, N], row pitch ldc elements, fully overwritten
+ * K must be a multiple of 32. a, b must be 16-byte aligned and contiguous.
+ *
+ * The GEMM entry points read scales in the tcgen05 scale-factor layout ("packed scales");
+ * wb200_repack_scales converts the row-major arrays above.
+ */
+#ifndef WAVE_B200_H_
+#define WAVE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------- */
+#define WB200_OK 0
+#define WB200_ERR_INVALID_ARG (-1)   /* bad size, null pointer, unknown dtype or flag */
+#define WB200_ERR_ALIGNMENT (-2)     /* pointer or pitch not aligned as required */
+#define WB200_ERR_WORKSPACE (-3)     /* workspace missing or too small */
+#define WB200_ERR_UNSUPPORTED (-4)   /* device is not sm_100, or shape outside the kernel's range */
+#define WB200_ERR_DEVICE_TIMEOUT (-5) /* a bounded device-side wait gave up; results are invalid */
+#define WB200_ERR_CUDA (-6)          /* a CUDA runtime/driver call failed; see wb200_last_error */
+
+/* ---- output element types ------------------------------------------------------------------ */
+#define WB200_F32 0
+#define WB200_BF16 1
+
+/* ---- flags of wb200_mxfp4_gemm ------------------------------------------------------------- */
+#define WB200_PATH_AUTO 0u        /* pick by shape */
+#define WB200_PATH_TILE_1CTA 1u   /* 128 x BN tiles, one CTA each */
+#define WB200_PATH_TILE_2CTA 2u   /* 256 x BN tiles on CTA pairs (cta_group::2) */
+#define WB200_PATH_SKINNY 3u      /* M <= 128: swapped operands, stream-K, needs a workspace */
+#define WB200_PATH_MASK 0xFu
+#define WB200_TILE_N128 0x10u     /* force BN = 128 (default 256 for the tile paths) */
+
+/* Library version (major * 1000 + minor). */
+int wb200_version(void);
+
+/* Message of the last failure on this thread ("" when none). Replaces the std::runtime_error
+ * text of HIP_CHECK_EXC in wave_lang/kernel/wave/runtime/runtime.cpp:96-109. */
+const char* wb200_last_error(void);
+
+/* Reads and clears the device status word of the current device after synchronising `stream`.
+ * Returns WB200_OK or WB200_ERR_DEVICE_TIMEOUT; *detail (may be NULL) receives the raw word
+ * (low byte: which wait gave up; upper bits: block index). */
+int wb200_check_device_status(void* stream, int* detail);
+
+/* Bytes of the packed scale array for a [rows, K/32] scale matrix. */
+size_t wb200_packed_scale_bytes(int rows, int K);
+
+/* Row-major E8M0 scales -> packed layout. Replaces the host-side scale preshuffle
+ * e8m0_shuffle (wave_lang/kernel/wave/utils/mxfp_utils.py:113-128) of the reference's
+ * preshuffled templates. src_row_stride in bytes (K/32 when contiguous). */
+int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int K, void* dst,
+                        void* stream);
+
+/* Test aid: out[r, k] = E2M1(q) * 2^(scale - 127) as f32, the dequantised operand of
+ * mxfp4_to_f32 / e8m0_to_f32 (wave_lang/kernel/wave/utils/mxfp_utils.py:60-95). */
+int wb200_mxfp4_dequant(const void* q, const void* scale, int rows, int K, float* out, void* stream);
+
+/* Workspace the GEMM may need for this shape (0 when none). Only the skinny path uses one:
+ * f32 partial tiles plus per-tile counters. The first wb200_workspace_init'ed bytes hold the
+ * counters; a workspace must be initialised once before its first use and is left clean by
+ * every successful call. */
+size_t wb200_mxfp4_gemm_workspace_bytes(int M, int N, int K);
+int wb200_workspace_init(void* workspace, size_t bytes, void* stream);
+
+/* c = dequant(a, a_scale) * dequant(b, b_scale)^T, scales in packed layout.
+ * Replaces the launch of the kernel built from get_scaled_gemm_kernel / get_tagged_mxfp4_gemm
+ * (wave_lang/kernel/wave/templates/gemm.py:134-205, tagged_mxfp4_gemm.py:38-145) through
+ * wave_runtime.launch (runtime.cpp:123-203). Asynchronous on `stream`. */
+int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,
+                     const void* b_scale_packed, void* c, int c_dtype, long long ldc, void* workspace,
+                     size_t workspace_bytes, unsigned flags, void* stream);
+
+/* Grouped (per-expert) GEMM: group g computes c[row_offsets[g] : row_offsets[g+1], :] =
+ * a[rows of g] * b_g^T with its own weight matrix b_ptrs[g] ([N, K/2]) and packed scales
+ * b_scale_ptrs[g]. a is the gathered activation matrix [total_rows, K/2]; a_scale_packed is
+ * packed per group: group g's scales start at 128-row block row_block_offsets[g]. The pointer
+ * and offset arrays live in HOST memory. The reference has no grouped MXFP4 kernel; its MoE
+ * path loops a GEMM per expert from Python (tests/kernel/moe_test.py:183-240). */
+int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* row_block_offsets,
+                             int N, int K, const void* a, const void* a_scale_packed,
+                             const void* const* b_ptrs, const void* const* b_scale_ptrs, void* c,
+                             int c_dtype, long long ldc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WAVE_B200_H_ */

@@ -1,0 +1,181 @@
+"""CPU oracle for the MXFP4 scaled GEMM — TEST INFRASTRUCTURE, not a product path.
+
+A restatement, in torch on the CPU, of the reference's own CPU implementation of the path
+(`wave_lang/kernel/wave/utils/mxfp_utils.py`). Only `tests/`, `__graft_entry__.smoke()` and the
+CPU-baseline / reference legs of `bench.py` may import this module; the library itself has no CPU
+path and fails loudly without its CUDA extension.
+
+Parity is pinned: `tests/golden/make_golden.py` imports the reference module itself (in the build
+container, where the reference tree is mounted) and stores its outputs on seeded inputs;
+`tests/test_oracle.py` checks every function here against those stored outputs.
+
+Reference lines restated by each function are cited in its docstring.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+# wave_lang/kernel/wave/utils/mxfp_utils.py:17
+SCALE_GROUP_SIZE = 32
+
+# wave_lang/kernel/wave/utils/mxfp_utils.py:65-82 — E2M1 code -> value, sign in bit 3.
+E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
+
+
+def generate_gemm_afp4wfp4_inputs(shape, scale_lo: int = 124, scale_hi: int = 128, seed: int = 5):
+    """Seeded random packed-FP4 operands and E8M0 scales.
+
+    Follows wave_lang/kernel/wave/utils/mxfp_utils.py:20-57 call for call (same generator, same
+    draw order, same shapes), so that with the defaults the tensors equal the reference's:
+    x [M, K/2] uint8, w [K/2, N] uint8 (a transposed VIEW, as the reference returns it),
+    x_scales [M, K/32], w_scales [N, K/32]. `scale_hi` is exclusive.
+    """
+    M, N, K = shape
+    torch.manual_seed(seed)
+    x_low = torch.randint(0, 16, (M, K // 2), dtype=torch.uint8)
+    x_high = torch.randint(0, 16, (M, K // 2), dtype=torch.uint8)
+    x = x_low | (x_high << 4)
+    w_low = torch.randint(0, 16, (N, K // 2), dtype=torch.uint8)
+    w_high = torch.randint(0, 16, (N, K // 2), dtype=torch.uint8)
+    w = (w_low | (w_high << 4)).T
+    x_scales = torch.randint(scale_lo, scale_hi, (K // SCALE_GROUP_SIZE, M), dtype=torch.uint8)
+    w_scales = torch.randint(scale_lo, scale_hi, (K // SCALE_GROUP_SIZE, N), dtype=torch.uint8)
+    return x, w, x_scales.T.contiguous(), w_scales.T.contiguous()
+
+
+def mxfp4_to_f32(x: torch.Tensor) -> torch.Tensor:
+    """Packed E2M1 [R, K/2] uint8 -> [R, K] f32; even k is the low nibble.
+
+    wave_lang/kernel/wave/utils/mxfp_utils.py:60-83.
+    """
+    lut = torch.tensor(E2M1_VALUES, dtype=torch.float32)
+    out = torch.empty(x.shape[0], x.shape[1] * 2, dtype=torch.float32)
+    out[:, ::2] = lut[(x & 0xF).to(torch.int64)]
+    out[:, 1::2] = lut[(x >> 4).to(torch.int64)]
+    return out
+
+
+def e8m0_to_f32(x: torch.Tensor) -> torch.Tensor:
+    """E8M0 code (any numeric dtype) -> 2**(x - 127) as f32; code 255 is NaN.
+
+    wave_lang/kernel/wave/utils/mxfp_utils.py:86-95.
+    """
+    xf = x.to(torch.float32)
+    out = torch.pow(torch.tensor(2.0, dtype=torch.float32), xf - 127.0)
+    out[xf == 255] = float("nan")
+    return out
+
+
+def dequant_mxfp4(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """[R, K/2] codes and [R, K/32] scales -> dequantised [R, K] f32 operand.
+
+    The operand the reference feeds its matmul: wave_lang/kernel/wave/utils/mxfp_utils.py:135-143.
+    """
+    vals = mxfp4_to_f32(q)
+    s = e8m0_to_f32(scale.repeat_interleave(SCALE_GROUP_SIZE, dim=1).to(torch.float32))
+    return vals * s
+
+
+def torch_scaled_gemm_mxfp4(x, w, x_scales, w_scales) -> torch.Tensor:
+    """The reference GEMM: dequantise, then an f32 torch.mm. `w` is [K/2, N] as the reference passes it.
+
+    wave_lang/kernel/wave/utils/mxfp_utils.py:131-143.
+    """
+    x_f32 = mxfp4_to_f32(x)
+    w_f32 = mxfp4_to_f32(w.T).T
+    xs = e8m0_to_f32(x_scales.repeat_interleave(SCALE_GROUP_SIZE, dim=1).to(torch.float32))
+    ws = e8m0_to_f32(w_scales.repeat_interleave(SCALE_GROUP_SIZE, dim=1).to(torch.float32))
+    return torch.mm(x_f32 * xs, w_f32 * ws.T)
+
+
+def scaled_gemm(a, a_scale, b, b_scale, n_chunk: int = 4096) -> torch.Tensor:
+    """Same as torch_scaled_gemm_mxfp4 with b in the kernel's [N, K/2] layout, evaluated in column
+    chunks of C so that large N does not need the whole dequantised b at once."""
+    a_deq = dequant_mxfp4(a, a_scale)
+    N = b.shape[0]
+    out = torch.empty(a.shape[0], N, dtype=torch.float32)
+    for n0 in range(0, N, n_chunk):
+        n1 = min(N, n0 + n_chunk)
+        out[:, n0:n1] = torch.mm(a_deq, dequant_mxfp4(b[n0:n1], b_scale[n0:n1]).T)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Layout oracle for the scale repack (no counterpart in the reference: its e8m0_shuffle,
+# mxfp_utils.py:113-128, targets the AMD layout; this states the tcgen05 scale-factor layout)
+# ---------------------------------------------------------------------------------------------
+SF_PAD = 127
+
+
+def pack_scales(scale: torch.Tensor) -> torch.Tensor:
+    """[rows, K/32] uint8 -> flat uint8 array of 512-byte atoms.
+
+    One atom holds 128 rows x 4 K-blocks; the byte of (row r, K-block j) inside its atom is
+    (r % 32) * 16 + (r // 32) * 4 + j; atoms of one 128-row block are contiguous along K; the
+    atom count along K is rounded up to an even number; padding bytes are 127.
+    """
+    s = scale.numpy()
+    rows, kb = s.shape
+    rb = (rows + 127) // 128
+    ka = 2 * ((kb * 32 + 255) // 256)
+    padded = np.full((rb * 128, ka * 4), SF_PAD, dtype=np.uint8)
+    padded[:rows, :kb] = s
+    # [rb, r/32 (4), r%32 (32), ka, j (4)] -> [rb, ka, r%32, r/32, j]
+    v = padded.reshape(rb, 4, 32, ka, 4).transpose(0, 3, 2, 1, 4)
+    return torch.from_numpy(np.ascontiguousarray(v).reshape(-1))
+
+
+# ---------------------------------------------------------------------------------------------
+# Harness quantiser (not in the reference, which only feeds random codes): f32 -> MXFP4
+# ---------------------------------------------------------------------------------------------
+def quantize_mxfp4(x: torch.Tensor):
+    """f32 [R, K] -> (codes [R, K/2] uint8, scales [R, K/32] uint8).
+
+    Per 32-element block: e = floor(log2(amax)) - 2 (E2M1's largest value is 6 = 1.5 * 2^2), scale
+    byte clamp(e + 127, 0, 254), amax == 0 -> e = 0; values x * 2^-e clamped to [-6, 6] and rounded
+    to the nearest E2M1 value, ties to the even code; low nibble = even k.
+    """
+    R, K = x.shape
+    assert K % SCALE_GROUP_SIZE == 0
+    xb = x.reshape(R, K // 32, 32).to(torch.float32)
+    amax = xb.abs().amax(dim=2)
+    e = torch.floor(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)))) - 2.0
+    e = torch.where(amax > 0, e, torch.zeros_like(e))
+    sb = torch.clamp(e + 127.0, 0, 254)
+    scale = torch.pow(torch.tensor(2.0), sb - 127.0).unsqueeze(2)
+    y = torch.clamp(xb / scale, -6.0, 6.0)
+    mag = y.abs()
+    grid = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    # nearest grid value, ties to the even index
+    d = (mag.unsqueeze(-1) - grid).abs()
+    idx = d.argmin(dim=-1)
+    # argmin takes the lower index on ties; move to the upper one when the lower is odd
+    upper = torch.clamp(idx + 1, max=7)
+    tie = (d.gather(-1, upper.unsqueeze(-1)).squeeze(-1) == d.gather(-1, idx.unsqueeze(-1)).squeeze(-1)) & (upper != idx)
+    idx = torch.where(tie & (idx % 2 == 1), upper, idx)
+    code = (idx + torch.where(torch.signbit(y), 8, 0)).to(torch.uint8).reshape(R, K)
+    packed = code[:, 0::2] | (code[:, 1::2] << 4)
+    return packed.contiguous(), sb.to(torch.uint8).contiguous()
+
+
+# ---------------------------------------------------------------------------------------------
+# Tolerances of the parity bar
+# ---------------------------------------------------------------------------------------------
+def f32_tolerance(a_deq: torch.Tensor, b_deq: torch.Tensor, ref: torch.Tensor, K: int) -> torch.Tensor:
+    """|c - ref| must stay below rtol 1e-5 * |ref| + 1e-5 * sqrt(K) * amax_ij with
+    amax_ij = max_k |A_ik| * max_k |B_jk| over the dequantised rows."""
+    amax = a_deq.abs().amax(dim=1, keepdim=True) * b_deq.abs().amax(dim=1, keepdim=True).T
+    return 1e-5 * ref.abs() + 1e-5 * math.sqrt(K) * amax
+
+
+def bf16_ulp_distance(c_bf16: torch.Tensor, ref_f32: torch.Tensor) -> torch.Tensor:
+    """Distance, in bf16 units in the last place, between c and the reference rounded to bf16.
+    The 16-bit patterns are mapped to a monotonic integer line so that +0 and -0 coincide."""
+    def ordered(t):
+        bits = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+        return torch.where(bits >= 0x8000, 0x8000 - bits, bits)
+    return (ordered(c_bf16.cpu()) - ordered(ref_f32.to(torch.bfloat16))).abs()

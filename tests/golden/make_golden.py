@@ -1,0 +1,79 @@
+"""Generate the golden fixtures in this folder from the reference itself.
+
+Run in the build container, where the reference tree is mounted read-only:
+
+    python tests/golden/make_golden.py /root/reference
+
+It imports the reference's own module `wave_lang/kernel/wave/utils/mxfp_utils.py` (pure torch; it
+runs on the CPU without the reference's compiler stack) and stores its outputs on seeded inputs as
+small .npz files. The tests compare the oracle in `oracle/` and, on a GPU, the CUDA kernels
+against these files, so the pin travels to machines that do not have the reference.
+"""
+
+import hashlib
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def main(ref_root: str) -> None:
+    sys.path.insert(0, ref_root)
+    from wave_lang.kernel.wave.utils import mxfp_utils as ref  # noqa: E402
+
+    torch.set_num_threads(1)  # fixed summation order inside torch.mm for the stored GEMM outputs
+
+    # 1. Known-answer tables: every packed byte, every scale code.
+    all_bytes = torch.arange(256, dtype=torch.uint8).reshape(1, 256)
+    e2m1 = ref.mxfp4_to_f32(all_bytes.clone())
+    e8m0 = ref.e8m0_to_f32(torch.arange(256, dtype=torch.float32))
+    np.savez_compressed(HERE / "kat_codecs.npz", bytes=all_bytes.numpy(), e2m1_f32=e2m1.numpy(),
+                        e8m0_f32=e8m0.numpy())
+
+    # 2. The reference's own input generator (seed 5) and GEMM on a small shape.
+    shape = (64, 96, 128)
+    x, w, xs, ws = ref.generate_gemm_afp4wfp4_inputs(shape, device=torch.device("cpu"))
+    out = ref.torchScaledGemmMXFP4(x, w, xs, ws)
+    np.savez_compressed(HERE / "gemm_seed5_64x96x128.npz", x=x.numpy(), w=np.ascontiguousarray(w.numpy()),
+                        x_scales=xs.numpy(), w_scales=ws.numpy(), out=out.numpy())
+
+    # 3. Wider scale range [124, 130] (the 1024^3 config's distribution) on a ragged small shape,
+    #    with the NaN code and the extreme scale codes planted in known places.
+    g = torch.Generator().manual_seed(77)
+    M, N, K = 48, 80, 256
+    a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, generator=g)
+    b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+    a_s = torch.randint(124, 131, (M, K // 32), dtype=torch.uint8, generator=g)
+    b_s = torch.randint(124, 131, (N, K // 32), dtype=torch.uint8, generator=g)
+    out = ref.torchScaledGemmMXFP4(a, b.T, a_s, b_s)
+    a_deq = ref.mxfp4_to_f32(a.clone()) * ref.e8m0_to_f32(a_s.repeat_interleave(32, dim=1).to(torch.float32))
+    edge_s = a_s.clone()
+    edge_s[0, 0], edge_s[1, 1], edge_s[2, 2], edge_s[3, 3] = 255, 0, 254, 1
+    edge_deq = ref.mxfp4_to_f32(a.clone()) * ref.e8m0_to_f32(edge_s.repeat_interleave(32, dim=1).to(torch.float32))
+    np.savez_compressed(HERE / "gemm_wide_scales_48x80x256.npz", a=a.numpy(), b=b.numpy(), a_scale=a_s.numpy(),
+                        b_scale=b_s.numpy(), out=out.numpy(), a_deq=a_deq.numpy(), edge_scale=edge_s.numpy(),
+                        edge_deq=edge_deq.numpy())
+
+    # 4. The reference's AMD preshuffles (kept in the API for parity).
+    sc = torch.randint(0, 256, (300, 40), dtype=torch.uint8, generator=g)
+    bb = torch.randint(0, 256, (64, 128), dtype=torch.uint8, generator=g)
+    np.savez_compressed(HERE / "preshuffle.npz", scale=sc.numpy(), scale_shuffled=ref.e8m0_shuffle(sc).numpy(),
+                        b=bb.numpy(), b_shuffled=ref.b_preshuffle(bb).numpy())
+
+    # 5. The 1024^3 seed-5 case of the reference's tests: digests of the inputs and a strided
+    #    sample of the output (the full arrays are too large to commit).
+    x, w, xs, ws = ref.generate_gemm_afp4wfp4_inputs((1024, 1024, 1024), device=torch.device("cpu"))
+    torch.set_num_threads(8)
+    out = ref.torchScaledGemmMXFP4(x, w, xs, ws)
+    digest = {k: hashlib.sha256(np.ascontiguousarray(v.numpy()).tobytes()).hexdigest()
+              for k, v in dict(x=x, w=w, x_scales=xs, w_scales=ws).items()}
+    np.savez_compressed(HERE / "gemm_seed5_1024_sample.npz", out_sample=out[::64, ::64].numpy(),
+                        **{f"sha256_{k}": np.array(v) for k, v in digest.items()})
+    print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

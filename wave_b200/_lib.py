@@ -1,0 +1,111 @@
+"""ctypes binding of libwave_b200.so (the C ABI declared in include/wave_b200.h).
+
+There is no CPU fallback: when the shared library is missing or a call fails, an exception is
+raised. Error classes follow the reference's launch path, which raises RuntimeError for device
+errors (wave_lang/kernel/wave/runtime/runtime.cpp:96-109) and ValueError for bad arguments
+(wave_lang/kernel/wave/utils/run_utils.py:110-121, wave_lang/kernel/wave/compile.py:1489-1500).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+WB200_OK = 0
+WB200_ERR_INVALID_ARG = -1
+WB200_ERR_ALIGNMENT = -2
+WB200_ERR_WORKSPACE = -3
+WB200_ERR_UNSUPPORTED = -4
+WB200_ERR_DEVICE_TIMEOUT = -5
+WB200_ERR_CUDA = -6
+
+WB200_F32 = 0
+WB200_BF16 = 1
+
+PATH_AUTO = 0
+PATH_TILE_1CTA = 1
+PATH_TILE_2CTA = 2
+PATH_SKINNY = 3
+TILE_N128 = 0x10
+
+# Every symbol include/wave_b200.h declares; tests check that the built library exports them all.
+EXPORTED_SYMBOLS = (
+    "wb200_version",
+    "wb200_last_error",
+    "wb200_check_device_status",
+    "wb200_packed_scale_bytes",
+    "wb200_repack_scales",
+    "wb200_mxfp4_dequant",
+    "wb200_mxfp4_gemm_workspace_bytes",
+    "wb200_workspace_init",
+    "wb200_mxfp4_gemm",
+    "wb200_mxfp4_grouped_gemm",
+)
+
+
+class DeviceTimeoutError(RuntimeError):
+    """A bounded device-side wait gave up; the outputs of the affected launches are invalid."""
+
+
+def library_path() -> Path:
+    env = os.environ.get("WAVE_B200_LIB")
+    if env:
+        return Path(env)
+    return Path(__file__).resolve().parent / "libwave_b200.so"
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once. Raises RuntimeError when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not path.exists():
+        raise RuntimeError(
+            f"{path} not found: build it with `python -m wave_b200.build` (needs nvcc for sm_100a). "
+            "wave_b200 has no CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(str(path))
+    c_void_p, c_int, c_size_t, c_ll, c_uint = (
+        ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_longlong, ctypes.c_uint)
+    lib.wb200_version.restype = c_int
+    lib.wb200_version.argtypes = []
+    lib.wb200_last_error.restype = ctypes.c_char_p
+    lib.wb200_last_error.argtypes = []
+    lib.wb200_check_device_status.restype = c_int
+    lib.wb200_check_device_status.argtypes = [c_void_p, ctypes.POINTER(c_int)]
+    lib.wb200_packed_scale_bytes.restype = c_size_t
+    lib.wb200_packed_scale_bytes.argtypes = [c_int, c_int]
+    lib.wb200_repack_scales.restype = c_int
+    lib.wb200_repack_scales.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p]
+    lib.wb200_mxfp4_dequant.restype = c_int
+    lib.wb200_mxfp4_dequant.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    lib.wb200_mxfp4_gemm_workspace_bytes.restype = c_size_t
+    lib.wb200_mxfp4_gemm_workspace_bytes.argtypes = [c_int, c_int, c_int]
+    lib.wb200_workspace_init.restype = c_int
+    lib.wb200_workspace_init.argtypes = [c_void_p, c_size_t, c_void_p]
+    lib.wb200_mxfp4_gemm.restype = c_int
+    lib.wb200_mxfp4_gemm.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_ll, c_void_p, c_size_t, c_uint, c_void_p]
+    lib.wb200_mxfp4_grouped_gemm.restype = c_int
+    lib.wb200_mxfp4_grouped_gemm.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, c_int,
+                                             c_void_p, c_void_p, ctypes.POINTER(c_void_p),
+                                             ctypes.POINTER(c_void_p), c_void_p, c_int, c_ll, c_void_p]
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    """Turn a status code of the C ABI into the exception class the reference would raise."""
+    if rc == WB200_OK:
+        return
+    msg = load().wb200_last_error().decode("utf-8", "replace")
+    if rc in (WB200_ERR_INVALID_ARG, WB200_ERR_ALIGNMENT, WB200_ERR_WORKSPACE):
+        raise ValueError(f"wave_b200: {msg}")
+    if rc == WB200_ERR_DEVICE_TIMEOUT:
+        raise DeviceTimeoutError(f"wave_b200: {msg}")
+    raise RuntimeError(f"wave_b200: {msg} (status {rc})")

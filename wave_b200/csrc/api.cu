@@ -1,0 +1,379 @@
+// C ABI of the wave_b200 library: argument checks, TMA descriptor set-up, path selection and
+// launches. Plays the role of the reference's native launch shim
+// (wave_lang/kernel/wave/runtime/runtime.cpp:123-263) for the MXFP4 scaled-GEMM kernels.
+#include "../../include/wave_b200.h"
+#include "gemm_sm100.cuh"
+#include "scales.cuh"
+#include "skinny_sm100.cuh"
+
+#include <cudaTypedefs.h>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define WB_CUDA(expr)                                                                           \
+  do {                                                                                          \
+    cudaError_t e__ = (expr);                                                                   \
+    if (e__ != cudaSuccess)                                                                     \
+      return fail(WB200_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, \
+                  __LINE__);                                                                    \
+  } while (0)
+
+// Device status word written by kernels whose bounded waits give up.
+__device__ int g_status_word[4];
+
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0;
+  int* status_ptr = nullptr;
+};
+DeviceInfo g_dev[kMaxDevices];
+std::mutex g_mu;
+PFN_cuTensorMapEncodeTiled g_encode = nullptr;
+
+int get_device(DeviceInfo** out) {
+  int dev = 0;
+  WB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(WB200_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    WB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    WB_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (d.cc_major != 10)
+      return fail(WB200_ERR_UNSUPPORTED, "device %d has compute capability %d.x; this library is sm_100a only",
+                  dev, d.cc_major);
+    void* sp = nullptr;
+    WB_CUDA(cudaGetSymbolAddress(&sp, g_status_word));
+    d.status_ptr = static_cast<int*>(sp);
+    WB_CUDA(cudaMemset(sp, 0, sizeof(int) * 4));
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      WB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (qres != cudaDriverEntryPointSuccess || !fn)
+        return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+    }
+    d.ready = true;
+  }
+  *out = &d;
+  return WB200_OK;
+}
+
+// [rows, row_bytes] uint8 matrix, box = 128 bytes x box_rows, 128-byte swizzle, zero fill.
+int make_operand_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_rows) {
+  cuuint64_t dims[2] = {cuuint64_t(row_bytes), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(row_bytes)};
+  cuuint32_t box[2] = {128u, cuuint32_t(box_rows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows %lld, row bytes %lld)", int(r),
+                rows, row_bytes);
+  return WB200_OK;
+}
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  WB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return WB200_OK;
+}
+
+int check_common(int M, int N, int K, const void* a, const void* as, const void* b, const void* bs, const void* c,
+                 int c_dtype, long long ldc) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(WB200_ERR_INVALID_ARG, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
+  if (K % 32 != 0) return fail(WB200_ERR_INVALID_ARG, "K = %d is not a multiple of the scale group size 32", K);
+  if (!a || !as || !b || !bs || !c) return fail(WB200_ERR_INVALID_ARG, "null tensor pointer");
+  if (c_dtype != WB200_F32 && c_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "unknown output dtype %d", c_dtype);
+  if (ldc < N) return fail(WB200_ERR_INVALID_ARG, "ldc = %lld is smaller than N = %d", ldc, N);
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
+    return fail(WB200_ERR_ALIGNMENT, "a and b must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(as) & 15) || (reinterpret_cast<uintptr_t>(bs) & 15))
+    return fail(WB200_ERR_ALIGNMENT, "packed scale arrays must be 16-byte aligned");
+  const int esz = (c_dtype == WB200_F32) ? 4 : 2;
+  if (reinterpret_cast<uintptr_t>(c) % esz) return fail(WB200_ERR_ALIGNMENT, "c is not aligned to its element size");
+  return WB200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// tile paths
+// ------------------------------------------------------------------------------------------
+template <int CG, int BN, int STAGES, typename OutT>
+int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
+                const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, cudaStream_t stream) {
+  using Cfg = wb::GemmCfg<CG, BN, STAGES>;
+  CUtensorMap tmA, tmB;
+  int rc = make_operand_map(&tmA, a, M, K / 2, Cfg::BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tmB, b, N, K / 2, Cfg::B_ROWS);
+  if (rc) return rc;
+  wb::GemmParams p;
+  p.sfa = static_cast<const uint8_t*>(as);
+  p.sfb = static_cast<const uint8_t*>(bs);
+  p.c = c;
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = int(ldc);
+  p.ka_atoms = wb::sf_k_atoms(K);
+  p.sfa_row_blocks = sfa_row_blocks;
+  p.sfb_row_blocks = sfb_row_blocks;
+  p.tiles_m = (M + Cfg::BM * CG - 1) / (Cfg::BM * CG);
+  p.tiles_n = (N + BN - 1) / BN;
+  p.group_n = 16;
+  const int esz = int(sizeof(OutT));
+  p.vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0) ? 1 : 0;
+  p.status = dev.status_ptr;
+  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, STAGES, OutT>;
+  rc = set_smem(kernel, Cfg::SMEM_BYTES);
+  if (rc) return rc;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n;
+  const int units = dev.sm_count / CG;  // CTAs or CTA pairs that fit at one per SM
+  const int grid = int(tiles < units ? tiles : units) * CG;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p));
+  return WB200_OK;
+}
+
+template <int CG, int BN, int STAGES>
+int launch_tile_dtype(int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as,
+                      const void* b, const void* bs, void* c, long long ldc, int sfa_rb, int sfb_rb,
+                      cudaStream_t stream) {
+  if (c_dtype == WB200_F32)
+    return launch_tile<CG, BN, STAGES, float>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+  return launch_tile<CG, BN, STAGES, __nv_bfloat16>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+}
+
+int dispatch_tile(unsigned path, bool n128, int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a,
+                  const void* as, const void* b, const void* bs, void* c, long long ldc, int sfa_rb, int sfb_rb,
+                  cudaStream_t stream) {
+  if (path == WB200_PATH_TILE_2CTA) {
+    if (n128) return launch_tile_dtype<2, 128, 8>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+    return launch_tile_dtype<2, 256, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+  }
+  if (n128) return launch_tile_dtype<1, 128, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+  return launch_tile_dtype<1, 256, 4>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// skinny path
+// ------------------------------------------------------------------------------------------
+constexpr size_t kCounterBytes = 16384;  // room for 4096 N tiles (N up to 524288)
+
+size_t skinny_workspace_bytes(int sm_count, int M) {
+  return kCounterBytes + size_t(2) * sm_count * M * 128 * sizeof(float);
+}
+
+template <int NP, int STAGES, typename OutT>
+int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
+                  const void* bs, void* c, long long ldc, void* ws, cudaStream_t stream) {
+  using Cfg = wb::SkinnyCfg<NP, STAGES>;
+  CUtensorMap tmW, tmX;
+  int rc = make_operand_map(&tmW, b, N, K / 2, 128);
+  if (rc) return rc;
+  rc = make_operand_map(&tmX, a, M, K / 2, NP);
+  if (rc) return rc;
+  wb::SkinnyParams p;
+  p.sfw = static_cast<const uint8_t*>(bs);
+  p.sfx = static_cast<const uint8_t*>(as);
+  p.c = c;
+  p.counters = static_cast<unsigned int*>(ws);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kCounterBytes);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = int(ldc);
+  p.ka_atoms = wb::sf_k_atoms(K);
+  p.sfw_row_blocks = wb::sf_row_blocks(N);
+  p.tiles_n = (N + 127) / 128;
+  p.num_kb = (K + 255) / 256;
+  p.status = dev.status_ptr;
+  auto kernel = wb::mxfp4_skinny_kernel<NP, STAGES, OutT>;
+  rc = set_smem(kernel, Cfg::SMEM_BYTES);
+  if (rc) return rc;
+  const long long units = (long long)p.tiles_n * p.num_kb;
+  const int grid = int(units < dev.sm_count ? units : dev.sm_count);
+  kernel<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, p);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+template <typename OutT>
+int dispatch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
+                    const void* bs, void* c, long long ldc, void* ws, cudaStream_t stream) {
+  if (M <= 16) return launch_skinny<16, 10, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, stream);
+  if (M <= 32) return launch_skinny<32, 9, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, stream);
+  if (M <= 64) return launch_skinny<64, 8, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, stream);
+  return launch_skinny<128, 6, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int wb200_version(void) { return 1000; }
+
+const char* wb200_last_error(void) { return g_err; }
+
+int wb200_check_device_status(void* stream, int* detail) {
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int word = 0;
+  WB_CUDA(cudaMemcpyAsync(&word, dev->status_ptr, sizeof(int), cudaMemcpyDeviceToHost, s));
+  WB_CUDA(cudaStreamSynchronize(s));
+  if (detail) *detail = word;
+  if (word != 0) {
+    WB_CUDA(cudaMemsetAsync(dev->status_ptr, 0, sizeof(int), s));
+    return fail(WB200_ERR_DEVICE_TIMEOUT, "device-side wait %d gave up in block %d; results of the last launches are invalid",
+                word & 0xff, word >> 8);
+  }
+  return WB200_OK;
+}
+
+size_t wb200_packed_scale_bytes(int rows, int K) {
+  if (rows <= 0 || K <= 0) return 0;
+  return wb::sf_packed_bytes(rows, K);
+}
+
+int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int K, void* dst, void* stream) {
+  if (rows <= 0 || K <= 0 || K % 32 != 0)
+    return fail(WB200_ERR_INVALID_ARG, "repack_scales: rows = %d, K = %d (K must be a positive multiple of 32)", rows, K);
+  if (!src || !dst) return fail(WB200_ERR_INVALID_ARG, "repack_scales: null pointer");
+  if (src_row_stride < K / 32) return fail(WB200_ERR_INVALID_ARG, "repack_scales: row stride %lld < K/32 = %d", src_row_stride, K / 32);
+  if (reinterpret_cast<uintptr_t>(dst) & 15) return fail(WB200_ERR_ALIGNMENT, "repack_scales: dst must be 16-byte aligned");
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  const int k_atoms = wb::sf_k_atoms(K);
+  dim3 grid((k_atoms + 7) / 8, wb::sf_row_blocks(rows));
+  wb::repack_scales_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), src_row_stride, rows, K / 32, k_atoms, static_cast<uint8_t*>(dst));
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+int wb200_mxfp4_dequant(const void* q, const void* scale, int rows, int K, float* out, void* stream) {
+  if (rows <= 0 || K <= 0 || K % 32 != 0)
+    return fail(WB200_ERR_INVALID_ARG, "dequant: rows = %d, K = %d (K must be a positive multiple of 32)", rows, K);
+  if (!q || !scale || !out) return fail(WB200_ERR_INVALID_ARG, "dequant: null pointer");
+  if (reinterpret_cast<uintptr_t>(out) & 7) return fail(WB200_ERR_ALIGNMENT, "dequant: out must be 8-byte aligned");
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  const long long total = (long long)rows * (K / 2);
+  const unsigned blocks = unsigned((total + 255) / 256);
+  wb::dequant_mxfp4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(q), static_cast<const uint8_t*>(scale), rows, K, out);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+size_t wb200_mxfp4_gemm_workspace_bytes(int M, int N, int K) {
+  (void)N; (void)K;
+  if (M <= 0 || M > 128) return 0;
+  // 148 SMs on B200; sized for up to 160 so the same buffer fits any sm_100 part.
+  return skinny_workspace_bytes(160, M);
+}
+
+int wb200_workspace_init(void* workspace, size_t bytes, void* stream) {
+  if (!workspace || bytes == 0) return fail(WB200_ERR_INVALID_ARG, "workspace_init: empty workspace");
+  const size_t n = bytes < kCounterBytes ? bytes : kCounterBytes;
+  WB_CUDA(cudaMemsetAsync(workspace, 0, n, static_cast<cudaStream_t>(stream)));
+  return WB200_OK;
+}
+
+int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,
+                     const void* b_scale_packed, void* c, int c_dtype, long long ldc, void* workspace,
+                     size_t workspace_bytes, unsigned flags, void* stream) {
+  int rc = check_common(M, N, K, a, a_scale_packed, b, b_scale_packed, c, c_dtype, ldc);
+  if (rc) return rc;
+  DeviceInfo* dev;
+  rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned path = flags & WB200_PATH_MASK;
+  if (path > WB200_PATH_SKINNY) return fail(WB200_ERR_INVALID_ARG, "unknown path flag %u", path);
+  const bool n128_forced = (flags & WB200_TILE_N128) != 0;
+  if (path == WB200_PATH_AUTO) {
+    const bool ws_ok = workspace && workspace_bytes >= skinny_workspace_bytes(dev->sm_count, M);
+    if (M <= 128 && ws_ok) path = WB200_PATH_SKINNY;
+    else path = (M > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
+  }
+  if (path == WB200_PATH_SKINNY) {
+    if (M > 128) return fail(WB200_ERR_UNSUPPORTED, "the skinny path handles M <= 128 (got %d)", M);
+    if (N > 4096 * 128) return fail(WB200_ERR_UNSUPPORTED, "the skinny path handles N <= 524288 (got %d)", N);
+    if (!workspace || workspace_bytes < skinny_workspace_bytes(dev->sm_count, M))
+      return fail(WB200_ERR_WORKSPACE, "the skinny path needs a workspace of %zu bytes (got %zu)",
+                  skinny_workspace_bytes(dev->sm_count, M), workspace ? workspace_bytes : size_t(0));
+    if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(WB200_ERR_ALIGNMENT, "workspace must be 16-byte aligned");
+    if (c_dtype == WB200_F32)
+      return dispatch_skinny<float>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, s);
+    return dispatch_skinny<__nv_bfloat16>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, s);
+  }
+  // Narrow problems fill more SMs with 128-wide tiles.
+  bool n128 = n128_forced;
+  if (!n128_forced && (flags & WB200_PATH_MASK) == WB200_PATH_AUTO) {
+    const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+    if (tiles256 < dev->sm_count) n128 = true;
+  }
+  return dispatch_tile(path, n128, c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc,
+                       wb::sf_row_blocks(M), wb::sf_row_blocks(N), s);
+}
+
+int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* row_block_offsets, int N, int K,
+                             const void* a, const void* a_scale_packed, const void* const* b_ptrs,
+                             const void* const* b_scale_ptrs, void* c, int c_dtype, long long ldc, void* stream) {
+  if (num_groups <= 0 || !row_offsets || !row_block_offsets || !b_ptrs || !b_scale_ptrs)
+    return fail(WB200_ERR_INVALID_ARG, "grouped gemm: bad group description");
+  if (K <= 0 || K % 32 != 0) return fail(WB200_ERR_INVALID_ARG, "K = %d is not a positive multiple of 32", K);
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  const int esz = (c_dtype == WB200_F32) ? 4 : 2;
+  const size_t atom_row_bytes = size_t(wb::sf_k_atoms(K)) * 512;
+  for (int g = 0; g < num_groups; ++g) {
+    const int r0 = row_offsets[g], r1 = row_offsets[g + 1];
+    if (r1 < r0) return fail(WB200_ERR_INVALID_ARG, "grouped gemm: row offsets decrease at group %d", g);
+    const int Mg = r1 - r0;
+    if (Mg == 0) continue;
+    const uint8_t* ag = static_cast<const uint8_t*>(a) + size_t(r0) * (K / 2);
+    const uint8_t* asg = static_cast<const uint8_t*>(a_scale_packed) + size_t(row_block_offsets[g]) * atom_row_bytes;
+    uint8_t* cg = static_cast<uint8_t*>(c) + size_t(r0) * ldc * esz;
+    rc = check_common(Mg, N, K, ag, asg, b_ptrs[g], b_scale_ptrs[g], cg, c_dtype, ldc);
+    if (rc) return rc;
+    const unsigned path = (Mg > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
+    rc = dispatch_tile(path, false, c_dtype, *dev, Mg, N, K, ag, asg, b_ptrs[g], b_scale_ptrs[g], cg, ldc,
+                       wb::sf_row_blocks(Mg), wb::sf_row_blocks(N), static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+  }
+  return WB200_OK;
+}
+
+}  // extern "C"

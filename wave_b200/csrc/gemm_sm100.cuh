@@ -1,0 +1,342 @@
+// MXFP4 x MXFP4 block-scaled GEMM for sm_100a: C[M,N] = dequant(A) * dequant(B)^T.
+//
+// Replaces, for this one kernel family, what the reference generates from its scaled-GEMM
+// templates (wave_lang/kernel/wave/templates/gemm.py:134-205 and
+// wave_lang/kernel/wave/templates/tagged_mxfp4_gemm.py:38-145): the K loop of
+// read -> bitcast -> scaled_mma and the f32 / bf16 write of C.
+//
+// Shape of the kernel
+//   * persistent: one CTA (or CTA pair) per SM walks a static list of output tiles in an
+//     N-grouped order (same intent as tagged_mxfp4_gemm.py:1038-1089: keep the A rows in L2
+//     while a group of N tiles is swept down M);
+//   * warp-specialised: warp 0 issues TMA loads, warp 1 issues tcgen05.cp / tcgen05.mma,
+//     warps 2..5 drain the accumulator (tcgen05.ld -> convert -> 16-byte stores);
+//   * A and B tiles arrive as rows of 128 bytes (256 packed E2M1 values) with the 128-byte
+//     swizzle; scale factors arrive as 512-byte atoms (128 rows x 4 K-blocks) and are copied to
+//     tensor memory with tcgen05.cp before the four K = 64 MMAs of a stage;
+//   * two accumulators live in tensor memory so that the epilogue of tile i overlaps the main
+//     loop of tile i+1. With BN = 256 the two accumulators overlap by 32 columns (512 columns
+//     cannot hold 2 x 256 plus the scale factors); the epilogue drains the shared columns first
+//     and releases the next main loop as soon as they are free;
+//   * CG = 2 pairs two CTAs of a cluster on one 256-row tile (cta_group::2): each CTA loads its
+//     own 128 rows of A and its half of the B rows with plain TMA loads (no multicast).
+#pragma once
+#include "ptx.cuh"
+#include <cuda_bf16.h>
+
+namespace wb {
+
+template <int CG, int BN_, int STAGES_>
+struct GemmCfg {
+  static constexpr int BM = 128;  // accumulator rows per CTA (tensor-memory lanes)
+  static constexpr int BN = BN_;
+  static constexpr int BK = 256;  // K elements per pipeline stage = one 128-byte swizzle row
+  static constexpr int STAGES = STAGES_;
+  static constexpr int B_ROWS = BN / CG;  // B rows this CTA loads
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = B_ROWS * 128;
+  static constexpr int SFA_BYTES = 2 * 512;               // 128 rows x 8 K-blocks
+  static constexpr int SFB_BYTES = (BN / 128) * 2 * 512;  // BN rows x 8 K-blocks
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int NUM_BARRIERS = 3 * STAGES + 4;
+  static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
+  // tensor-memory columns
+  static constexpr int TMEM_COLS = 512;
+  static constexpr bool OVERLAP = (BN == 256);
+  static constexpr int ACC_COL0 = 0;
+  static constexpr int ACC_COL1 = OVERLAP ? 224 : BN;
+  static constexpr int SFA_COL = 480;  // 8 columns: 2 atoms x 4
+  static constexpr int SFB_COL = 488;  // (BN/128) * 8 columns
+  static constexpr int THREADS = 192;
+  static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
+  static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+};
+
+struct GemmParams {
+  const uint8_t* sfa;  // A scales, atom layout
+  const uint8_t* sfb;  // B scales, atom layout
+  void* c;
+  int M, N, K;
+  int ldc;            // elements
+  int ka_atoms;       // 512-byte atoms per 128-row block (2 per 256 K elements)
+  int sfa_row_blocks;  // 128-row blocks in the A scale array
+  int sfb_row_blocks;
+  int tiles_m, tiles_n;
+  int group_n;        // N tiles per raster group
+  int vec_ok;         // C base and row pitch allow 16-byte stores
+  int* status;
+};
+
+// Tile order: groups of `group_n` N tiles, each group swept down M with N fastest.
+__device__ __forceinline__ void raster_tile(int t, int tiles_m, int tiles_n, int group_n, int& mt,
+                                            int& nt) {
+  const int per_group = group_n * tiles_m;
+  const int g = t / per_group;
+  const int r = t - g * per_group;
+  const int n0 = g * group_n;
+  const int gw = min(group_n, tiles_n - n0);
+  mt = r / gw;
+  nt = n0 + (r - mt * gw);
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk32(OutT* __restrict__ p, const uint32_t (&r)[32],
+                                              int ncols, bool vec) {
+  if constexpr (sizeof(OutT) == 4) {
+    if (vec && ncols == 32) {
+      uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) reinterpret_cast<uint32_t*>(p)[j] = r[j];
+    }
+  } else {
+    if (vec && ncols == 32) {
+      uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+        v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+        v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+        v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        q[j] = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) p[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+    }
+  }
+}
+
+template <int CG, int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(192, 1)
+mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const GemmParams p) {
+  using Cfg = GemmCfg<CG, BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the 128-byte swizzle; identical offset in both CTAs of a pair.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const bool leader = (rank == 0);
+
+  // barrier block after the stages
+  const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto peer_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto acc_full_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + s); };
+  auto acc_empty_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + 2 + s); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::NUM_BARRIERS * 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  WaitCtx ctx{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(peer_full_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(acc_full_bar(s), 1);
+      mbar_init(acc_empty_bar(s), 4 * CG);
+    }
+    *abort_flag = 0u;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<CG>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish<CG>();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CG == 2) {  // peer barriers must exist before anyone signals them
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int first_tile = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+  const int tile_step = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
+  const int num_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int t = first_tile; t < num_tiles; t += tile_step) {
+        int mt, nt;
+        raster_tile(t, p.tiles_m, p.tiles_n, p.group_n, mt, nt);
+        const int a_row = (mt * CG + int(rank)) * Cfg::BM;
+        const int b_row = nt * BN + int(rank) * Cfg::B_ROWS;
+        const int sfa_rb = min(mt * CG + int(rank), p.sfa_row_blocks - 1);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const uint32_t sSFA = sB + Cfg::B_BYTES;
+          const uint32_t sSFB = sSFA + Cfg::SFA_BYTES;
+          const uint32_t fb = full_bar(stage);
+          mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+          tma_load_2d(sA, &tmA, kb * 128, a_row, fb);
+          if constexpr (Cfg::B_ROWS <= 256) tma_load_2d(sB, &tmB, kb * 128, b_row, fb);
+          bulk_load(sSFA, p.sfa + (size_t(sfa_rb) * p.ka_atoms + 2 * kb) * 512, 1024, fb);
+#pragma unroll
+          for (int j = 0; j < BN / 128; ++j) {
+            const int rb = min(nt * (BN / 128) + j, p.sfb_row_blocks - 1);
+            bulk_load(sSFB + j * 1024, p.sfb + (size_t(rb) * p.ka_atoms + 2 * kb) * 512, 1024, fb);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer / peer relay
+    if (lane == 0) {
+      if (leader) {
+        constexpr uint32_t idesc = make_idesc_mxf4(Cfg::BM * CG, BN);
+        uint32_t stage = 0, phase = 0;
+        int it = 0;
+        for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
+          const int as = it & 1;
+          // accumulator availability
+          if constexpr (Cfg::OVERLAP) {
+            // Needs the previous tile's epilogue to have drained the 32 shared columns
+            // (which also means the tile before that is fully drained).
+            if (it > 0) {
+              const int ps = (it - 1) & 1;
+              mbar_wait<CG == 2>(acc_empty_bar(ps), uint32_t((it - 1) >> 1) & 1u, ctx,
+                                 WB_DEV_TIMEOUT_MMA_ACC);
+            }
+          } else {
+            if (it >= 2)
+              mbar_wait<CG == 2>(acc_empty_bar(as), uint32_t((it - 2) >> 1) & 1u, ctx,
+                                 WB_DEV_TIMEOUT_MMA_ACC);
+          }
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + (as ? Cfg::ACC_COL1 : Cfg::ACC_COL0);
+          for (int kb = 0; kb < num_kb; ++kb) {
+            mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
+            if constexpr (CG == 2)
+              mbar_wait<true>(peer_full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_PEER);
+            tc_fence_after_sync();
+            const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+            const uint32_t sB = sA + Cfg::A_BYTES;
+            const uint32_t sSFA = sB + Cfg::B_BYTES;
+            const uint32_t sSFB = sSFA + Cfg::SFA_BYTES;
+            // scale factors: smem atoms -> tensor memory (4 columns per atom)
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+              utccp_sf_atom<CG>(tmem_base + Cfg::SFA_COL + a * 4, make_desc_sf_atom(sSFA + a * 512));
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+#pragma unroll
+              for (int a = 0; a < 2; ++a)
+                utccp_sf_atom<CG>(tmem_base + Cfg::SFB_COL + a * (BN / 32) + j * 4,
+                                  make_desc_sf_atom(sSFB + j * 1024 + a * 512));
+            const uint64_t a_desc = make_desc_k_sw128(sA);
+            const uint64_t b_desc = make_desc_k_sw128(sB);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              // K = 64 per instruction = 32 bytes inside the 128-byte swizzle row
+              const uint32_t sf_id = (k & 1) * 2;
+              mma_mxf4<CG>(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2),
+                           idesc_with_sf_id(idesc, sf_id),
+                           tmem_base + Cfg::SFA_COL + (k >> 1) * 4,
+                           tmem_base + Cfg::SFB_COL + (k >> 1) * (BN / 32),
+                           (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            // free the stage in both CTAs once these MMAs have read it
+            tc_commit<CG>(empty_bar(stage));
+            if constexpr (CG == 2) tc_commit<CG>(mapa_shared(empty_bar(stage), 1));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          tc_commit<CG>(acc_full_bar(as));
+          if constexpr (CG == 2) tc_commit<CG>(mapa_shared(acc_full_bar(as), 1));
+        }
+      } else {
+        // Second CTA of a pair: tell the leader when this CTA's stage has landed.
+        uint32_t stage = 0, phase = 0;
+        for (int t = first_tile; t < num_tiles; t += tile_step) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
+            mbar_arrive_cluster(mapa_shared(peer_full_bar(stage), 0));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps 2..5
+    const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+    OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
+    const uint32_t acc_empty_leader0 = (CG == 2) ? mapa_shared(acc_empty_bar(0), 0) : 0u;
+    const uint32_t acc_empty_leader1 = (CG == 2) ? mapa_shared(acc_empty_bar(1), 0) : 0u;
+    int it = 0;
+    for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
+      int mt, nt;
+      raster_tile(t, p.tiles_m, p.tiles_n, p.group_n, mt, nt);
+      const int as = it & 1;
+      mbar_wait(acc_full_bar(as), uint32_t(it >> 1) & 1u, ctx, WB_DEV_TIMEOUT_EPILOGUE);
+      tc_fence_after_sync();
+      const int row = (mt * CG + int(rank)) * Cfg::BM + quad * 32 + lane;
+      const int col0 = nt * BN;
+      const uint32_t t_acc = tmem_base + (uint32_t(quad * 32) << 16) + (as ? Cfg::ACC_COL1 : Cfg::ACC_COL0);
+      auto release = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 2) mbar_arrive_cluster(as ? acc_empty_leader1 : acc_empty_leader0);
+          else mbar_arrive(acc_empty_bar(as));
+        }
+      };
+      constexpr int NCHUNK = BN / 32;
+#pragma unroll 1
+      for (int ci = 0; ci < NCHUNK; ++ci) {
+        // With overlapping accumulators the 32 columns shared with the other accumulator go first:
+        // the last chunk of accumulator 0, the first chunk of accumulator 1.
+        int chunk = ci;
+        if constexpr (Cfg::OVERLAP) {
+          if (as == 0) chunk = (ci == 0) ? (NCHUNK - 1) : (ci - 1);
+        }
+        uint32_t r[32];
+        tmem_ld_32x32(t_acc + chunk * 32, r);
+        tmem_ld_wait();
+        if constexpr (Cfg::OVERLAP) {
+          if (ci == 0) release();
+        }
+        const int col = col0 + chunk * 32;
+        if (row < p.M && col < p.N)
+          store_chunk32<OutT>(C + size_t(row) * p.ldc + col, r, min(32, p.N - col), p.vec_ok != 0);
+      }
+      if constexpr (!Cfg::OVERLAP) release();
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CG == 2) {  // the pair shares tensor memory traffic and barriers: leave together
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<CG>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace wb

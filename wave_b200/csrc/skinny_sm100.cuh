@@ -1,0 +1,283 @@
+// Skinny (M <= 128) MXFP4 GEMM for sm_100a: the weight-streaming, HBM-bound regime.
+//
+// Takes the role of the reference's split-K template
+// (wave_lang/kernel/wave/templates/tagged_mxfp4_gemm.py:611-816: grid z = num_splits, partial
+// accumulators added into C with atomics) with two differences that the 1-ulp bf16 bar needs:
+// partial sums stay in f32 and are added in a fixed order, so the result does not depend on
+// arrival order and C needs no zero-initialisation.
+//
+//   * operands are swapped, as the reference's wide-store variant does
+//     (tagged_mxfp4_gemm.py:538-583): the 128 accumulator rows (tensor-memory lanes) hold 128
+//     weight rows n, the accumulator columns hold the M activation rows padded to NP in
+//     {16, 32, 64, 128}; a warp then writes 32 consecutive n of one output row at a time;
+//   * stream-K: the (N tile x K block) units are split evenly over one CTA per SM, each CTA
+//     streams a contiguous run of units through a deep TMA pipeline so that b is read exactly
+//     once at full bandwidth;
+//   * a CTA whose run covers a whole tile writes C directly; otherwise it writes an f32 partial
+//     to the workspace and bumps the tile's counter; the CTA that arrives last adds the partials
+//     in CTA order, converts once and writes C. Nobody spins on another CTA.
+#pragma once
+#include "ptx.cuh"
+#include <cuda_bf16.h>
+
+namespace wb {
+
+template <int NP_, int STAGES_>
+struct SkinnyCfg {
+  static constexpr int NP = NP_;  // padded M = MMA N
+  static constexpr int STAGES = STAGES_;
+  static constexpr int BK = 256;
+  static constexpr int W_BYTES = 128 * 128;
+  static constexpr int X_BYTES = NP * 128;
+  static constexpr int SF_BYTES = 1024;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int ACC_COL1 = NP;
+  static constexpr int SFW_COL = 480;
+  static constexpr int SFX_COL = 488;
+  static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+};
+
+struct SkinnyParams {
+  const uint8_t* sfw;  // weight (b) scales, atom layout
+  const uint8_t* sfx;  // activation (a) scales, atom layout (one 128-row block)
+  void* c;
+  float* partials;         // [2 * gridDim.x][M][128] f32
+  unsigned int* counters;  // [tiles_n], zero before the first launch; the kernel re-zeroes them
+  int M, N, K;
+  int ldc;
+  int ka_atoms;
+  int sfw_row_blocks;
+  int tiles_n;   // ceil(N / 128)
+  int num_kb;    // ceil(K / 256)
+  int* status;
+};
+
+// Units [u0, u1) of CTA c when `total` units are dealt as evenly as possible to `g` CTAs.
+__host__ __device__ __forceinline__ void skinny_range(long long total, int g, int c, int& u0, int& u1) {
+  u0 = int((total * c) / g);
+  u1 = int((total * (c + 1)) / g);
+}
+// CTA that owns unit u under skinny_range.
+__device__ __forceinline__ int skinny_owner(long long total, int g, int u) {
+  int c = int(((long long)(u + 1) * g - 1) / total);
+  // guard against rounding at the boundaries
+  int a, b;
+  skinny_range(total, g, c, a, b);
+  while (u < a) { --c; skinny_range(total, g, c, a, b); }
+  while (u >= b) { ++c; skinny_range(total, g, c, a, b); }
+  return c;
+}
+
+template <int NP, int STAGES, typename OutT>
+__global__ void __launch_bounds__(192, 1)
+mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                    const SkinnyParams p) {
+  using Cfg = SkinnyCfg<NP, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::NUM_BARRIERS * 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* last_flag = tmem_slot + 2;
+  WaitCtx ctx{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(acc_full_bar(s), 1);
+      mbar_init(acc_empty_bar(s), 4);
+    }
+    *abort_flag = 0u;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmW);
+    prefetch_tensormap(&tmX);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const long long total_units = (long long)p.tiles_n * p.num_kb;
+  int u0, u1;
+  skinny_range(total_units, gridDim.x, blockIdx.x, u0, u1);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t stream_policy = l2_policy_evict_first();  // weights are read once
+      const uint64_t keep_policy = l2_policy_evict_last();     // activations are re-read by every CTA
+      uint32_t stage = 0, phase = 0;
+      for (int u = u0; u < u1; ++u) {
+        const int tile = u / p.num_kb;
+        const int kb = u - tile * p.num_kb;
+        mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
+        const uint32_t sW = smem_base + stage * Cfg::STAGE_BYTES;
+        const uint32_t sX = sW + Cfg::W_BYTES;
+        const uint32_t sSFW = sX + Cfg::X_BYTES;
+        const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
+        const uint32_t fb = full_bar(stage);
+        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+        tma_load_2d_hint(sW, &tmW, kb * 128, tile * 128, fb, stream_policy);
+        tma_load_2d_hint(sX, &tmX, kb * 128, 0, fb, keep_policy);
+        const int rb = min(tile, p.sfw_row_blocks - 1);
+        bulk_load(sSFW, p.sfw + (size_t(rb) * p.ka_atoms + 2 * kb) * 512, 1024, fb);
+        bulk_load(sSFX, p.sfx + size_t(2 * kb) * 512, 1024, fb);
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_mxf4(128, NP);
+      uint32_t stage = 0, phase = 0;
+      int seg = 0;
+      for (int u = u0; u < u1; ++seg) {
+        const int tile = u / p.num_kb;
+        const int kbs = u - tile * p.num_kb;
+        const int kbe = min(p.num_kb, kbs + (u1 - u));
+        const int as = seg & 1;
+        if (seg >= 2)
+          mbar_wait(acc_empty_bar(as), uint32_t((seg - 2) >> 1) & 1u, ctx, WB_DEV_TIMEOUT_MMA_ACC);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (as ? Cfg::ACC_COL1 : 0);
+        for (int kb = kbs; kb < kbe; ++kb) {
+          mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
+          tc_fence_after_sync();
+          const uint32_t sW = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sX = sW + Cfg::W_BYTES;
+          const uint32_t sSFW = sX + Cfg::X_BYTES;
+          const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            utccp_sf_atom<1>(tmem_base + Cfg::SFW_COL + a * 4, make_desc_sf_atom(sSFW + a * 512));
+            utccp_sf_atom<1>(tmem_base + Cfg::SFX_COL + a * 4, make_desc_sf_atom(sSFX + a * 512));
+          }
+          const uint64_t w_desc = make_desc_k_sw128(sW);
+          const uint64_t x_desc = make_desc_k_sw128(sX);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            mma_mxf4<1>(d_tmem, w_desc + uint64_t(k * 2), x_desc + uint64_t(k * 2),
+                        idesc_with_sf_id(idesc, (k & 1) * 2),
+                        tmem_base + Cfg::SFW_COL + (k >> 1) * 4,
+                        tmem_base + Cfg::SFX_COL + (k >> 1) * 4, (kb > kbs || k > 0) ? 1u : 0u);
+          }
+          tc_commit<1>(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        tc_commit<1>(acc_full_bar(as));
+        u += kbe - kbs;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps 2..5
+    const int quad = warp & 3;
+    const int nl = quad * 32 + lane;  // weight row inside the tile
+    OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
+    const int first_tile = u0 / p.num_kb;
+    int seg = 0;
+    for (int u = u0; u < u1; ++seg) {
+      const int tile = u / p.num_kb;
+      const int kbs = u - tile * p.num_kb;
+      const int kbe = min(p.num_kb, kbs + (u1 - u));
+      const int as = seg & 1;
+      const int n = tile * 128 + nl;
+      const bool whole = (kbs == 0 && kbe == p.num_kb);
+      mbar_wait(acc_full_bar(as), uint32_t(seg >> 1) & 1u, ctx, WB_DEV_TIMEOUT_EPILOGUE);
+      tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + (uint32_t(quad * 32) << 16) + (as ? Cfg::ACC_COL1 : 0);
+      float* part = p.partials +
+                    (size_t(2 * blockIdx.x + (tile == first_tile ? 0 : 1)) * p.M) * 128 + nl;
+#pragma unroll 1
+      for (int c0 = 0; c0 < NP; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x16(t_acc + c0, r);
+        tmem_ld_wait();
+        if (c0 + 16 >= NP) {  // accumulator fully read: hand it back to the MMA warp
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty_bar(as));
+        }
+        if (whole) {
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = c0 + j;
+              if (m < p.M) {
+                if constexpr (sizeof(OutT) == 4) C[size_t(m) * p.ldc + n] = __uint_as_float(r[j]);
+                else C[size_t(m) * p.ldc + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c0 + j;
+            if (m < p.M) __stcg(part + size_t(m) * 128, __uint_as_float(r[j]));
+          }
+        }
+      }
+      if (!whole) {
+        // publish the partial, then find out whether this CTA completes the tile
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int t_lo = tile * p.num_kb;
+        const int c_lo = skinny_owner(total_units, gridDim.x, t_lo);
+        const int c_hi = skinny_owner(total_units, gridDim.x, t_lo + p.num_kb - 1);
+        if (threadIdx.x == 64) {
+          const unsigned int prev = atomicAdd(p.counters + tile, 1u);
+          *last_flag = (prev == (unsigned int)(c_hi - c_lo)) ? 1u : 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          if (n < p.N) {
+            for (int m = 0; m < p.M; ++m) {
+              float acc = 0.f;
+              for (int c = c_lo; c <= c_hi; ++c) {
+                int a0, a1;
+                skinny_range(total_units, gridDim.x, c, a0, a1);
+                const int slot = 2 * c + ((a0 / p.num_kb) == tile ? 0 : 1);
+                acc += __ldcg(p.partials + (size_t(slot) * p.M + m) * 128 + nl);
+              }
+              if constexpr (sizeof(OutT) == 4) C[size_t(m) * p.ldc + n] = acc;
+              else C[size_t(m) * p.ldc + n] = __float2bfloat16_rn(acc);
+            }
+          }
+          if (threadIdx.x == 64) p.counters[tile] = 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is reused by the next segment
+      }
+      u += kbe - kbs;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace wb
