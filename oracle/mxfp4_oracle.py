@@ -141,25 +141,30 @@ def quantize_mxfp4(x: torch.Tensor):
     """
     R, K = x.shape
     assert K % SCALE_GROUP_SIZE == 0
-    xb = x.reshape(R, K // 32, 32).to(torch.float32)
-    amax = xb.abs().amax(dim=2)
-    e = torch.floor(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)))) - 2.0
-    e = torch.where(amax > 0, e, torch.zeros_like(e))
-    sb = torch.clamp(e + 127.0, 0, 254)
-    scale = torch.pow(torch.tensor(2.0), sb - 127.0).unsqueeze(2)
-    y = torch.clamp(xb / scale, -6.0, 6.0)
-    mag = y.abs()
-    grid = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
-    # nearest grid value, ties to the even index
-    d = (mag.unsqueeze(-1) - grid).abs()
-    idx = d.argmin(dim=-1)
-    # argmin takes the lower index on ties; move to the upper one when the lower is odd
-    upper = torch.clamp(idx + 1, max=7)
-    tie = (d.gather(-1, upper.unsqueeze(-1)).squeeze(-1) == d.gather(-1, idx.unsqueeze(-1)).squeeze(-1)) & (upper != idx)
-    idx = torch.where(tie & (idx % 2 == 1), upper, idx)
-    code = (idx + torch.where(torch.signbit(y), 8, 0)).to(torch.uint8).reshape(R, K)
-    packed = code[:, 0::2] | (code[:, 1::2] << 4)
-    return packed.contiguous(), sb.to(torch.uint8).contiguous()
+    packed = torch.empty(R, K // 2, dtype=torch.uint8)
+    scales = torch.empty(R, K // 32, dtype=torch.uint8)
+    two = torch.tensor(2.0)
+    # Midpoints between neighbouring E2M1 magnitudes. A value on a midpoint goes to the neighbour
+    # with the even code: above an even code it stays (strict >), above an odd code it moves up (>=).
+    strict = (0.25, 1.25, 2.5, 5.0)
+    inclusive = (0.75, 1.75, 3.5)
+    for r0 in range(0, R, 1024):
+        xb = x[r0:r0 + 1024].reshape(-1, K // 32, 32).to(torch.float32)
+        amax = xb.abs().amax(dim=2)
+        e = torch.floor(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)))) - 2.0
+        e = torch.where(amax > 0, e, torch.zeros_like(e))
+        sb = torch.clamp(e + 127.0, 0, 254)
+        y = torch.clamp(xb / torch.pow(two, sb - 127.0).unsqueeze(2), -6.0, 6.0)
+        mag = y.abs()
+        idx = torch.zeros_like(mag, dtype=torch.uint8)
+        for t in strict:
+            idx += (mag > t).to(torch.uint8)
+        for t in inclusive:
+            idx += (mag >= t).to(torch.uint8)
+        code = (idx | (torch.signbit(y).to(torch.uint8) << 3)).reshape(-1, K)
+        packed[r0:r0 + 1024] = code[:, 0::2] | (code[:, 1::2] << 4)
+        scales[r0:r0 + 1024] = sb.to(torch.uint8)
+    return packed, scales
 
 
 # ---------------------------------------------------------------------------------------------

@@ -1,0 +1,356 @@
+"""GPU parity: the CUDA kernels, called through the C ABI and through the template API, against the
+CPU oracle and the golden vectors made from the reference. Mirrors the reference's own MXFP4 tests
+(tests/kernel/wave_gemm_mxfp_test.py, tests/kernel/wave_gemm_test.py:3640-3690).
+
+Tolerances (stated by the task this library serves):
+  * dequantised operands and repacked scales: bit-exact;
+  * f32 output: |c - ref| <= 1e-5 * |ref| + 1e-5 * sqrt(K) * max|row of dequant(a)| * max|row of dequant(b)|;
+  * bf16 output: within 1 bf16 ulp of the f32 reference rounded to bf16.
+"""
+
+import ctypes
+import functools
+
+import numpy as np
+import pytest
+import torch
+
+import wave_b200 as wb
+from conftest import GOLDEN
+from oracle import mxfp4_oracle as orc
+from wave_b200 import _lib, ops
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def check_f32(c, a, a_s, b, b_s, ref=None):
+    K = a.shape[1] * 2
+    if ref is None:
+        ref = orc.scaled_gemm(a, a_s, b, b_s)
+    tol = orc.f32_tolerance(orc.dequant_mxfp4(a, a_s), orc.dequant_mxfp4(b, b_s), ref, K)
+    err = (c.float().cpu() - ref).abs()
+    bad = ~(err <= tol)
+    assert not bool(bad.any()), f"{int(bad.sum())} of {bad.numel()} outside tolerance, max err {float(err.max())}"
+
+
+def check_bf16(c, ref):
+    d = orc.bf16_ulp_distance(c, ref)
+    assert int(d.max()) <= 1, f"{int((d > 1).sum())} of {d.numel()} differ by more than 1 bf16 ulp (max {int(d.max())})"
+
+
+def check(c, a, a_s, b, b_s, ref=None):
+    if ref is None:
+        ref = orc.scaled_gemm(a, a_s, b, b_s)
+    if c.dtype == torch.float32:
+        check_f32(c, a, a_s, b, b_s, ref)
+    else:
+        check_bf16(c, ref)
+    ops.check_device_status()
+
+
+def random_problem(M, N, K, seed, lo=124, hi=131):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, generator=g)
+    b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+    a_s = torch.randint(lo, hi, (M, K // 32), dtype=torch.uint8, generator=g)
+    b_s = torch.randint(lo, hi, (N, K // 32), dtype=torch.uint8, generator=g)
+    return a, a_s, b, b_s
+
+
+def quantized_problem(M, N, K, seed_a, seed_b, std_b=1.0):
+    a, a_s = orc.quantize_mxfp4(torch.randn(M, K, generator=torch.Generator().manual_seed(seed_a)))
+    b, b_s = orc.quantize_mxfp4(torch.randn(N, K, generator=torch.Generator().manual_seed(seed_b)) * std_b)
+    return a, a_s, b, b_s
+
+
+def run(a, a_s, b, b_s, out_dtype=torch.float32, path=_lib.PATH_AUTO, fill=float("nan")):
+    kernel, options = wb.get_tagged_mxfp4_gemm((a.shape[0], b.shape[0], a.shape[1] * 2),
+                                               output_dtype=wb.TORCH_DTYPE_TO_WAVE[out_dtype])
+    options.kernel_path = path
+    gemm = wb.wave_compile(wb.set_default_run_config(options), kernel)
+    c = torch.full((a.shape[0], b.shape[0]), fill, dtype=out_dtype, device=DEV)  # kernel must overwrite all of c
+    gemm(a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV), c)
+    return c
+
+
+# ---------------------------------------------------------------------------------------------
+# scale repack and dequantisation: bit-exact
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,K", [(128, 256), (1024, 1024), (100, 96), (300, 8192), (16, 8192), (257, 1184),
+                                    (1, 32), (4096, 16384)])
+def test_repack_scales_bit_exact(rows, K):
+    s = torch.randint(0, 256, (rows, K // 32), dtype=torch.uint8)
+    got = ops.repack_scales(s.to(DEV))
+    assert torch.equal(got.data.cpu(), orc.pack_scales(s))
+    assert got.data.numel() == ops.packed_scale_bytes(rows, K)
+
+
+def test_repack_scales_strided_source():
+    s = torch.randint(0, 256, (70, 40), dtype=torch.uint8)
+    view = s.to(DEV)[:, 3:19]  # row stride 40, 16 K-blocks, misaligned start
+    got = ops.repack_scales(view)
+    assert torch.equal(got.data.cpu(), orc.pack_scales(s[:, 3:19].contiguous()))
+
+
+@pytest.mark.parametrize("rows,K", [(64, 256), (33, 96), (1000, 4096)])
+def test_dequant_bit_exact_all_codes(rows, K):
+    q = torch.randint(0, 256, (rows, K // 2), dtype=torch.uint8)
+    s = torch.randint(0, 256, (rows, K // 32), dtype=torch.uint8)  # includes 0, 254 and the NaN code 255
+    got = wb.mxfp4_dequant(q.to(DEV), s.to(DEV)).cpu()
+    exp = orc.dequant_mxfp4(q, s)
+    same = (got.view(torch.int32) == exp.view(torch.int32)) | (got.isnan() & exp.isnan())
+    assert bool(same.all()), f"{int((~same).sum())} mismatches"
+
+
+def test_dequant_golden_edges():
+    g = np.load(GOLDEN / "gemm_wide_scales_48x80x256.npz")
+    a = torch.from_numpy(g["a"])
+    for scale_key, deq_key in (("a_scale", "a_deq"), ("edge_scale", "edge_deq")):
+        got = wb.mxfp4_dequant(a.to(DEV), torch.from_numpy(g[scale_key]).to(DEV)).cpu().numpy()
+        exp = g[deq_key]
+        assert bool(((got.view(np.int32) == exp.view(np.int32)) | (np.isnan(got) & np.isnan(exp))).all())
+
+
+# ---------------------------------------------------------------------------------------------
+# golden GEMM vectors from the reference
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_golden_seed5_small(out_dtype):
+    g = np.load(GOLDEN / "gemm_seed5_64x96x128.npz")
+    x, w, xs, ws = (torch.from_numpy(g[k]) for k in ("x", "w", "x_scales", "w_scales"))
+    c = run(x, xs, w.T.contiguous(), ws, out_dtype)
+    check(c, x, xs, w.T.contiguous(), ws, ref=torch.from_numpy(g["out"]))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_golden_wide_scales(out_dtype):
+    g = np.load(GOLDEN / "gemm_wide_scales_48x80x256.npz")
+    a, b, a_s, b_s = (torch.from_numpy(g[k]) for k in ("a", "b", "a_scale", "b_scale"))
+    c = run(a, a_s, b, b_s, out_dtype)
+    check(c, a, a_s, b, b_s, ref=torch.from_numpy(g["out"]))
+
+
+def test_reference_test_shape_1024_seed5_f32():
+    """testScaledGemmMXFP4 (wave_gemm_mxfp_test.py:94-201) at (1024, 1024, 1024), written as the reference writes it."""
+    shape = (1024, 1024, 1024)
+    kernel, hyper = wb.get_scaled_gemm_kernel(shape, wb.ScaledMMAType.F32_16x16x128_F8F6F4)
+    options = wb.WaveCompileOptions(subs=hyper, canonicalize=True, schedule=wb.SchedulingType.NONE)
+    gemm = wb.wave_compile(wb.set_default_run_config(options), kernel)
+    x, w, x_scales, w_scales = wb.generate_gemm_afp4wfp4_inputs(shape, device=torch.device("cpu"))
+    ox, ow, oxs, ows = orc.generate_gemm_afp4wfp4_inputs(shape)
+    assert torch.equal(x, ox) and torch.equal(w, ow) and torch.equal(x_scales, oxs) and torch.equal(w_scales, ows)
+    out = torch.zeros(x.shape[0], w.shape[1], dtype=torch.float32, device=DEV)
+    w_t = w.T.contiguous()
+    gemm(x.to(DEV), x_scales.to(DEV), w_t.to(DEV), w_scales.to(DEV), out)
+    torch_out = orc.torch_scaled_gemm_mxfp4(x, w, x_scales, w_scales)
+    torch.testing.assert_close(torch_out, out.cpu(), check_dtype=False)  # the reference's own (default) tolerance
+    check(out, x, x_scales, w_t, w_scales, ref=torch_out)
+    g = np.load(GOLDEN / "gemm_seed5_1024_sample.npz")
+    torch.testing.assert_close(out.cpu()[::64, ::64], torch.from_numpy(g["out_sample"]), rtol=1e-5, atol=1e-3)
+
+
+def test_config1_1024_cubed_wide_scales_f32():
+    """Scales uniform in [124, 130], codes uniform over all 16 values, f32 output."""
+    x, w, xs, ws = orc.generate_gemm_afp4wfp4_inputs((1024, 1024, 1024), scale_lo=124, scale_hi=131)
+    w_t = w.T.contiguous()
+    check(run(x, xs, w_t, ws, torch.float32), x, xs, w_t, ws)
+
+
+# ---------------------------------------------------------------------------------------------
+# every kernel path, ragged and aligned shapes, both output types
+# ---------------------------------------------------------------------------------------------
+TILE_PATHS = [_lib.PATH_TILE_1CTA, _lib.PATH_TILE_1CTA | _lib.TILE_N128, _lib.PATH_TILE_2CTA,
+              _lib.PATH_TILE_2CTA | _lib.TILE_N128]
+
+
+@pytest.mark.parametrize("flags", TILE_PATHS)
+@pytest.mark.parametrize("shape", [(128, 128, 256), (256, 512, 1024), (1000, 1100, 992), (130, 260, 32),
+                                   (1024, 1600, 2048), (512, 1920, 1024), (3, 5, 64)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_tile_paths(flags, shape, out_dtype):
+    M, N, K = shape
+    a, a_s, b, b_s = random_problem(M, N, K, seed=M + N + K)
+    ad, asd, bd, bsd = a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV)
+    c = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_packed(ad, ops.repack_scales(asd), bd, ops.repack_scales(bsd), c, flags)
+    check(c, a, a_s, b, b_s)
+
+
+@pytest.mark.parametrize("M", [1, 4, 16, 17, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (1000, 992), (4096, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_skinny_path(M, N, K, out_dtype):
+    a, a_s, b, b_s = random_problem(M, N, K, seed=7 * M + N)
+    c = run(a, a_s, b, b_s, out_dtype, path=_lib.PATH_SKINNY)
+    check(c, a, a_s, b, b_s)
+    # the same launch again gives the same bits (fixed-order reduction; counters left clean)
+    c2 = run(a, a_s, b, b_s, out_dtype, path=_lib.PATH_SKINNY)
+    assert torch.equal(c.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32),
+                       c2.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32))
+
+
+def test_many_tiles_per_cta_and_accumulator_reuse():
+    """More tiles than SMs on every path, so each CTA runs several tiles through both accumulators."""
+    M, N, K = 2048, 6144, 512
+    a, a_s, b, b_s = random_problem(M, N, K, seed=99)
+    ref = orc.scaled_gemm(a, a_s, b, b_s)
+    for flags in TILE_PATHS:
+        c = run(a, a_s, b, b_s, torch.bfloat16, path=flags & 0xF)
+        check(c, a, a_s, b, b_s, ref=ref)
+
+
+def test_output_column_block_with_row_pitch():
+    """c may be a column block of a wider matrix (what the N-sharded launcher writes into)."""
+    M, N, K = 256, 384, 512
+    a, a_s, b, b_s = random_problem(M, N, K, seed=5)
+    wide = torch.full((M, 1024), -7.0, dtype=torch.bfloat16, device=DEV)
+    ad, bd = a.to(DEV), b.to(DEV)
+    ops.scaled_gemm_packed(ad, ops.repack_scales(a_s.to(DEV)), bd, ops.repack_scales(b_s.to(DEV)), wide[:, 256:640])
+    check_bf16(wide[:, 256:640].contiguous(), orc.scaled_gemm(a, a_s, b, b_s))
+    assert bool((wide[:, :256] == -7.0).all()) and bool((wide[:, 640:] == -7.0).all())
+
+
+def test_unaligned_output_falls_back_to_scalar_stores():
+    M, N, K = 130, 70, 256
+    a, a_s, b, b_s = random_problem(M, N, K, seed=11)
+    wide = torch.zeros(M, 75, dtype=torch.float32, device=DEV)  # row pitch 300 bytes: not a multiple of 16
+    ops.scaled_gemm_packed(a.to(DEV), ops.repack_scales(a_s.to(DEV)), b.to(DEV), ops.repack_scales(b_s.to(DEV)),
+                           wide[:, 3:73], _lib.PATH_TILE_1CTA)
+    check_f32(wide[:, 3:73].contiguous(), a, a_s, b, b_s)
+
+
+# ---------------------------------------------------------------------------------------------
+# reference API variants
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,num_splits", [((256, 256, 256), 2), ((256, 256, 512), 4), ((256, 256, 1024), 4),
+                                              ((512, 512, 1024), 4)])
+@pytest.mark.parametrize("output_type", [torch.float32, torch.bfloat16])
+def test_splitk_adds_into_c(shape, num_splits, output_type):
+    """testSplitKMxfp4Gemm (wave_gemm_test.py:3640-3690): zero-initialised c, result added in."""
+    kernel, options = wb.get_tagged_splitk_mxfp4_gemm(shape, num_splits=num_splits, block_shape=(128, 128, 128),
+                                                      output_type=wb.TORCH_DTYPE_TO_WAVE[output_type])
+    gemm = wb.wave_compile(wb.set_default_run_config(options), kernel, wb.get_mxfp4_dbuf_schedule(True, 1))
+    x, w, xs, ws = orc.generate_gemm_afp4wfp4_inputs(shape)
+    ref = orc.torch_scaled_gemm_mxfp4(x, w, xs, ws)
+    w_t = w.T.contiguous()
+    c = torch.zeros(shape[0], shape[1], dtype=output_type, device=DEV)
+    gemm(x.to(DEV), xs.to(DEV), w_t.to(DEV), ws.to(DEV), c)
+    check(c, x, xs, w_t, ws, ref=ref)  # far inside the reference's rtol 1e-3 / atol 1e-2 (f32) and atol 4.0 (bf16)
+    if output_type == torch.float32:
+        gemm(x.to(DEV), xs.to(DEV), w_t.to(DEV), ws.to(DEV), c)  # second call accumulates: c == 2 * ref
+        torch.testing.assert_close(c.cpu(), 2 * ref, rtol=1e-5, atol=1e-2)
+
+
+def test_splitk_skinny_accumulates():
+    M, N, K = 16, 512, 2048
+    a, a_s, b, b_s = random_problem(M, N, K, seed=21)
+    kernel, options = wb.get_tagged_splitk_mxfp4_gemm((M, N, K), num_splits=2)
+    gemm = wb.wave_compile(options, kernel)
+    c = torch.ones(M, N, dtype=torch.float32, device=DEV)
+    gemm(a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV), c)
+    ref = orc.scaled_gemm(a, a_s, b, b_s) + 1.0
+    check_f32(c, a, a_s, b, b_s, ref=ref)
+
+
+def test_batched_activations_shared_weights():
+    """testScaledBatchedGemmMXFP4 (wave_gemm_mxfp_test.py:205-339): a is [B, M, K/2], b is shared."""
+    B, M, N, K = 4, 96, 256, 512
+    a, a_s, b, b_s = random_problem(B * M, N, K, seed=31)
+    kernel, options = wb.get_tagged_mxfp4_gemm((B * M, N, K))
+    options.dynamic_symbols = ["M", "N", "K"]
+    gemm = wb.wave_compile(options, kernel)
+    c = torch.empty(B, M, N, dtype=torch.float32, device=DEV)
+    gemm(a.view(B, M, -1).to(DEV), a_s.view(B, M, -1).to(DEV), b.to(DEV), b_s.to(DEV), c)
+    check_f32(c.view(B * M, N), a, a_s, b, b_s)
+
+
+def test_preshuffled_scale_templates():
+    shape = (256, 384, 1024)
+    a, a_s, b, b_s = random_problem(*shape, seed=41)
+    ref = orc.scaled_gemm(a, a_s, b, b_s)
+    for make in (wb.get_tagged_mxfp4_gemm_preshuffle_scales, wb.get_tagged_mxfp4_gemm_preshuffle_scales_and_B,
+                 wb.get_tagged_mxfp4_gemm_preshuffle_b, wb.get_tagged_mxfp4_gemm_preshuffle_b_wide_store):
+        kernel, options = make(shape, output_dtype=wb.bf16)
+        gemm = wb.wave_compile(options, kernel)
+        c = torch.empty(shape[0], shape[1], dtype=torch.bfloat16, device=DEV)
+        gemm(a.to(DEV), wb.e8m0_shuffle(a_s.to(DEV)), wb.b_preshuffle(b.to(DEV)), wb.e8m0_shuffle(b_s.to(DEV)), c)
+        check_bf16(c, ref)
+        with pytest.raises(ValueError, match="pre-shuffled"):
+            gemm(a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV), c)
+
+
+def test_call_time_errors():
+    kernel, options = wb.get_tagged_mxfp4_gemm((64, 64, 64))
+    gemm = wb.wave_compile(options, kernel)
+    a = torch.zeros(64, 32, dtype=torch.uint8, device=DEV)
+    s = torch.zeros(64, 2, dtype=torch.uint8, device=DEV)
+    with pytest.raises(ValueError, match="writes f32"):
+        gemm(a, s, a, s, torch.zeros(64, 64, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(ValueError, match="was built for"):
+        gemm(a[:32], s[:32], a, s, torch.zeros(32, 64, device=DEV))
+    with pytest.raises(ValueError, match="a_scale must be"):
+        gemm(a, s[:, :1], a, s, torch.zeros(64, 64, device=DEV))
+    with pytest.raises(ValueError, match="uint8 or int8"):
+        gemm(a.float(), s, a, s, torch.zeros(64, 64, device=DEV))
+    with pytest.raises(ValueError, match="workspace"):
+        _lib.check(_lib.load().wb200_mxfp4_gemm(16, 64, 64, a.data_ptr(), a.data_ptr(), a.data_ptr(), a.data_ptr(),
+                                                a.data_ptr(), 0, 64, None, 0, _lib.PATH_SKINNY, None))
+    assert ctypes.c_int(_lib.load().wb200_version()).value >= 1000
+
+
+def test_noncontiguous_inputs_are_copied():
+    M, N, K = 64, 128, 256
+    a, a_s, b, b_s = random_problem(M, N, K, seed=51)
+    a_wide = torch.zeros(M, K, dtype=torch.uint8, device=DEV)
+    a_wide[:, ::2] = a.to(DEV)
+    c = torch.empty(M, N, device=DEV)
+    kernel, options = wb.get_tagged_mxfp4_gemm((M, N, K))
+    wb.wave_compile(options, kernel)(a_wide[:, ::2], a_s.to(DEV), b.to(DEV), b_s.to(DEV), c)
+    check_f32(c, a, a_s, b, b_s)
+
+
+# ---------------------------------------------------------------------------------------------
+# full-size configurations: sampled oracle rows plus size-independent properties
+# ---------------------------------------------------------------------------------------------
+def test_config2_8192_cubed_bf16_sampled_rows_and_scaling_property():
+    """M = N = K = 8192, operands quantised from N(0, 1), bf16 output. The oracle is evaluated for 64
+    sampled rows of A against all of B; the whole output is checked through an exact property:
+    raising every A scale by one doubles C bit for bit (power-of-two scaling is exact)."""
+    M = N = K = 8192
+    a, a_s, b, b_s = quantized_problem(M, N, K, 1002, 2002)
+    ad, asd, bd, bsd = a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV)
+    kernel, options = wb.get_tagged_mxfp4_gemm((M, N, K), output_dtype=wb.bf16)
+    gemm = wb.wave_compile(options, kernel)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    gemm(ad, asd, bd, bsd, c)
+    rows = torch.arange(0, M, 128) + torch.arange(64).remainder(128)
+    ref = orc.scaled_gemm(a[rows], a_s[rows], b, b_s)
+    check_bf16(c[rows.to(DEV)], ref)
+    c2 = torch.empty_like(c)
+    gemm(ad, asd + 1, bd, bsd, c2)
+    assert torch.equal((c.float() * 2).to(torch.bfloat16), c2)
+    ops.check_device_status()
+
+
+@functools.lru_cache(maxsize=1)
+def _config3_operands():
+    N, K = 28672, 8192
+    a, a_s = orc.quantize_mxfp4(torch.randn(128, K, generator=torch.Generator().manual_seed(1003)))
+    b, b_s = orc.quantize_mxfp4(torch.randn(N, K, generator=torch.Generator().manual_seed(2003)) * 0.02)
+    return a, a_s, b, b_s
+
+
+@pytest.mark.parametrize("M", [1, 4, 16, 64, 128])
+def test_config3_decode_shapes_bf16(M):
+    """N = 28672, K = 8192, weights from N(0, 0.02), activations from N(0, 1); column blocks of the
+    oracle are checked (the full dequantised weight matrix would be 0.9 GB)."""
+    N = 28672
+    a, a_s, b, b_s = _config3_operands()
+    a, a_s = a[:M].contiguous(), a_s[:M].contiguous()
+    c = run(a, a_s, b, b_s, torch.bfloat16)
+    for n0 in (0, 12288, N - 2048):
+        ref = orc.scaled_gemm(a, a_s, b[n0:n0 + 2048], b_s[n0:n0 + 2048])
+        check_bf16(c[:, n0:n0 + 2048].contiguous(), ref)
+    ops.check_device_status()

@@ -1,0 +1,183 @@
+"""`wave_compile` and the callable it returns, for the MXFP4 scaled-GEMM templates.
+
+The reference compiles a traced kernel with its JIT and returns a `WaveKernel` whose call launches
+the generated binary (wave_lang/kernel/wave/compile.py:1021-1280 `wave_compile`, :140-339
+`WaveKernel`). Here nothing is generated at run time: the templates are descriptors, the kernels
+are precompiled in libwave_b200.so, and "compiling" checks the options and picks the kernel path.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+from . import _lib, ops
+from .lang import DataType, f32
+
+
+class SchedulingType:
+    """Names of the reference's scheduling modes (wave_lang/kernel/wave/scheduling/schedule_enums.py).
+    Accepted and ignored: the B200 kernels have one fixed TMA / tcgen05 pipeline."""
+    NONE = "none"
+    PREFETCH = "prefetch"
+    MODULO = "modulo"
+    FOUR_STAGE = "four_stage"
+    MANUAL = "manual"
+
+
+@dataclass
+class WaveCompileOptions:
+    """The subset of the reference's option set (wave_lang/kernel/wave/compile_options.py:18-160)
+    that callers of the MXFP4 templates set. Fields that steer AMD code generation are accepted so
+    that existing call sites run, and have no effect."""
+
+    # symbol mappings
+    subs: dict = field(default_factory=dict)
+    dynamic_symbols: list = field(default_factory=list)
+    # general / scheduling (no effect)
+    postprocess: Optional[str] = None
+    canonicalize: bool = True
+    func_name: str = "isolated_benchmark"
+    schedule: Any = SchedulingType.NONE
+    use_scheduling_barriers: bool = False
+    multi_buffer_count: Optional[int] = None
+    # backend
+    backend: str = "cuda"
+    device: str = "cuda"
+    target: str = "sm_100a"
+    num_devices: int = 1
+    use_water_backend: bool = False
+    # benchmark options
+    run_bench: bool = False
+    benchmark_batch_size: Optional[int] = None
+    benchmark_repetitions: Optional[int] = None
+    benchmark_results_file: Optional[str] = None
+    profile_python_wrapper: bool = False
+    # performance options (no effect unless noted)
+    wave_runtime: bool = True
+    use_buffer_ops: bool = False
+    use_global_to_shared: bool = False
+    linearize_shared_access: bool = False
+    minimize_shared_allocs: bool = True
+    reorder_allocs: bool = True
+    use_bound_check: bool = False
+    specialize: bool = False
+    eliminate_epilogue: bool = False
+    print_mlir: bool = False
+    print_mlir_file: Optional[str] = None
+    kernel_hash: Optional[str] = None
+    # wave_b200 only: force a kernel path (a PATH_* flag of the C ABI), 0 = choose by shape
+    kernel_path: int = _lib.PATH_AUTO
+
+
+def get_default_arch() -> str:
+    """The reference returns the AMD gcnArchName (wave_lang/kernel/wave/utils/run_utils.py:137-156);
+    this library has exactly one target."""
+    return "sm_100a"
+
+
+def set_default_run_config(options: WaveCompileOptions) -> WaveCompileOptions:
+    """wave_lang/kernel/wave/utils/run_utils.py:183-198: fill in device and target."""
+    options.device = "cuda"
+    options.target = get_default_arch()
+    return options
+
+
+def validate_options(options: WaveCompileOptions) -> None:
+    """Reject option combinations this library cannot honour (the reference's validate_options,
+    wave_lang/kernel/wave/compile.py:1489-1500, raises ValueError in the same way)."""
+    if options.num_devices != 1:
+        raise ValueError("num_devices > 1 is served by wave_b200.multi_gpu.ShardedScaledGemm, not by wave_compile")
+    if options.kernel_path not in (_lib.PATH_AUTO, _lib.PATH_TILE_1CTA, _lib.PATH_TILE_2CTA, _lib.PATH_SKINNY):
+        raise ValueError(f"unknown kernel_path {options.kernel_path}")
+
+
+class ScaledGemmKernel:
+    """The callable `wave_compile` returns: `kernel(a, a_scale, b, b_scale, c)` writes c in place and
+    returns None (wave_lang/kernel/wave/compile.py:225-339).
+
+    a [M, K/2] (or [B, M, K/2]) and b [N, K/2] are packed E2M1 bytes, a_scale [.., K/32] and
+    b_scale [N, K/32] are E8M0 bytes, c is f32 or bf16 as the template says. M, N, K are read from
+    the tensors (the reference's dynamic dims, compile.py:256-265); static sizes given at template
+    creation are checked against them unless they were declared dynamic.
+    """
+
+    def __init__(self, template, options: WaveCompileOptions):
+        self.template = template
+        self.options = options
+        self.asm = ""  # the reference exposes generated code here; nothing is generated at run time
+        self._weight_scales = ops.WeightScaleCache()
+        self._a_scale_buf: dict[int, torch.Tensor] = {}
+        self._static = None
+        if template.shape is not None and not options.dynamic_symbols:
+            self._static = tuple(template.shape)
+
+    # the reference offers both spellings
+    def __call__(self, *args):
+        return self.invoke(*args)
+
+    def invoke(self, a, a_scale, b, b_scale, c) -> None:
+        t = self.template
+        if a.dim() == 3:  # batched activations, shared weights (tests/kernel/wave_gemm_mxfp_test.py:205-288)
+            if c.dim() != 3 or not c.is_contiguous():
+                raise ValueError("batched call needs a contiguous 3-D output")
+            a2 = a.reshape(-1, a.shape[-1])
+            as2 = a_scale if isinstance(a_scale, ops.PackedScales) else a_scale.reshape(-1, a_scale.shape[-1])
+            return self.invoke(a2, as2, b, b_scale, c.view(-1, c.shape[-1]))
+        for name, x in (("a", a), ("b", b)):
+            ops._as_u8(x, name)
+            if x.dim() != 2:
+                raise ValueError(f"{name} must be 2-D, got shape {tuple(x.shape)}")
+        if not c.is_cuda:
+            raise ValueError("c must be a CUDA tensor")
+        if c.dtype != t.output_dtype.torch_dtype:
+            raise ValueError(f"this kernel writes {t.output_dtype}; got an output tensor of {c.dtype}")
+        # Non-contiguous inputs are copied, as the reference does (run_utils.py:106-109).
+        if not a.is_contiguous():
+            a = a.contiguous()
+        if not b.is_contiguous():
+            b = b.contiguous()
+        M, N, K = a.shape[0], b.shape[0], a.shape[1] * 2
+        if self._static is not None and self._static != (M, N, K):
+            raise ValueError(f"kernel was built for (M, N, K) = {self._static}, called with {(M, N, K)}")
+        if t.preshuffled_scales and not (isinstance(a_scale, ops.PackedScales) and isinstance(b_scale, ops.PackedScales)):
+            raise ValueError(f"{t.name} takes pre-shuffled scales: pass mxfp_utils.e8m0_shuffle(scale) for a_scale and b_scale")
+        a_sf = self._pack_activation_scales(a_scale, M, K)
+        b_sf = b_scale if isinstance(b_scale, ops.PackedScales) else self._weight_scales.get(self._check_scale(b_scale, N, K, "b_scale"))
+        flags = self.options.kernel_path
+        if t.accumulate:
+            flags |= _lib.ACCUMULATE
+        ops.scaled_gemm_packed(a, a_sf, b, b_sf, c, flags)
+
+    @staticmethod
+    def _check_scale(s, rows, K, name):
+        ops._as_u8(s, name)
+        if tuple(s.shape) != (rows, K // ops.SCALE_GROUP_SIZE):
+            raise ValueError(f"{name} must be [{rows}, {K // ops.SCALE_GROUP_SIZE}], got {tuple(s.shape)}")
+        return s
+
+    def _pack_activation_scales(self, a_scale, M, K):
+        if isinstance(a_scale, ops.PackedScales):
+            return a_scale
+        self._check_scale(a_scale, M, K, "a_scale")
+        idx = a_scale.device.index or 0
+        need = ops.packed_scale_bytes(M, K)
+        buf = self._a_scale_buf.get(idx)
+        if buf is None or buf.numel() < need:
+            buf = torch.empty(need, dtype=torch.uint8, device=a_scale.device)
+            self._a_scale_buf[idx] = buf
+        return ops.repack_scales(a_scale, out=buf)
+
+
+def wave_compile(options: WaveCompileOptions, kernel, schedule=None) -> ScaledGemmKernel:
+    """wave_lang/kernel/wave/compile.py:1021: (options, kernel[, schedule]) -> callable.
+    `schedule` objects from wave_b200.schedules are accepted and have no effect."""
+    from .templates import ScaledGemmTemplate
+
+    if not isinstance(kernel, ScaledGemmTemplate):
+        raise TypeError("wave_compile here only compiles the MXFP4 scaled-GEMM templates of wave_b200.templates")
+    validate_options(options)
+    _lib.load()  # fail now, not at the first call, when the CUDA library is missing
+    return ScaledGemmKernel(kernel, options)

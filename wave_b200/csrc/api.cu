@@ -118,7 +118,8 @@ int check_common(int M, int N, int K, const void* a, const void* as, const void*
 // ------------------------------------------------------------------------------------------
 template <int CG, int BN, int STAGES, typename OutT>
 int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
-                const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, cudaStream_t stream) {
+                const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, int accumulate,
+                cudaStream_t stream) {
   using Cfg = wb::GemmCfg<CG, BN, STAGES>;
   CUtensorMap tmA, tmB;
   int rc = make_operand_map(&tmA, a, M, K / 2, Cfg::BM);
@@ -139,6 +140,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   p.group_n = 16;
   const int esz = int(sizeof(OutT));
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0) ? 1 : 0;
+  p.accumulate = accumulate;
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_gemm_kernel<CG, BN, STAGES, OutT>;
   rc = set_smem(kernel, Cfg::SMEM_BYTES);
@@ -165,21 +167,21 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
 template <int CG, int BN, int STAGES>
 int launch_tile_dtype(int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as,
                       const void* b, const void* bs, void* c, long long ldc, int sfa_rb, int sfb_rb,
-                      cudaStream_t stream) {
+                      int accumulate, cudaStream_t stream) {
   if (c_dtype == WB200_F32)
-    return launch_tile<CG, BN, STAGES, float>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
-  return launch_tile<CG, BN, STAGES, __nv_bfloat16>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+    return launch_tile<CG, BN, STAGES, float>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+  return launch_tile<CG, BN, STAGES, __nv_bfloat16>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
 }
 
 int dispatch_tile(unsigned path, bool n128, int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a,
                   const void* as, const void* b, const void* bs, void* c, long long ldc, int sfa_rb, int sfb_rb,
-                  cudaStream_t stream) {
+                  int accumulate, cudaStream_t stream) {
   if (path == WB200_PATH_TILE_2CTA) {
-    if (n128) return launch_tile_dtype<2, 128, 8>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
-    return launch_tile_dtype<2, 256, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+    if (n128) return launch_tile_dtype<2, 128, 8>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    return launch_tile_dtype<2, 256, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
   }
-  if (n128) return launch_tile_dtype<1, 128, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
-  return launch_tile_dtype<1, 256, 4>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, stream);
+  if (n128) return launch_tile_dtype<1, 128, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+  return launch_tile_dtype<1, 256, 4>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -193,7 +195,7 @@ size_t skinny_workspace_bytes(int sm_count, int M) {
 
 template <int NP, int STAGES, typename OutT>
 int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
-                  const void* bs, void* c, long long ldc, void* ws, cudaStream_t stream) {
+                  const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream) {
   using Cfg = wb::SkinnyCfg<NP, STAGES>;
   CUtensorMap tmW, tmX;
   int rc = make_operand_map(&tmW, b, N, K / 2, 128);
@@ -212,6 +214,7 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   p.sfw_row_blocks = wb::sf_row_blocks(N);
   p.tiles_n = (N + 127) / 128;
   p.num_kb = (K + 255) / 256;
+  p.accumulate = accumulate;
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_skinny_kernel<NP, STAGES, OutT>;
   rc = set_smem(kernel, Cfg::SMEM_BYTES);
@@ -225,11 +228,11 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
 
 template <typename OutT>
 int dispatch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
-                    const void* bs, void* c, long long ldc, void* ws, cudaStream_t stream) {
-  if (M <= 16) return launch_skinny<16, 10, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, stream);
-  if (M <= 32) return launch_skinny<32, 9, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, stream);
-  if (M <= 64) return launch_skinny<64, 8, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, stream);
-  return launch_skinny<128, 6, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, stream);
+                    const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream) {
+  if (M <= 16) return launch_skinny<16, 10, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
+  if (M <= 32) return launch_skinny<32, 9, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
+  if (M <= 64) return launch_skinny<64, 8, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
+  return launch_skinny<128, 6, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
 }
 
 }  // namespace
@@ -319,8 +322,10 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   unsigned path = flags & WB200_PATH_MASK;
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE)) != 0) return fail(WB200_ERR_INVALID_ARG, "unknown flag bits %#x", flags);
   if (path > WB200_PATH_SKINNY) return fail(WB200_ERR_INVALID_ARG, "unknown path flag %u", path);
   const bool n128_forced = (flags & WB200_TILE_N128) != 0;
+  const int accumulate = (flags & WB200_ACCUMULATE) ? 1 : 0;
   if (path == WB200_PATH_AUTO) {
     const bool ws_ok = workspace && workspace_bytes >= skinny_workspace_bytes(dev->sm_count, M);
     if (M <= 128 && ws_ok) path = WB200_PATH_SKINNY;
@@ -334,8 +339,8 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
                   skinny_workspace_bytes(dev->sm_count, M), workspace ? workspace_bytes : size_t(0));
     if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(WB200_ERR_ALIGNMENT, "workspace must be 16-byte aligned");
     if (c_dtype == WB200_F32)
-      return dispatch_skinny<float>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, s);
-    return dispatch_skinny<__nv_bfloat16>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, s);
+      return dispatch_skinny<float>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, accumulate, s);
+    return dispatch_skinny<__nv_bfloat16>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, accumulate, s);
   }
   // Narrow problems fill more SMs with 128-wide tiles.
   bool n128 = n128_forced;
@@ -344,7 +349,7 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
     if (tiles256 < dev->sm_count) n128 = true;
   }
   return dispatch_tile(path, n128, c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc,
-                       wb::sf_row_blocks(M), wb::sf_row_blocks(N), s);
+                       wb::sf_row_blocks(M), wb::sf_row_blocks(N), accumulate, s);
 }
 
 int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* row_block_offsets, int N, int K,
@@ -370,7 +375,7 @@ int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* 
     if (rc) return rc;
     const unsigned path = (Mg > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
     rc = dispatch_tile(path, false, c_dtype, *dev, Mg, N, K, ag, asg, b_ptrs[g], b_scale_ptrs[g], cg, ldc,
-                       wb::sf_row_blocks(Mg), wb::sf_row_blocks(N), static_cast<cudaStream_t>(stream));
+                       wb::sf_row_blocks(Mg), wb::sf_row_blocks(N), 0, static_cast<cudaStream_t>(stream));
     if (rc) return rc;
   }
   return WB200_OK;

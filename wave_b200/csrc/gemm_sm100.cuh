@@ -64,6 +64,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int group_n;        // N tiles per raster group
   int vec_ok;         // C base and row pitch allow 16-byte stores
+  int accumulate;     // add to the values already in C instead of overwriting them
   int* status;
 };
 
@@ -77,6 +78,34 @@ __device__ __forceinline__ void raster_tile(int t, int tiles_m, int tiles_n, int
   const int gw = min(group_n, tiles_n - n0);
   mt = r / gw;
   nt = n0 + (r - mt * gw);
+}
+
+// Adds the 32 values already in C (row pointer p) to r: the accumulate-into-C form the
+// reference's split-K template has (tagged_mxfp4_gemm.py:780-781, caller-initialised C).
+template <typename OutT>
+__device__ __forceinline__ void add_old_chunk32(const OutT* __restrict__ p, uint32_t (&r)[32], int ncols,
+                                                bool vec) {
+  if constexpr (sizeof(OutT) == 4) {
+    if (vec && ncols == 32) {
+      const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = q[j];
+        r[4 * j + 0] = __float_as_uint(__uint_as_float(r[4 * j + 0]) + __uint_as_float(v.x));
+        r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(v.y));
+        r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(v.z));
+        r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + __uint_as_float(v.w));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) r[j] = __float_as_uint(__uint_as_float(r[j]) + reinterpret_cast<const float*>(p)[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(p[j]));
+  }
 }
 
 template <typename OutT>
@@ -192,7 +221,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t fb = full_bar(stage);
           mbar_expect_tx(fb, Cfg::STAGE_BYTES);
           tma_load_2d(sA, &tmA, kb * 128, a_row, fb);
-          if constexpr (Cfg::B_ROWS <= 256) tma_load_2d(sB, &tmB, kb * 128, b_row, fb);
+          tma_load_2d(sB, &tmB, kb * 128, b_row, fb);
           bulk_load(sSFA, p.sfa + (size_t(sfa_rb) * p.ka_atoms + 2 * kb) * 512, 1024, fb);
 #pragma unroll
           for (int j = 0; j < BN / 128; ++j) {
@@ -319,8 +348,12 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (ci == 0) release();
         }
         const int col = col0 + chunk * 32;
-        if (row < p.M && col < p.N)
-          store_chunk32<OutT>(C + size_t(row) * p.ldc + col, r, min(32, p.N - col), p.vec_ok != 0);
+        if (row < p.M && col < p.N) {
+          OutT* dst = C + size_t(row) * p.ldc + col;
+          const int ncols = min(32, p.N - col);
+          if (p.accumulate) add_old_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);
+          store_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);
+        }
       }
       if constexpr (!Cfg::OVERLAP) release();
     }

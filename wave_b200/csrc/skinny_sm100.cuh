@@ -52,6 +52,7 @@ struct SkinnyParams {
   int sfw_row_blocks;
   int tiles_n;   // ceil(N / 128)
   int num_kb;    // ceil(K / 256)
+  int accumulate;  // add to the values already in C instead of overwriting them
   int* status;
 };
 
@@ -223,8 +224,15 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             for (int j = 0; j < 16; ++j) {
               const int m = c0 + j;
               if (m < p.M) {
-                if constexpr (sizeof(OutT) == 4) C[size_t(m) * p.ldc + n] = __uint_as_float(r[j]);
-                else C[size_t(m) * p.ldc + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                OutT* dst = C + size_t(m) * p.ldc + n;
+                float v = __uint_as_float(r[j]);
+                if constexpr (sizeof(OutT) == 4) {
+                  if (p.accumulate) v += *dst;
+                  *dst = v;
+                } else {
+                  if (p.accumulate) v += __bfloat162float(*dst);
+                  *dst = __float2bfloat16_rn(v);
+                }
               }
             }
           }
@@ -259,8 +267,14 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 const int slot = 2 * c + ((a0 / p.num_kb) == tile ? 0 : 1);
                 acc += __ldcg(p.partials + (size_t(slot) * p.M + m) * 128 + nl);
               }
-              if constexpr (sizeof(OutT) == 4) C[size_t(m) * p.ldc + n] = acc;
-              else C[size_t(m) * p.ldc + n] = __float2bfloat16_rn(acc);
+              OutT* dst = C + size_t(m) * p.ldc + n;
+              if constexpr (sizeof(OutT) == 4) {
+                if (p.accumulate) acc += *dst;
+                *dst = acc;
+              } else {
+                if (p.accumulate) acc += __bfloat162float(*dst);
+                *dst = __float2bfloat16_rn(acc);
+              }
             }
           }
           if (threadIdx.x == 64) p.counters[tile] = 0u;

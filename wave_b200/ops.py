@@ -1,0 +1,151 @@
+"""Torch-tensor front ends of the C ABI: scale repack, dequantisation aid, and the GEMM launch.
+
+PyTorch is used for device memory and streams only; every computation happens in
+libwave_b200.so. Launches go to `torch.cuda.current_stream()` and return without synchronising,
+as the reference's launch shim does (wave_lang/kernel/wave/utils/run_utils.py:87,134).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from collections import OrderedDict
+
+import torch
+
+from . import _lib
+
+SCALE_GROUP_SIZE = 32
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _as_u8(t: torch.Tensor, what: str) -> torch.Tensor:
+    if t.dtype not in (torch.uint8, torch.int8):
+        raise ValueError(f"{what} must be uint8 or int8 (packed bytes), got {t.dtype}")
+    if not t.is_cuda:
+        raise ValueError(f"{what} must be a CUDA tensor; wave_b200 has no CPU path")
+    return t
+
+
+class PackedScales:
+    """E8M0 scales of a [rows, K/32] matrix in the tcgen05 scale-factor layout (flat uint8)."""
+
+    __slots__ = ("data", "rows", "K")
+
+    def __init__(self, data: torch.Tensor, rows: int, K: int):
+        self.data, self.rows, self.K = data, rows, K
+
+    @property
+    def device(self):
+        return self.data.device
+
+
+def packed_scale_bytes(rows: int, K: int) -> int:
+    return int(_lib.load().wb200_packed_scale_bytes(rows, K))
+
+
+def repack_scales(scale: torch.Tensor, out: torch.Tensor | None = None) -> PackedScales:
+    """Row-major [rows, K/32] E8M0 scales -> PackedScales, on the current stream."""
+    lib = _lib.load()
+    _as_u8(scale, "scale")
+    if scale.dim() != 2:
+        raise ValueError(f"scale must be 2-D [rows, K/32], got shape {tuple(scale.shape)}")
+    if scale.stride(1) != 1:
+        scale = scale.contiguous()
+    rows, kb = scale.shape
+    K = kb * SCALE_GROUP_SIZE
+    nbytes = packed_scale_bytes(rows, K)
+    if out is None:
+        out = torch.empty(nbytes, dtype=torch.uint8, device=scale.device)
+    elif out.numel() < nbytes or out.dtype != torch.uint8 or not out.is_contiguous():
+        raise ValueError("repack_scales: `out` must be a contiguous uint8 tensor of at least packed_scale_bytes(rows, K)")
+    with torch.cuda.device(scale.device):
+        _lib.check(lib.wb200_repack_scales(scale.data_ptr(), scale.stride(0), rows, K, out.data_ptr(), _stream()))
+    return PackedScales(out, rows, K)
+
+
+def dequant_mxfp4(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """[R, K/2] codes, [R, K/32] scales -> [R, K] f32 on the GPU (test aid)."""
+    lib = _lib.load()
+    q = _as_u8(q, "q").contiguous()
+    scale = _as_u8(scale, "scale").contiguous()
+    rows, K = q.shape[0], q.shape[1] * 2
+    if tuple(scale.shape) != (rows, K // SCALE_GROUP_SIZE):
+        raise ValueError(f"scale shape {tuple(scale.shape)} does not match q {tuple(q.shape)}")
+    out = torch.empty(rows, K, dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(lib.wb200_mxfp4_dequant(q.data_ptr(), scale.data_ptr(), rows, K, out.data_ptr(), _stream()))
+    return out
+
+
+# One skinny-path workspace per device, created on first use.
+_workspaces: dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _lib.check(_lib.load().wb200_workspace_init(ws.data_ptr(), nbytes, _stream()))
+        _workspaces[idx] = ws
+    return ws
+
+
+_DTYPE_CODE = {torch.float32: _lib.WB200_F32, torch.bfloat16: _lib.WB200_BF16}
+
+
+def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_sf: PackedScales, c: torch.Tensor,
+                       flags: int = _lib.PATH_AUTO) -> None:
+    """c[M, N] = dequant(a) @ dequant(b).T with both scale sets already packed. c may be a column
+    block of a wider matrix (row stride >= N)."""
+    lib = _lib.load()
+    M, N, K = a.shape[0], b.shape[0], a.shape[1] * 2
+    if c.dtype not in _DTYPE_CODE:
+        raise ValueError(f"c must be float32 or bfloat16, got {c.dtype}")
+    if c.dim() != 2 or tuple(c.shape) != (M, N) or c.stride(1) != 1:
+        raise ValueError(f"c must be [M, N] = [{M}, {N}] with unit column stride, got {tuple(c.shape)} strides {c.stride()}")
+    if b.shape[1] * 2 != K:
+        raise ValueError(f"a and b disagree on K: {K} vs {b.shape[1] * 2}")
+    if (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
+        raise ValueError("packed scales do not match the operand shapes")
+    ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
+    ws_ptr = 0
+    if ws_bytes:
+        ws_ptr = _workspace(a.device, ws_bytes).data_ptr()
+    with torch.cuda.device(a.device):
+        _lib.check(lib.wb200_mxfp4_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
+                                        c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0), ws_ptr, ws_bytes, flags,
+                                        _stream()))
+
+
+class WeightScaleCache:
+    """Packed copies of weight scales, keyed by the identity and version of the row-major tensor,
+    so that a weight's scales are repacked once and reused by later calls."""
+
+    def __init__(self, capacity: int = 64):
+        self.capacity = capacity
+        self._entries: OrderedDict = OrderedDict()
+
+    def get(self, scale: torch.Tensor) -> PackedScales:
+        key = (scale.data_ptr(), tuple(scale.shape), scale.stride(), scale.device.index, scale._version)
+        hit = self._entries.get(key)
+        if hit is not None:
+            self._entries.move_to_end(key)
+            return hit
+        packed = repack_scales(scale)
+        self._entries[key] = packed
+        while len(self._entries) > self.capacity:
+            self._entries.popitem(last=False)
+        return packed
+
+    def clear(self) -> None:
+        self._entries.clear()
+
+
+def check_device_status() -> None:
+    """Synchronise the current stream and raise DeviceTimeoutError if a kernel's bounded wait gave up."""
+    detail = ctypes.c_int(0)
+    _lib.check(_lib.load().wb200_check_device_status(_stream(), ctypes.byref(detail)))

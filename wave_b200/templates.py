@@ -1,0 +1,174 @@
+"""MXFP4 scaled-GEMM kernel templates with the reference's names and signatures.
+
+In the reference these functions build a traced DSL kernel plus its symbol table
+(wave_lang/kernel/wave/templates/gemm.py:134-205, wave_lang/kernel/wave/templates/tagged_mxfp4_gemm.py).
+Here they return a small descriptor that `wave_compile` turns into a launcher of the precompiled
+sm_100a kernels. Tile, wave and address-space arguments describe AMD work distribution; they are
+accepted, recorded, and have no effect on B200, where the tile shape is fixed by tcgen05.mma
+(128 or 256 rows x 128/256 columns x 256 K elements per stage).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+from . import _lib
+from .compile import SchedulingType, WaveCompileOptions
+from .constraints import ScaledMMAType
+from .lang import SHARED_ADDRESS_SPACE, DataType, as_output_dtype, f32
+
+
+@dataclass
+class ScaledGemmTemplate:
+    """What a template function returns in place of the reference's traced kernel."""
+
+    name: str
+    shape: Optional[tuple]                 # (M, N, K) given at creation, or None
+    output_dtype: DataType = f32
+    accumulate: bool = False               # split-K contract: add into caller-initialised c
+    num_splits: int = 1
+    preshuffled_scales: bool = False       # scale arguments are PackedScales from e8m0_shuffle
+    preshuffled_b: bool = False            # b went through b_preshuffle (identity on B200)
+    hints: dict = field(default_factory=dict)
+
+
+def _hyperparams(shape, block_shape, extra=None):
+    h = {"M": shape[0], "N": shape[1], "K": shape[2],
+         "BLOCK_M": block_shape[0], "BLOCK_N": block_shape[1], "BLOCK_K": block_shape[2]}
+    if extra:
+        h.update(extra)
+    return h
+
+
+def get_scaled_gemm_kernel(shape, mfma_variant: ScaledMMAType, block_shape=None, waves_per_block=None):
+    """(kernel, hyperparams) for c[M, N] f32 = a * b^T — wave_lang/kernel/wave/templates/gemm.py:134-205.
+
+    Use as the reference does:
+        kernel, hyper = get_scaled_gemm_kernel(shape, ScaledMMAType.F32_16x16x128_F8F6F4)
+        gemm = wave_compile(WaveCompileOptions(subs=hyper), kernel)
+        gemm(a, a_scale, b, b_scale, c)
+    """
+    if not isinstance(mfma_variant, ScaledMMAType):
+        raise TypeError("mfma_variant must be a ScaledMMAType")
+    block_shape = block_shape or (32, 32, 256)
+    waves_per_block = waves_per_block or (2, 2)
+    tpl = ScaledGemmTemplate("scaled_gemm", tuple(shape), f32,
+                             hints={"mfma_variant": mfma_variant, "block_shape": tuple(block_shape),
+                                    "waves_per_block": tuple(waves_per_block)})
+    return tpl, _hyperparams(shape, block_shape, {"ADDRESS_SPACE": SHARED_ADDRESS_SPACE})
+
+
+def _tagged(name, shape, block_shape, wave_shape, mfma_variant, output_dtype, **flags):
+    out = as_output_dtype(output_dtype)
+    tpl = ScaledGemmTemplate(name, tuple(shape), out,
+                             hints={"mfma_variant": mfma_variant, "block_shape": tuple(block_shape),
+                                    "wave_shape": tuple(wave_shape)}, **flags)
+    options = WaveCompileOptions(subs=_hyperparams(shape, block_shape), canonicalize=True,
+                                 schedule=SchedulingType.MANUAL, use_global_to_shared=True,
+                                 minimize_shared_allocs=False)
+    return tpl, options
+
+
+def get_tagged_mxfp4_gemm(shape=(1024, 1024, 8192), block_shape=(256, 256, 256), wave_shape=(2, 2),
+                          mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4, a_address_space=SHARED_ADDRESS_SPACE,
+                          b_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True, group_size_n=32,
+                          output_dtype=f32):
+    """(kernel, options); f32 or bf16 output — wave_lang/kernel/wave/templates/tagged_mxfp4_gemm.py:38-145."""
+    return _tagged("tagged_mxfp4_gemm", shape, block_shape, wave_shape, mfma_variant, output_dtype)
+
+
+def get_tagged_mxfp4_gemm_preshuffle_scales(shape=(1024, 1024, 8192), block_shape=(256, 256, 256), wave_shape=(2, 2),
+                                            mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
+                                            a_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True,
+                                            group_size_n=32, output_dtype=f32):
+    """Scales arrive pre-shuffled: pass the result of `mxfp_utils.e8m0_shuffle` for a_scale and b_scale
+    (tagged_mxfp4_gemm.py:334-365). On B200 the shuffle is the tcgen05 scale-factor repack."""
+    return _tagged("tagged_mxfp4_gemm_preshuffle_scales", shape, block_shape, wave_shape, mfma_variant, output_dtype,
+                   preshuffled_scales=True)
+
+
+def get_tagged_mxfp4_gemm_preshuffle_scales_and_B(shape=(1024, 1024, 8192), block_shape=(256, 256, 256),
+                                                  wave_shape=(2, 2),
+                                                  mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
+                                                  a_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True,
+                                                  group_size_n=32, output_dtype=f32):
+    """tagged_mxfp4_gemm.py:368-403: pre-shuffled scales and pre-shuffled b."""
+    return _tagged("tagged_mxfp4_gemm_preshuffle_scales_and_B", shape, block_shape, wave_shape, mfma_variant,
+                   output_dtype, preshuffled_scales=True, preshuffled_b=True)
+
+
+def get_tagged_mxfp4_gemm_preshuffle_b(shape=(1024, 1024, 8192), block_shape=(256, 256, 256), wave_shape=(2, 2),
+                                       mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
+                                       a_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True,
+                                       group_size_n=32, output_dtype=f32):
+    """tagged_mxfp4_gemm.py:950-991."""
+    return _tagged("tagged_mxfp4_gemm_preshuffle_b", shape, block_shape, wave_shape, mfma_variant, output_dtype,
+                   preshuffled_scales=True, preshuffled_b=True)
+
+
+def get_tagged_mxfp4_gemm_preshuffle_b_wide_store(shape=(1024, 1024, 8192), block_shape=(256, 256, 256),
+                                                  wave_shape=(2, 2),
+                                                  mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
+                                                  a_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True,
+                                                  group_size_n=32, output_dtype=f32):
+    """tagged_mxfp4_gemm.py:994-1035; every epilogue here already stores 16 bytes per thread."""
+    return _tagged("tagged_mxfp4_gemm_preshuffle_b_wide_store", shape, block_shape, wave_shape, mfma_variant,
+                   output_dtype, preshuffled_scales=True, preshuffled_b=True)
+
+
+def _splitk(name, shape, num_splits, block_shape, wave_shape, mfma_variant, output_type, **flags):
+    # Same preconditions and messages as tagged_mxfp4_gemm.py:636-645.
+    k_per_split = math.ceil(shape[2] / num_splits)
+    if k_per_split < block_shape[2]:
+        raise ValueError(
+            f"K per split ({k_per_split}) is less than BLOCK_K ({block_shape[2]}). "
+            f"Reduce num_splits or BLOCK_K so that each split has at least BLOCK_K elements.")
+    if k_per_split % block_shape[2] != 0:
+        raise ValueError(f"k_per_split ({k_per_split}) must be a multiple of BLOCK_K ({block_shape[2]}).")
+    tpl, options = _tagged(name, shape, block_shape, wave_shape, mfma_variant, output_type, accumulate=True,
+                           num_splits=num_splits, **flags)
+    return tpl, options
+
+
+def get_tagged_splitk_mxfp4_gemm(shape, num_splits=2, block_shape=(128, 128, 256), wave_shape=(2, 2),
+                                 mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
+                                 a_address_space=SHARED_ADDRESS_SPACE, output_type=f32):
+    """Split-K GEMM that ADDS into c; the caller zero-initialises c (tagged_mxfp4_gemm.py:819-858).
+
+    The reference sums per-split partials with atomics in the output type. Here the K range is split
+    by the kernel itself (stream-K for M <= 128), partials stay in f32 and are added in a fixed
+    order; `num_splits` is validated and otherwise ignored.
+    """
+    return _splitk("tagged_splitk_mxfp4_gemm", shape, num_splits, block_shape, wave_shape, mfma_variant, output_type)
+
+
+def get_tagged_splitk_mxfp4_gemm_preshuffle_scales(shape, num_splits=2, block_shape=(128, 128, 256),
+                                                   wave_shape=(2, 2),
+                                                   mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
+                                                   a_address_space=SHARED_ADDRESS_SPACE, output_type=f32):
+    """tagged_mxfp4_gemm.py:861-903."""
+    return _splitk("tagged_splitk_mxfp4_gemm_preshuffle_scales", shape, num_splits, block_shape, wave_shape,
+                   mfma_variant, output_type, preshuffled_scales=True)
+
+
+def get_tagged_splitk_mxfp4_gemm_preshuffle_b(shape, num_splits=2, block_shape=(128, 128, 256), wave_shape=(2, 2),
+                                              mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
+                                              a_address_space=SHARED_ADDRESS_SPACE, output_type=f32):
+    """tagged_mxfp4_gemm.py:906-947."""
+    return _splitk("tagged_splitk_mxfp4_gemm_preshuffle_b", shape, num_splits, block_shape, wave_shape,
+                   mfma_variant, output_type, preshuffled_scales=True, preshuffled_b=True)
+
+
+def reorder_mxfp4_workgroups(m_tiles: int, n_tiles: int, group_size_n: int, flat_id: int):
+    """Tile order of the persistent kernels, as a host function for tests: tile ids run through
+    groups of `group_size_n` N tiles, each group swept down M with N fastest. Same purpose as the
+    reference's _reorder_mxfp4_workgroups (tagged_mxfp4_gemm.py:1038-1089): consecutive ids share
+    A rows and a bounded set of B rows, so they hit in L2."""
+    per_group = group_size_n * m_tiles
+    g, r = divmod(flat_id, per_group)
+    n0 = g * group_size_n
+    gw = min(group_size_n, n_tiles - n0)
+    mt, j = divmod(r, gw)
+    return mt, n0 + j
