@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 
 namespace {
@@ -91,6 +92,22 @@ int make_operand_map(CUtensorMap* map, const void* base, long long rows, long lo
   return WB200_OK;
 }
 
+// Packed scale array ([row_blocks][k_atoms][512 bytes]) as a 2-D tensor of 32-bit words, one
+// row per 128-row block; a box is 1024 bytes (the two atoms of one pipeline stage) x box_rows.
+int make_scale_map(CUtensorMap* map, const void* base, int row_blocks, int k_atoms, int box_rows) {
+  cuuint64_t dims[2] = {cuuint64_t(k_atoms) * 128, cuuint64_t(row_blocks)};
+  cuuint64_t strides[1] = {cuuint64_t(k_atoms) * 512};
+  cuuint32_t box[2] = {256u, cuuint32_t(box_rows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with CUresult %d (row blocks %d, atoms %d)", int(r),
+                row_blocks, k_atoms);
+  return WB200_OK;
+}
+
 template <typename K>
 int set_smem(K kernel, int bytes) {
   WB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
@@ -121,10 +138,14 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
                 const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, int accumulate,
                 cudaStream_t stream) {
   using Cfg = wb::GemmCfg<CG, BN, STAGES>;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB;
   int rc = make_operand_map(&tmA, a, M, K / 2, Cfg::BM);
   if (rc) return rc;
   rc = make_operand_map(&tmB, b, N, K / 2, Cfg::B_ROWS);
+  if (rc) return rc;
+  rc = make_scale_map(&tmSFA, as, sfa_row_blocks, wb::sf_k_atoms(K), 1);
+  if (rc) return rc;
+  rc = make_scale_map(&tmSFB, bs, sfb_row_blocks, wb::sf_k_atoms(K), BN / 128);
   if (rc) return rc;
   wb::GemmParams p;
   p.sfa = static_cast<const uint8_t*>(as);
@@ -141,6 +162,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   const int esz = int(sizeof(OutT));
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0) ? 1 : 0;
   p.accumulate = accumulate;
+  p.dbg = getenv("WB200_DBG") ? atoi(getenv("WB200_DBG")) : 0;
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_gemm_kernel<CG, BN, STAGES, OutT>;
   rc = set_smem(kernel, Cfg::SMEM_BYTES);
@@ -160,7 +182,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p));
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, p));
   return WB200_OK;
 }
 
@@ -178,6 +200,8 @@ int dispatch_tile(unsigned path, bool n128, int c_dtype, const DeviceInfo& dev, 
                   int accumulate, cudaStream_t stream) {
   if (path == WB200_PATH_TILE_2CTA) {
     if (n128) return launch_tile_dtype<2, 128, 8>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    if (getenv("WB200_STAGES") && atoi(getenv("WB200_STAGES")) == 5) return launch_tile_dtype<2, 256, 5>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    if (getenv("WB200_STAGES") && atoi(getenv("WB200_STAGES")) == 4) return launch_tile_dtype<2, 256, 4>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
     return launch_tile_dtype<2, 256, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
   }
   if (n128) return launch_tile_dtype<1, 128, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
@@ -197,10 +221,14 @@ template <int NP, int STAGES, typename OutT>
 int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                   const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream) {
   using Cfg = wb::SkinnyCfg<NP, STAGES>;
-  CUtensorMap tmW, tmX;
+  CUtensorMap tmW, tmX, tmSFW, tmSFX;
   int rc = make_operand_map(&tmW, b, N, K / 2, 128);
   if (rc) return rc;
   rc = make_operand_map(&tmX, a, M, K / 2, NP);
+  if (rc) return rc;
+  rc = make_scale_map(&tmSFW, bs, wb::sf_row_blocks(N), wb::sf_k_atoms(K), 1);
+  if (rc) return rc;
+  rc = make_scale_map(&tmSFX, as, 1, wb::sf_k_atoms(K), 1);
   if (rc) return rc;
   wb::SkinnyParams p;
   p.sfw = static_cast<const uint8_t*>(bs);
@@ -215,13 +243,14 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   p.tiles_n = (N + 127) / 128;
   p.num_kb = (K + 255) / 256;
   p.accumulate = accumulate;
+  p.dbg = getenv("WB200_DBG") ? atoi(getenv("WB200_DBG")) : 0;
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_skinny_kernel<NP, STAGES, OutT>;
   rc = set_smem(kernel, Cfg::SMEM_BYTES);
   if (rc) return rc;
   const long long units = (long long)p.tiles_n * p.num_kb;
   const int grid = int(units < dev.sm_count ? units : dev.sm_count);
-  kernel<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, p);
+  kernel<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, tmSFW, tmSFX, p);
   WB_CUDA(cudaGetLastError());
   return WB200_OK;
 }

@@ -15,11 +15,12 @@
 //     swizzle; scale factors arrive as 512-byte atoms (128 rows x 4 K-blocks) and are copied to
 //     tensor memory with tcgen05.cp before the four K = 64 MMAs of a stage;
 //   * two accumulators live in tensor memory so that the epilogue of tile i overlaps the main
-//     loop of tile i+1. With BN = 256 the two accumulators overlap by 32 columns (512 columns
+//     loop of tile i+1. With BN = 256 the two accumulators overlap by 48 columns (512 columns
 //     cannot hold 2 x 256 plus the scale factors); the epilogue drains the shared columns first
 //     and releases the next main loop as soon as they are free;
 //   * CG = 2 pairs two CTAs of a cluster on one 256-row tile (cta_group::2): each CTA loads its
-//     own 128 rows of A and its half of the B rows with plain TMA loads (no multicast).
+//     own 128 rows of A and its half of the B rows with plain TMA loads (no multicast); the loads
+//     of both CTAs complete on the leader CTA's barrier, and the leader issues the MMAs.
 #pragma once
 #include "ptx.cuh"
 #include <cuda_bf16.h>
@@ -38,15 +39,20 @@ struct GemmCfg {
   static constexpr int SFA_BYTES = 2 * 512;               // 128 rows x 8 K-blocks
   static constexpr int SFB_BYTES = (BN / 128) * 2 * 512;  // BN rows x 8 K-blocks
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-  static constexpr int NUM_BARRIERS = 3 * STAGES + 4;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
   static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
   // tensor-memory columns
   static constexpr int TMEM_COLS = 512;
   static constexpr bool OVERLAP = (BN == 256);
   static constexpr int ACC_COL0 = 0;
-  static constexpr int ACC_COL1 = OVERLAP ? 224 : BN;
-  static constexpr int SFA_COL = 480;  // 8 columns: 2 atoms x 4
-  static constexpr int SFB_COL = 488;  // (BN/128) * 8 columns
+  // Scale factors live in a small ring of column sets so that the tcgen05.cp of one K block does
+  // not have to wait for the MMAs of the previous block to finish reading theirs.
+  static constexpr int SF_SET_COLS = 8 + BN / 16;  // A: 2 atoms x 4 columns, B: (BN/128) x 2 atoms x 4
+  static constexpr int SF_SETS = OVERLAP ? 2 : 4;
+  static constexpr int SF_COL = OVERLAP ? 464 : 256;
+  static constexpr int OVERLAP_CHUNKS = 2;         // 32-column chunks shared by the two accumulators (48 columns)
+  static constexpr int ACC_COL1 = OVERLAP ? 208 : BN;
+  static_assert(SF_COL + SF_SETS * SF_SET_COLS <= 512, "scale-factor ring does not fit in tensor memory");
   static constexpr int THREADS = 192;
   static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
@@ -65,6 +71,7 @@ struct GemmParams {
   int group_n;        // N tiles per raster group
   int vec_ok;         // C base and row pitch allow 16-byte stores
   int accumulate;     // add to the values already in C instead of overwriting them
+  int dbg;
   int* status;
 };
 
@@ -144,6 +151,7 @@ __device__ __forceinline__ void store_chunk32(OutT* __restrict__ p, const uint32
 template <int CG, int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                   const GemmParams p) {
   using Cfg = GemmCfg<CG, BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -160,9 +168,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  auto peer_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
-  auto acc_full_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + s); };
-  auto acc_empty_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + 2 + s); };
+  auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::NUM_BARRIERS * 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   WaitCtx ctx{abort_flag, p.status};
@@ -171,7 +178,6 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(peer_full_bar(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(acc_full_bar(s), 1);
@@ -187,6 +193,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmSFA);
+    prefetch_tensormap(&tmSFB);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -204,107 +212,105 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      for (int t = first_tile; t < num_tiles; t += tile_step) {
-        int mt, nt;
-        raster_tile(t, p.tiles_m, p.tiles_n, p.group_n, mt, nt);
-        const int a_row = (mt * CG + int(rank)) * Cfg::BM;
-        const int b_row = nt * BN + int(rank) * Cfg::B_ROWS;
-        const int sfa_rb = min(mt * CG + int(rank), p.sfa_row_blocks - 1);
+    // The whole warp walks the loop; one elected lane issues the copies.
+    uint32_t stage = 0, phase = 0;
+    for (int t = first_tile; t < num_tiles; t += tile_step) {
+      int mt, nt;
+      raster_tile(t, p.tiles_m, p.tiles_n, p.group_n, mt, nt);
+      const int a_row = (mt * CG + int(rank)) * Cfg::BM;
+      const int b_row = nt * BN + int(rank) * Cfg::B_ROWS;
+      const int sfa_rb = mt * CG + int(rank);
+      const int sfb_rb = nt * (BN / 128);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
+        const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+        const uint32_t sB = sA + Cfg::A_BYTES;
+        const uint32_t sSFA = sB + Cfg::B_BYTES;
+        const uint32_t sSFB = sSFA + Cfg::SFA_BYTES;
+        // With a CTA pair, every load of both CTAs reports to the leader's barrier, which
+        // therefore expects the bytes of two stages; the second CTA only issues its copies.
+        const uint32_t fb = (CG == 2) ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
+        if (elect_one()) {
+          if (leader) mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES * CG);
+          tma_load_2d<CG>(sA, &tmA, kb * 128, a_row, fb);
+          tma_load_2d<CG>(sB, &tmB, kb * 128, b_row, fb);
+          // scale factors: 1024 bytes (two atoms) per 128-row block and stage
+          tma_load_2d<CG>(sSFA, &tmSFA, kb * 256, sfa_rb, fb);
+          tma_load_2d<CG>(sSFB, &tmSFB, kb * 256, sfb_rb, fb);
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader) {
+      constexpr uint32_t idesc = make_idesc_mxf4(Cfg::BM * CG, BN);
+      const uint32_t peer_empty0 = (CG == 2) ? mapa_shared(empty_bar(0), 1) : 0u;
+      const uint32_t peer_acc_full0 = (CG == 2) ? mapa_shared(acc_full_bar(0), 1) : 0u;
+      uint32_t stage = 0, phase = 0, sf_set = 0;
+      int it = 0;
+      for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
+        const int as = it & 1;
+        // accumulator availability
+        if constexpr (Cfg::OVERLAP) {
+          // Needs the previous tile's epilogue to have drained the 48 shared columns
+          // (which also means the tile before that is fully drained).
+          if (it > 0 && !(p.dbg & 64)) {
+            const int ps = (it - 1) & 1;
+            mbar_wait<CG == 2>(acc_empty_bar(ps), uint32_t((it - 1) >> 1) & 1u, ctx, WB_DEV_TIMEOUT_MMA_ACC);
+          }
+        } else {
+          if (it >= 2)
+            mbar_wait<CG == 2>(acc_empty_bar(as), uint32_t((it - 2) >> 1) & 1u, ctx, WB_DEV_TIMEOUT_MMA_ACC);
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (as ? Cfg::ACC_COL1 : Cfg::ACC_COL0);
         for (int kb = 0; kb < num_kb; ++kb) {
-          mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
+          const uint32_t t_sfa = tmem_base + Cfg::SF_COL + sf_set * Cfg::SF_SET_COLS;
+          const uint32_t t_sfb = t_sfa + 8;
+          if (++sf_set == Cfg::SF_SETS) sf_set = 0;
+          mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
+          tc_fence_after_sync();
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sB = sA + Cfg::A_BYTES;
           const uint32_t sSFA = sB + Cfg::B_BYTES;
           const uint32_t sSFB = sSFA + Cfg::SFA_BYTES;
-          const uint32_t fb = full_bar(stage);
-          mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-          tma_load_2d(sA, &tmA, kb * 128, a_row, fb);
-          tma_load_2d(sB, &tmB, kb * 128, b_row, fb);
-          bulk_load(sSFA, p.sfa + (size_t(sfa_rb) * p.ka_atoms + 2 * kb) * 512, 1024, fb);
+          const uint64_t a_desc = make_desc_k_sw128(sA);
+          const uint64_t b_desc = make_desc_k_sw128(sB);
+          const uint64_t sfa_desc = make_desc_sf_atom(sSFA);
+          const uint64_t sfb_desc = make_desc_sf_atom(sSFB);
+          if (elect_one()) {
+            // scale factors: smem atoms -> tensor memory (4 columns per atom); +32 in the
+            // descriptor's address field = +512 bytes = the next atom
+            if (!(p.dbg & 2) || kb == 0) {
 #pragma unroll
-          for (int j = 0; j < BN / 128; ++j) {
-            const int rb = min(nt * (BN / 128) + j, p.sfb_row_blocks - 1);
-            bulk_load(sSFB + j * 1024, p.sfb + (size_t(rb) * p.ka_atoms + 2 * kb) * 512, 1024, fb);
-          }
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer / peer relay
-    if (lane == 0) {
-      if (leader) {
-        constexpr uint32_t idesc = make_idesc_mxf4(Cfg::BM * CG, BN);
-        uint32_t stage = 0, phase = 0;
-        int it = 0;
-        for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
-          const int as = it & 1;
-          // accumulator availability
-          if constexpr (Cfg::OVERLAP) {
-            // Needs the previous tile's epilogue to have drained the 32 shared columns
-            // (which also means the tile before that is fully drained).
-            if (it > 0) {
-              const int ps = (it - 1) & 1;
-              mbar_wait<CG == 2>(acc_empty_bar(ps), uint32_t((it - 1) >> 1) & 1u, ctx,
-                                 WB_DEV_TIMEOUT_MMA_ACC);
+              for (int a = 0; a < 2; ++a) utccp_sf_atom<CG>(t_sfa + a * 4, sfa_desc + uint64_t(a * 32));
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j)
+#pragma unroll
+                for (int a = 0; a < 2; ++a)
+                  utccp_sf_atom<CG>(t_sfb + a * (BN / 32) + j * 4, sfb_desc + uint64_t(j * 64 + a * 32));
             }
-          } else {
-            if (it >= 2)
-              mbar_wait<CG == 2>(acc_empty_bar(as), uint32_t((it - 2) >> 1) & 1u, ctx,
-                                 WB_DEV_TIMEOUT_MMA_ACC);
-          }
-          tc_fence_after_sync();
-          const uint32_t d_tmem = tmem_base + (as ? Cfg::ACC_COL1 : Cfg::ACC_COL0);
-          for (int kb = 0; kb < num_kb; ++kb) {
-            mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
-            if constexpr (CG == 2)
-              mbar_wait<true>(peer_full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_PEER);
-            tc_fence_after_sync();
-            const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
-            const uint32_t sB = sA + Cfg::A_BYTES;
-            const uint32_t sSFA = sB + Cfg::B_BYTES;
-            const uint32_t sSFB = sSFA + Cfg::SFA_BYTES;
-            // scale factors: smem atoms -> tensor memory (4 columns per atom)
+            if (!(p.dbg & 8)) {
 #pragma unroll
-            for (int a = 0; a < 2; ++a)
-              utccp_sf_atom<CG>(tmem_base + Cfg::SFA_COL + a * 4, make_desc_sf_atom(sSFA + a * 512));
-#pragma unroll
-            for (int j = 0; j < BN / 128; ++j)
-#pragma unroll
-              for (int a = 0; a < 2; ++a)
-                utccp_sf_atom<CG>(tmem_base + Cfg::SFB_COL + a * (BN / 32) + j * 4,
-                                  make_desc_sf_atom(sSFB + j * 1024 + a * 512));
-            const uint64_t a_desc = make_desc_k_sw128(sA);
-            const uint64_t b_desc = make_desc_k_sw128(sB);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              // K = 64 per instruction = 32 bytes inside the 128-byte swizzle row
-              const uint32_t sf_id = (k & 1) * 2;
-              mma_mxf4<CG>(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2),
-                           idesc_with_sf_id(idesc, sf_id),
-                           tmem_base + Cfg::SFA_COL + (k >> 1) * 4,
-                           tmem_base + Cfg::SFB_COL + (k >> 1) * (BN / 32),
-                           (kb > 0 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < 4; ++k) {
+                // K = 64 per instruction = 32 bytes inside the 128-byte swizzle row
+                mma_mxf4<CG>(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2),
+                             idesc_with_sf_id(idesc, (k & 1) * 2), t_sfa + (k >> 1) * 4,
+                             t_sfb + (k >> 1) * (BN / 32), (kb > 0 || k > 0) ? 1u : 0u);
+              }
             }
             // free the stage in both CTAs once these MMAs have read it
             tc_commit<CG>(empty_bar(stage));
-            if constexpr (CG == 2) tc_commit<CG>(mapa_shared(empty_bar(stage), 1));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if constexpr (CG == 2) tc_commit<CG>(peer_empty0 + 8u * stage);
+            if (kb == num_kb - 1) {
+              tc_commit<CG>(acc_full_bar(as));
+              if constexpr (CG == 2) tc_commit<CG>(peer_acc_full0 + 8u * as);
+            }
           }
-          tc_commit<CG>(acc_full_bar(as));
-          if constexpr (CG == 2) tc_commit<CG>(mapa_shared(acc_full_bar(as), 1));
-        }
-      } else {
-        // Second CTA of a pair: tell the leader when this CTA's stage has landed.
-        uint32_t stage = 0, phase = 0;
-        for (int t = first_tile; t < num_tiles; t += tile_step) {
-          for (int kb = 0; kb < num_kb; ++kb) {
-            mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
-            mbar_arrive_cluster(mapa_shared(peer_full_bar(stage), 0));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -328,27 +334,31 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-          if constexpr (CG == 2) mbar_arrive_cluster(as ? acc_empty_leader1 : acc_empty_leader0);
+          if constexpr (CG == 2) {
+            if (p.dbg & 128) mbar_arrive_cluster_relaxed(as ? acc_empty_leader1 : acc_empty_leader0);
+            else mbar_arrive_cluster(as ? acc_empty_leader1 : acc_empty_leader0);
+          }
           else mbar_arrive(acc_empty_bar(as));
         }
       };
       constexpr int NCHUNK = BN / 32;
 #pragma unroll 1
       for (int ci = 0; ci < NCHUNK; ++ci) {
-        // With overlapping accumulators the 32 columns shared with the other accumulator go first:
-        // the last chunk of accumulator 0, the first chunk of accumulator 1.
+        // With overlapping accumulators the columns shared with the other accumulator go first:
+        // the last two chunks of accumulator 0, the first two chunks of accumulator 1.
         int chunk = ci;
         if constexpr (Cfg::OVERLAP) {
-          if (as == 0) chunk = (ci == 0) ? (NCHUNK - 1) : (ci - 1);
+          if (as == 0)
+            chunk = (ci < Cfg::OVERLAP_CHUNKS) ? (NCHUNK - Cfg::OVERLAP_CHUNKS + ci) : (ci - Cfg::OVERLAP_CHUNKS);
         }
         uint32_t r[32];
         tmem_ld_32x32(t_acc + chunk * 32, r);
         tmem_ld_wait();
         if constexpr (Cfg::OVERLAP) {
-          if (ci == 0) release();
+          if (ci == Cfg::OVERLAP_CHUNKS - 1) release();
         }
         const int col = col0 + chunk * 32;
-        if (row < p.M && col < p.N) {
+        if (row < p.M && col < p.N && !(p.dbg & 32)) {
           OutT* dst = C + size_t(row) * p.ldc + col;
           const int ncols = min(32, p.N - col);
           if (p.accumulate) add_old_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);

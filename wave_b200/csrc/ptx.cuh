@@ -40,6 +40,21 @@ __device__ __forceinline__ uint32_t lane_id() {
   return l;
 }
 
+// True in exactly one lane of a converged warp. The role loops below are executed by whole warps
+// with warp-uniform values, and only the instruction issue is guarded by this predicate: that
+// keeps descriptors and addresses in uniform registers, which the TMA and tcgen05 instructions
+// take their operands from. Issuing them from a `lane == 0` branch instead costs a
+// vector-to-uniform register move per operand and was measured to bound both kernels.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -78,6 +93,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // Arrive on a barrier that lives in another CTA of the cluster (address from mapa_shared).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+// Same, without a release fence: for signals that publish no data written by this thread
+// (e.g. "the TMA copies into my shared memory have landed", which the barrier itself observed).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
@@ -142,13 +163,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 // TMA: tiled 2D load (global -> shared, completes on an mbarrier), untiled bulk load,
 // and tiled 2D store (shared -> global). No multicast forms anywhere.
 // ---------------------------------------------------------------------------------------------
+// CTA_GROUP = 2: the form a CTA pair uses; the mbarrier may then live in the peer CTA
+// (a shared::cluster address from mapa_shared) while the data lands in this CTA.
+template <int CTA_GROUP = 1>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* tmap, int x,
                                             int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
-      "l"(tmap), "r"(x), "r"(y), "r"(bar)
-      : "memory");
+  if constexpr (CTA_GROUP == 1)
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+        "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+  else
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+        "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
 }
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* tmap,
                                                  int x, int y, uint32_t bar, uint64_t policy) {

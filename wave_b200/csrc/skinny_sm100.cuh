@@ -35,8 +35,10 @@ struct SkinnyCfg {
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
   static constexpr int TMEM_COLS = 512;
   static constexpr int ACC_COL1 = NP;
-  static constexpr int SFW_COL = 480;
-  static constexpr int SFX_COL = 488;
+  // ring of scale-factor column sets (8 columns for the weights, 8 for the activations each), so
+  // that the tcgen05.cp of one unit does not wait for the MMAs of the previous unit
+  static constexpr int SF_COL = 256;
+  static constexpr int SF_SETS = 8;
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 };
 
@@ -53,6 +55,7 @@ struct SkinnyParams {
   int tiles_n;   // ceil(N / 128)
   int num_kb;    // ceil(K / 256)
   int accumulate;  // add to the values already in C instead of overwriting them
+  int dbg;
   int* status;
 };
 
@@ -75,6 +78,7 @@ __device__ __forceinline__ int skinny_owner(long long total, int g, int u) {
 template <int NP, int STAGES, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                    const __grid_constant__ CUtensorMap tmSFW, const __grid_constant__ CUtensorMap tmSFX,
                     const SkinnyParams p) {
   using Cfg = SkinnyCfg<NP, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -112,6 +116,8 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tmW);
     prefetch_tensormap(&tmX);
+    prefetch_tensormap(&tmSFW);
+    prefetch_tensormap(&tmSFX);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -124,70 +130,77 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      const uint64_t stream_policy = l2_policy_evict_first();  // weights are read once
-      const uint64_t keep_policy = l2_policy_evict_last();     // activations are re-read by every CTA
-      uint32_t stage = 0, phase = 0;
-      for (int u = u0; u < u1; ++u) {
-        const int tile = u / p.num_kb;
-        const int kb = u - tile * p.num_kb;
-        mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
+    // The whole warp walks the loop; one elected lane issues the copies.
+    const uint64_t stream_policy = l2_policy_evict_first();  // weights are read once
+    const uint64_t keep_policy = l2_policy_evict_last();     // activations are re-read by every CTA
+    uint32_t stage = 0, phase = 0;
+    int tile = u0 / p.num_kb;
+    int kb = u0 - tile * p.num_kb;
+    for (int u = u0; u < u1; ++u) {
+      mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
+      const uint32_t sW = smem_base + stage * Cfg::STAGE_BYTES;
+      const uint32_t sX = sW + Cfg::W_BYTES;
+      const uint32_t sSFW = sX + Cfg::X_BYTES;
+      const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
+      const uint32_t fb = full_bar(stage);
+      if (elect_one()) {
+        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+        tma_load_2d_hint(sW, &tmW, kb * 128, tile * 128, fb, stream_policy);
+        tma_load_2d_hint(sX, &tmX, kb * 128, 0, fb, keep_policy);
+        tma_load_2d(sSFW, &tmSFW, kb * 256, tile, fb);
+        tma_load_2d(sSFX, &tmSFX, kb * 256, 0, fb);
+      }
+      __syncwarp();
+      if (++kb == p.num_kb) { kb = 0; ++tile; }
+      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_mxf4(128, NP);
+    uint32_t stage = 0, phase = 0, sf_set = 0;
+    int seg = 0;
+    for (int u = u0; u < u1; ++seg) {
+      const int tile = u / p.num_kb;
+      const int kbs = u - tile * p.num_kb;
+      const int kbe = min(p.num_kb, kbs + (u1 - u));
+      const int as = seg & 1;
+      if (seg >= 2)
+        mbar_wait(acc_empty_bar(as), uint32_t((seg - 2) >> 1) & 1u, ctx, WB_DEV_TIMEOUT_MMA_ACC);
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + (as ? Cfg::ACC_COL1 : 0);
+      for (int kb = kbs; kb < kbe; ++kb) {
+        const uint32_t t_sfw = tmem_base + Cfg::SF_COL + sf_set * 16;
+        const uint32_t t_sfx = t_sfw + 8;
+        if (++sf_set == Cfg::SF_SETS) sf_set = 0;
+        mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
+        tc_fence_after_sync();
         const uint32_t sW = smem_base + stage * Cfg::STAGE_BYTES;
         const uint32_t sX = sW + Cfg::W_BYTES;
         const uint32_t sSFW = sX + Cfg::X_BYTES;
         const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
-        const uint32_t fb = full_bar(stage);
-        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-        tma_load_2d_hint(sW, &tmW, kb * 128, tile * 128, fb, stream_policy);
-        tma_load_2d_hint(sX, &tmX, kb * 128, 0, fb, keep_policy);
-        const int rb = min(tile, p.sfw_row_blocks - 1);
-        bulk_load(sSFW, p.sfw + (size_t(rb) * p.ka_atoms + 2 * kb) * 512, 1024, fb);
-        bulk_load(sSFX, p.sfx + size_t(2 * kb) * 512, 1024, fb);
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_mxf4(128, NP);
-      uint32_t stage = 0, phase = 0;
-      int seg = 0;
-      for (int u = u0; u < u1; ++seg) {
-        const int tile = u / p.num_kb;
-        const int kbs = u - tile * p.num_kb;
-        const int kbe = min(p.num_kb, kbs + (u1 - u));
-        const int as = seg & 1;
-        if (seg >= 2)
-          mbar_wait(acc_empty_bar(as), uint32_t((seg - 2) >> 1) & 1u, ctx, WB_DEV_TIMEOUT_MMA_ACC);
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (as ? Cfg::ACC_COL1 : 0);
-        for (int kb = kbs; kb < kbe; ++kb) {
-          mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
-          tc_fence_after_sync();
-          const uint32_t sW = smem_base + stage * Cfg::STAGE_BYTES;
-          const uint32_t sX = sW + Cfg::W_BYTES;
-          const uint32_t sSFW = sX + Cfg::X_BYTES;
-          const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
+        const uint64_t w_desc = make_desc_k_sw128(sW);
+        const uint64_t x_desc = make_desc_k_sw128(sX);
+        const uint64_t sfw_desc = make_desc_sf_atom(sSFW);
+        const uint64_t sfx_desc = make_desc_sf_atom(sSFX);
+        if (elect_one()) {
 #pragma unroll
           for (int a = 0; a < 2; ++a) {
-            utccp_sf_atom<1>(tmem_base + Cfg::SFW_COL + a * 4, make_desc_sf_atom(sSFW + a * 512));
-            utccp_sf_atom<1>(tmem_base + Cfg::SFX_COL + a * 4, make_desc_sf_atom(sSFX + a * 512));
+            utccp_sf_atom<1>(t_sfw + a * 4, sfw_desc + uint64_t(a * 32));
+            utccp_sf_atom<1>(t_sfx + a * 4, sfx_desc + uint64_t(a * 32));
           }
-          const uint64_t w_desc = make_desc_k_sw128(sW);
-          const uint64_t x_desc = make_desc_k_sw128(sX);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             mma_mxf4<1>(d_tmem, w_desc + uint64_t(k * 2), x_desc + uint64_t(k * 2),
-                        idesc_with_sf_id(idesc, (k & 1) * 2),
-                        tmem_base + Cfg::SFW_COL + (k >> 1) * 4,
-                        tmem_base + Cfg::SFX_COL + (k >> 1) * 4, (kb > kbs || k > 0) ? 1u : 0u);
+                        idesc_with_sf_id(idesc, (k & 1) * 2), t_sfw + (k >> 1) * 4, t_sfx + (k >> 1) * 4,
+                        (kb > kbs || k > 0) ? 1u : 0u);
           }
           tc_commit<1>(empty_bar(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (kb == kbe - 1) tc_commit<1>(acc_full_bar(as));
         }
-        tc_commit<1>(acc_full_bar(as));
-        u += kbe - kbs;
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
+      u += kbe - kbs;
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps 2..5
@@ -259,21 +272,44 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (*last_flag) {
           __threadfence();
           if (n < p.N) {
-            for (int m = 0; m < p.M; ++m) {
-              float acc = 0.f;
-              for (int c = c_lo; c <= c_hi; ++c) {
-                int a0, a1;
-                skinny_range(total_units, gridDim.x, c, a0, a1);
-                const int slot = 2 * c + ((a0 / p.num_kb) == tile ? 0 : 1);
-                acc += __ldcg(p.partials + (size_t(slot) * p.M + m) * 128 + nl);
+            // Partials are added in CTA order (fixed, so the sum does not depend on who arrived
+            // when), 16 output rows at a time so that the loads of one batch are all in flight.
+            auto slot_of = [&](int c) {
+              int a0, a1;
+              skinny_range(total_units, gridDim.x, c, a0, a1);
+              return 2 * c + ((a0 / p.num_kb) == tile ? 0 : 1);
+            };
+            const int ncontrib = c_hi - c_lo + 1;
+            int slots[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) slots[i] = (i < ncontrib) ? slot_of(c_lo + i) : 0;
+            for (int m0 = 0; m0 < p.M; m0 += 16) {
+              float acc[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+              for (int i = 0; i < ncontrib; ++i) {
+                const int slot = (i < 4) ? slots[i & 3] : slot_of(c_lo + i);
+                const float* src = p.partials + (size_t(slot) * p.M + m0) * 128 + nl;
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = (m0 + j < p.M) ? __ldcg(src + size_t(j) * 128) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] += v[j];
               }
-              OutT* dst = C + size_t(m) * p.ldc + n;
-              if constexpr (sizeof(OutT) == 4) {
-                if (p.accumulate) acc += *dst;
-                *dst = acc;
-              } else {
-                if (p.accumulate) acc += __bfloat162float(*dst);
-                *dst = __float2bfloat16_rn(acc);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int m = m0 + j;
+                if (m < p.M) {
+                  OutT* dst = C + size_t(m) * p.ldc + n;
+                  float r = acc[j];
+                  if constexpr (sizeof(OutT) == 4) {
+                    if (p.accumulate) r += *dst;
+                    *dst = r;
+                  } else {
+                    if (p.accumulate) r += __bfloat162float(*dst);
+                    *dst = __float2bfloat16_rn(r);
+                  }
+                }
               }
             }
           }
