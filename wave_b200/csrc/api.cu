@@ -108,10 +108,24 @@ int make_scale_map(CUtensorMap* map, const void* base, int row_blocks, int k_ato
   return WB200_OK;
 }
 
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device).
+// `done` must be a flag array owned by the caller's template instantiation: this function
+// template is instantiated per kernel TYPE, which several kernels share.
 template <typename K>
-int set_smem(K kernel, int bytes) {
-  WB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+int set_smem(K kernel, int bytes, bool* done) {
+  int dev = 0;
+  WB_CUDA(cudaGetDevice(&dev));
+  if (!done[dev]) {
+    WB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done[dev] = true;
+  }
   return WB200_OK;
+}
+
+int debug_knobs() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("WB200_DBG"); v = e ? atoi(e) : 0; }
+  return v;
 }
 
 int check_common(int M, int N, int K, const void* a, const void* as, const void* b, const void* bs, const void* c,
@@ -133,12 +147,29 @@ int check_common(int M, int N, int K, const void* a, const void* as, const void*
 // ------------------------------------------------------------------------------------------
 // tile paths
 // ------------------------------------------------------------------------------------------
-template <int CG, int BN, int STAGES, typename OutT>
+// C as a 2-D tensor of output elements for TMA stores: box = 32 columns x 32 rows, swizzled to the
+// row width of the staging buffer (64 bytes for bf16, 128 bytes for f32).
+int make_output_map(CUtensorMap* map, void* c, int M, int N, long long ldc, int esz) {
+  cuuint64_t dims[2] = {cuuint64_t(N), cuuint64_t(M)};
+  cuuint64_t strides[1] = {cuuint64_t(ldc) * esz};
+  cuuint32_t box[2] = {32u, 32u};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = g_encode(map, esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        esz == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d (M %d, N %d, ldc %lld)", int(r), M,
+                N, ldc);
+  return WB200_OK;
+}
+
+template <int CG, int BN, typename OutT>
 int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                 const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, int accumulate,
                 cudaStream_t stream) {
-  using Cfg = wb::GemmCfg<CG, BN, STAGES>;
-  CUtensorMap tmA, tmB, tmSFA, tmSFB;
+  using Cfg = wb::GemmCfg<CG, BN, int(sizeof(OutT))>;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB, tmC;
   int rc = make_operand_map(&tmA, a, M, K / 2, Cfg::BM);
   if (rc) return rc;
   rc = make_operand_map(&tmB, b, N, K / 2, Cfg::B_ROWS);
@@ -162,10 +193,18 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   const int esz = int(sizeof(OutT));
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0) ? 1 : 0;
   p.accumulate = accumulate;
-  p.dbg = getenv("WB200_DBG") ? atoi(getenv("WB200_DBG")) : 0;
+  p.tma_store = (p.vec_ok && !accumulate) ? 1 : 0;
+  if (p.tma_store) {
+    rc = make_output_map(&tmC, c, M, N, ldc, esz);
+    if (rc) return rc;
+  } else {
+    tmC = tmA;  // never dereferenced by the kernel on the direct-store path
+  }
+  p.dbg = debug_knobs();
   p.status = dev.status_ptr;
-  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, STAGES, OutT>;
-  rc = set_smem(kernel, Cfg::SMEM_BYTES);
+  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT>;
+  static bool smem_set[kMaxDevices] = {};
+  rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
   if (rc) return rc;
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   const int units = dev.sm_count / CG;  // CTAs or CTA pairs that fit at one per SM
@@ -182,30 +221,28 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, p));
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, tmC, p));
   return WB200_OK;
 }
 
-template <int CG, int BN, int STAGES>
+template <int CG, int BN>
 int launch_tile_dtype(int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as,
                       const void* b, const void* bs, void* c, long long ldc, int sfa_rb, int sfb_rb,
                       int accumulate, cudaStream_t stream) {
   if (c_dtype == WB200_F32)
-    return launch_tile<CG, BN, STAGES, float>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
-  return launch_tile<CG, BN, STAGES, __nv_bfloat16>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    return launch_tile<CG, BN, float>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+  return launch_tile<CG, BN, __nv_bfloat16>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
 }
 
 int dispatch_tile(unsigned path, bool n128, int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a,
                   const void* as, const void* b, const void* bs, void* c, long long ldc, int sfa_rb, int sfb_rb,
                   int accumulate, cudaStream_t stream) {
   if (path == WB200_PATH_TILE_2CTA) {
-    if (n128) return launch_tile_dtype<2, 128, 8>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
-    if (getenv("WB200_STAGES") && atoi(getenv("WB200_STAGES")) == 5) return launch_tile_dtype<2, 256, 5>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
-    if (getenv("WB200_STAGES") && atoi(getenv("WB200_STAGES")) == 4) return launch_tile_dtype<2, 256, 4>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
-    return launch_tile_dtype<2, 256, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    if (n128) return launch_tile_dtype<2, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    return launch_tile_dtype<2, 256>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
   }
-  if (n128) return launch_tile_dtype<1, 128, 6>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
-  return launch_tile_dtype<1, 256, 4>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+  if (n128) return launch_tile_dtype<1, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+  return launch_tile_dtype<1, 256>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -243,10 +280,11 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   p.tiles_n = (N + 127) / 128;
   p.num_kb = (K + 255) / 256;
   p.accumulate = accumulate;
-  p.dbg = getenv("WB200_DBG") ? atoi(getenv("WB200_DBG")) : 0;
+  p.dbg = debug_knobs();
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_skinny_kernel<NP, STAGES, OutT>;
-  rc = set_smem(kernel, Cfg::SMEM_BYTES);
+  static bool smem_set[kMaxDevices] = {};
+  rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
   if (rc) return rc;
   const long long units = (long long)p.tiles_n * p.num_kb;
   const int grid = int(units < dev.sm_count ? units : dev.sm_count);

@@ -27,20 +27,27 @@
 
 namespace wb {
 
-template <int CG, int BN_, int STAGES_>
+template <int CG, int BN_, int OUT_BYTES>
 struct GemmCfg {
   static constexpr int BM = 128;  // accumulator rows per CTA (tensor-memory lanes)
   static constexpr int BN = BN_;
   static constexpr int BK = 256;  // K elements per pipeline stage = one 128-byte swizzle row
-  static constexpr int STAGES = STAGES_;
   static constexpr int B_ROWS = BN / CG;  // B rows this CTA loads
   static constexpr int A_BYTES = BM * 128;
   static constexpr int B_BYTES = B_ROWS * 128;
   static constexpr int SFA_BYTES = 2 * 512;               // 128 rows x 8 K-blocks
   static constexpr int SFB_BYTES = (BN / 128) * 2 * 512;  // BN rows x 8 K-blocks
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  // Epilogue staging: each of the 4 epilogue warps owns two buffers of 32 rows x 32 columns of C,
+  // written with the TMA store swizzle (64-byte rows for bf16, 128-byte rows for f32).
+  static constexpr int CHUNK_BYTES = 32 * 32 * OUT_BYTES;
+  static constexpr int STAGING_BYTES = 4 * 2 * CHUNK_BYTES;
+  static constexpr int SMEM_LIMIT = 232448;  // largest dynamic shared memory a CTA may ask for on sm_100
+  static constexpr int STAGES_FIT = (SMEM_LIMIT - 1024 - STAGING_BYTES - 512) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
   static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
-  static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
+  static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 64;
+  static_assert(STAGES >= 3, "pipeline needs at least 3 stages");
   // tensor-memory columns
   static constexpr int TMEM_COLS = 512;
   static constexpr bool OVERLAP = (BN == 256);
@@ -70,6 +77,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int group_n;        // N tiles per raster group
   int vec_ok;         // C base and row pitch allow 16-byte stores
+  int tma_store;      // write C with TMA stores from swizzled shared memory (needs vec_ok, no accumulate)
   int accumulate;     // add to the values already in C instead of overwriting them
   int dbg;
   int* status;
@@ -148,12 +156,41 @@ __device__ __forceinline__ void store_chunk32(OutT* __restrict__ p, const uint32
   }
 }
 
-template <int CG, int BN, int STAGES, typename OutT>
+// One 16-byte store to shared memory.
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Lane `lane` holds 32 consecutive columns of output row `lane` of a 32 x 32 chunk. Write them to
+// the staging buffer in the layout a TMA store with a 32-column box reads: rows of 64 bytes with
+// the 64-byte swizzle (bf16) or rows of 128 bytes with the 128-byte swizzle (f32). The swizzle
+// also spreads the 32 lanes' 16-byte pieces over all banks.
+template <typename OutT>
+__device__ __forceinline__ void stage_chunk32(uint32_t buf, int lane, const uint32_t (&r)[32]) {
+  if constexpr (sizeof(OutT) == 4) {
+    const uint32_t row = buf + lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      st_shared_v4(row + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+  } else {
+    const uint32_t row = buf + lane * 64;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      st_shared_v4(row + ((j ^ ((lane >> 1) & 3)) << 4),
+                   pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1])),
+                   pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                   pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                   pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+  }
+}
+
+template <int CG, int BN, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
-                  const GemmParams p) {
-  using Cfg = GemmCfg<CG, BN, STAGES>;
+                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  using Cfg = GemmCfg<CG, BN, int(sizeof(OutT))>;
+  constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle; identical offset in both CTAs of a pair.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -165,12 +202,14 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const bool leader = (rank == 0);
 
   // barrier block after the stages
-  const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t staging_base = smem_base + STAGES * Cfg::STAGE_BYTES;  // 1024-byte aligned
+  const uint32_t bar_base = staging_base + Cfg::STAGING_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
   auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::NUM_BARRIERS * 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::STAGING_BYTES +
+                                                    Cfg::NUM_BARRIERS * 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   WaitCtx ctx{abort_flag, p.status};
 
@@ -195,6 +234,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     prefetch_tensormap(&tmB);
     prefetch_tensormap(&tmSFA);
     prefetch_tensormap(&tmSFB);
+    prefetch_tensormap(&tmC);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -320,6 +360,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
     const uint32_t acc_empty_leader0 = (CG == 2) ? mapa_shared(acc_empty_bar(0), 0) : 0u;
     const uint32_t acc_empty_leader1 = (CG == 2) ? mapa_shared(acc_empty_bar(1), 0) : 0u;
+    const uint32_t stg = staging_base + uint32_t(warp - 2) * 2 * Cfg::CHUNK_BYTES;
     int it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mt, nt;
@@ -327,17 +368,16 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int as = it & 1;
       mbar_wait(acc_full_bar(as), uint32_t(it >> 1) & 1u, ctx, WB_DEV_TIMEOUT_EPILOGUE);
       tc_fence_after_sync();
-      const int row = (mt * CG + int(rank)) * Cfg::BM + quad * 32 + lane;
+      const int row0 = (mt * CG + int(rank)) * Cfg::BM + quad * 32;
+      const int row = row0 + lane;
       const int col0 = nt * BN;
       const uint32_t t_acc = tmem_base + (uint32_t(quad * 32) << 16) + (as ? Cfg::ACC_COL1 : Cfg::ACC_COL0);
       auto release = [&]() {
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-          if constexpr (CG == 2) {
-            if (p.dbg & 128) mbar_arrive_cluster_relaxed(as ? acc_empty_leader1 : acc_empty_leader0);
-            else mbar_arrive_cluster(as ? acc_empty_leader1 : acc_empty_leader0);
-          }
+          // No data is published here: the tensor-memory reads have completed (wait::ld above).
+          if constexpr (CG == 2) mbar_arrive_cluster_relaxed(as ? acc_empty_leader1 : acc_empty_leader0);
           else mbar_arrive(acc_empty_bar(as));
         }
       };
@@ -358,7 +398,22 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (ci == Cfg::OVERLAP_CHUNKS - 1) release();
         }
         const int col = col0 + chunk * 32;
-        if (row < p.M && col < p.N && !(p.dbg & 32)) {
+        if (p.tma_store) {
+          // two staging buffers per warp: the store issued two chunks ago must have read its buffer
+          const uint32_t buf = stg + uint32_t(ci & 1) * Cfg::CHUNK_BYTES;
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
+          stage_chunk32<OutT>(buf, lane, r);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            // rows and columns past M, N are clipped by the store; a chunk that lies outside C
+            // altogether still commits an (empty) group, because the buffer hand-over above
+            // counts groups: one group per chunk, whether or not it stored anything
+            if (row0 < p.M && col < p.N && !(p.dbg & 32)) tma_store_2d(&tmC, buf, col, row0);
+            bulk_commit_group();
+          }
+        } else if (row < p.M && col < p.N && !(p.dbg & 32)) {
           OutT* dst = C + size_t(row) * p.ldc + col;
           const int ncols = min(32, p.N - col);
           if (p.accumulate) add_old_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);
@@ -367,6 +422,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
       if constexpr (!Cfg::OVERLAP) release();
     }
+    if (lane == 0) bulk_wait_group<0>();  // all of this warp's stores have left shared memory and landed
   }
 
   // ------------------------------------------------------------------ teardown
