@@ -73,10 +73,18 @@ class ShardedScaledGemm:
             raise ValueError(f"b_scale shard must be {(self.local_n, self.K // ops.SCALE_GROUP_SIZE)}, "
                              f"got {tuple(b_scale_shard.shape)}")
         self._b = b_shard.contiguous()
-        self._b_sf = ops.repack_scales(b_scale_shard) if self.local_n else None
+        self._b_sf = self._pack_scales(b_scale_shard) if self.local_n else None
+        self._kernel = self._build_kernel()
+
+    # The two hooks below are the only places that touch the CUDA library, so that the partitioning
+    # and gathering logic can be exercised by CPU ranks with stand-ins.
+    def _pack_scales(self, b_scale_shard: torch.Tensor):
+        return ops.repack_scales(b_scale_shard)
+
+    def _build_kernel(self):
         kernel, options = get_tagged_mxfp4_gemm((0, self.local_n, self.K), output_dtype=self.out)
         options.dynamic_symbols = ["M"]
-        self._kernel = wave_compile(options, kernel)
+        return wave_compile(options, kernel)
 
     def __call__(self, a: torch.Tensor, a_scale: torch.Tensor, gather: bool = False,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -88,23 +96,20 @@ class ShardedScaledGemm:
             if self.local_n:
                 self._kernel(a, a_scale, self._b, self._b_sf, c)
             return c
-        # Full C on every rank: each rank computes straight into its column block of the [M, N] result
-        # when all shards are equally wide, so that the all-gather needs no extra pass over C.
-        widths = {n1 - n0 for n0, n1 in self.bounds}
-        if len(widths) == 1:
-            stacked = torch.empty(self.world_size, M, self.local_n, dtype=self.out.torch_dtype, device=a.device)
-            self._kernel(a, a_scale, self._b, self._b_sf, stacked[self.rank])
-            if self.world_size > 1:
-                dist.all_gather_into_tensor(stacked.view(-1), stacked[self.rank].reshape(-1), group=self.group)
-            full = out if out is not None else torch.empty(M, self.N, dtype=self.out.torch_dtype, device=a.device)
-            full.view(M, self.world_size, self.local_n).copy_(stacked.permute(1, 0, 2))
-            return full
-        # ragged shards: gather a list
-        c = torch.empty(M, self.local_n, dtype=self.out.torch_dtype, device=a.device)
+        # Full C on every rank. Every rank computes into its slot of a [world, M, widest shard] buffer
+        # (narrower shards leave the tail columns of their slot unused), one all-gather fills the other
+        # slots, and one strided copy per shard lays the column blocks side by side.
+        wmax = max(n1 - n0 for n0, n1 in self.bounds)
+        stacked = torch.empty(self.world_size, M, wmax, dtype=self.out.torch_dtype, device=a.device)
         if self.local_n:
-            self._kernel(a, a_scale, self._b, self._b_sf, c)
-        parts = [torch.empty(M, n1 - n0, dtype=self.out.torch_dtype, device=a.device) for n0, n1 in self.bounds]
-        dist.all_gather(parts, c, group=self.group)
+            self._kernel(a, a_scale, self._b, self._b_sf, stacked[self.rank][:, : self.local_n])
+        if self.world_size > 1:
+            dist.all_gather_into_tensor(stacked.view(-1), stacked[self.rank].reshape(-1), group=self.group)
         full = out if out is not None else torch.empty(M, self.N, dtype=self.out.torch_dtype, device=a.device)
-        torch.cat(parts, dim=1, out=full)
+        if all(n1 - n0 == wmax for n0, n1 in self.bounds):
+            full.view(M, self.world_size, wmax).copy_(stacked.permute(1, 0, 2))
+        else:
+            for r, (n0, n1) in enumerate(self.bounds):
+                if n1 > n0:
+                    full[:, n0:n1].copy_(stacked[r][:, : n1 - n0])
         return full
