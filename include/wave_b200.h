@@ -93,6 +93,30 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
                      const void* b_scale_packed, void* c, int c_dtype, long long ldc, void* workspace,
                      size_t workspace_bytes, unsigned flags, void* stream);
 
+/* Allocation-free variant of the skinny (M <= 16) GEMM. No counterpart in the reference.
+ *
+ * For callers that may not allocate device memory at the point of the call and have no spare buffer
+ * to lend as a workspace: a host that gave all device memory to its own arena at start-up and
+ * forbids later cudaMalloc calls (an inference server with a fixed memory plan), a latency-critical
+ * decode loop where the implicit synchronisation of cudaMalloc / cudaFree is not acceptable, or a
+ * plug-in boundary that hands over tensors only. The stream-K partial tiles and tile counters that
+ * wb200_mxfp4_gemm takes from the caller's workspace live here in a fixed array inside the library
+ * image (about 2.5 MiB per GPU that loads the library, held until the process exits).
+ *
+ * Limits: M <= 16, N <= 65536, at most 160 SMs; larger problems are rejected with
+ * WB200_ERR_UNSUPPORTED and a message. flags: 0 or WB200_ACCUMULATE. a, b, packed scales and c are
+ * passed exactly as to wb200_mxfp4_gemm; results are bit-identical to its WB200_PATH_SKINNY path.
+ *
+ * The first call on each device looks up the array's device address (and does the library's
+ * one-time device set-up); make that call before starting any stream capture. The call itself
+ * calls no cudaMalloc, cudaFree or other allocating routine. All calls on a device share the one
+ * array (the tile counters are cleared on the stream at the start of every call): two calls
+ * whose kernels can overlap on the GPU - different streams without an ordering between them -
+ * race on it and produce wrong results; serialise them. */
+int wb200_mxfp4_gemm_skinny_noalloc(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,
+                                    const void* b_scale_packed, void* c, int c_dtype, long long ldc, unsigned flags,
+                                    void* stream);
+
 /* Grouped (per-expert) GEMM: group g computes c[row_offsets[g] : row_offsets[g+1], :] =
  * a[rows of g] * b_g^T with its own weight matrix b_ptrs[g] ([N, K/2]) and packed scales
  * b_scale_ptrs[g]. a is the gathered activation matrix [total_rows, K/2]; a_scale_packed is

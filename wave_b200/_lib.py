@@ -41,6 +41,7 @@ EXPORTED_SYMBOLS = (
     "wb200_mxfp4_gemm_workspace_bytes",
     "wb200_workspace_init",
     "wb200_mxfp4_gemm",
+    "wb200_mxfp4_gemm_skinny_noalloc",
     "wb200_mxfp4_grouped_gemm",
 )
 
@@ -92,6 +93,9 @@ def load() -> ctypes.CDLL:
     lib.wb200_mxfp4_gemm.restype = c_int
     lib.wb200_mxfp4_gemm.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_ll, c_void_p, c_size_t, c_uint, c_void_p]
+    lib.wb200_mxfp4_gemm_skinny_noalloc.restype = c_int
+    lib.wb200_mxfp4_gemm_skinny_noalloc.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                    c_int, c_ll, c_uint, c_void_p]
     lib.wb200_mxfp4_grouped_gemm.restype = c_int
     lib.wb200_mxfp4_grouped_gemm.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, c_int,
                                              c_void_p, c_void_p, ctypes.POINTER(c_void_p),

@@ -302,6 +302,34 @@ int dispatch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, c
   return launch_skinny<128, 6, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
 }
 
+// ------------------------------------------------------------------------------------------
+// allocation-free skinny entry point: its scratch lives in the library image
+// ------------------------------------------------------------------------------------------
+constexpr int kNoAllocMaxM = 16;
+constexpr int kNoAllocMaxN = 65536;
+constexpr int kNoAllocMaxSMs = 160;
+// Same layout as the caller-provided workspace of the skinny path: tile counters, then two f32
+// partial tiles (M x 128) per CTA.
+constexpr size_t kNoAllocScratchBytes = kCounterBytes + size_t(2) * kNoAllocMaxSMs * kNoAllocMaxM * 128 * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+// In host code the name above is only a handle for the runtime, not a device address; the address
+// is asked for once per device, with that device current.
+void* g_noalloc_ptr[kMaxDevices] = {};
+
+int noalloc_scratch(void** out) {
+  int dev = 0;
+  WB_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_noalloc_ptr[dev]) {
+    void* ptr = nullptr;
+    WB_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    if (!ptr) return fail(WB200_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the scratch array");
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return WB200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -417,6 +445,37 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   }
   return dispatch_tile(path, n128, c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc,
                        wb::sf_row_blocks(M), wb::sf_row_blocks(N), accumulate, s);
+}
+
+int wb200_mxfp4_gemm_skinny_noalloc(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,
+                                    const void* b_scale_packed, void* c, int c_dtype, long long ldc, unsigned flags,
+                                    void* stream) {
+  int rc = check_common(M, N, K, a, a_scale_packed, b, b_scale_packed, c, c_dtype, ldc);
+  if (rc) return rc;
+  if ((flags & ~WB200_ACCUMULATE) != 0)
+    return fail(WB200_ERR_INVALID_ARG, "skinny_noalloc takes no flag other than WB200_ACCUMULATE (got %#x)", flags);
+  if (M > kNoAllocMaxM)
+    return fail(WB200_ERR_UNSUPPORTED, "skinny_noalloc handles M <= %d (got %d): its built-in scratch array is sized for that; "
+                "use wb200_mxfp4_gemm with a workspace", kNoAllocMaxM, M);
+  if (N > kNoAllocMaxN)
+    return fail(WB200_ERR_UNSUPPORTED, "skinny_noalloc handles N <= %d (got %d): its built-in scratch array is sized for that; "
+                "use wb200_mxfp4_gemm with a workspace", kNoAllocMaxN, N);
+  DeviceInfo* dev;
+  rc = get_device(&dev);
+  if (rc) return rc;
+  if (dev->sm_count > kNoAllocMaxSMs)
+    return fail(WB200_ERR_UNSUPPORTED, "skinny_noalloc is sized for at most %d SMs (device has %d)", kNoAllocMaxSMs, dev->sm_count);
+  void* scratch = nullptr;
+  rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left; the tile counters must start at zero.
+  const size_t counter_bytes = size_t((N + 127) / 128) * sizeof(unsigned int);
+  WB_CUDA(cudaMemsetAsync(scratch, 0, counter_bytes, s));
+  const int accumulate = (flags & WB200_ACCUMULATE) ? 1 : 0;
+  if (c_dtype == WB200_F32)
+    return dispatch_skinny<float>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, scratch, accumulate, s);
+  return dispatch_skinny<__nv_bfloat16>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, scratch, accumulate, s);
 }
 
 int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* row_block_offsets, int N, int K,
