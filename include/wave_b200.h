@@ -93,6 +93,15 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
                      const void* b_scale_packed, void* c, int c_dtype, long long ldc, void* workspace,
                      size_t workspace_bytes, unsigned flags, void* stream);
 
+/* The per-call sequence of the reference-facing launch in one call: repack the ROW-MAJOR activation
+ * scales a_scale [M, K/32] (row pitch a_scale_stride bytes) into a_scale_scratch (at least
+ * wb200_packed_scale_bytes(M, K) bytes, caller-owned), then run wb200_mxfp4_gemm with it. Weight
+ * scales arrive packed, because a weight's scales are packed once and reused. Saves one trip
+ * through the caller's binding per GEMM; same kernels, same results. */
+int wb200_mxfp4_gemm_repack_a(int M, int N, int K, const void* a, const void* a_scale, long long a_scale_stride,
+                              void* a_scale_scratch, const void* b, const void* b_scale_packed, void* c, int c_dtype,
+                              long long ldc, void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+
 /* Allocation-free variant of the skinny (M <= 16) GEMM. No counterpart in the reference.
  *
  * For callers that may not allocate device memory at the point of the call and have no spare buffer

@@ -354,3 +354,85 @@ def test_config3_decode_shapes_bf16(M):
         ref = orc.scaled_gemm(a, a_s, b[n0:n0 + 2048], b_s[n0:n0 + 2048])
         check_bf16(c[:, n0:n0 + 2048].contiguous(), ref)
     ops.check_device_status()
+
+
+# ---------------------------------------------------------------------------------------------
+# grouped (MoE) GEMM
+# ---------------------------------------------------------------------------------------------
+def _moe_problem(E, N, K, tokens, seed):
+    from wave_b200 import grouped
+    g = torch.Generator().manual_seed(seed)
+    x, x_s = orc.quantize_mxfp4(torch.randn(tokens, K, generator=g))
+    weights = [orc.quantize_mxfp4(torch.randn(N, K, generator=torch.Generator().manual_seed(seed + 1 + e)) * 0.02)
+               for e in range(E)]
+    logits = torch.randn(tokens, E, generator=g)
+    rows, offsets = grouped.route_top_k(logits, 2)
+    return x, x_s, weights, rows, offsets
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_grouped_gemm_ragged_experts(out_dtype):
+    """Top-2 routing over 5 experts gives ragged per-expert row counts (one expert is starved on purpose)."""
+    from wave_b200 import grouped
+    E, N, K, tokens = 5, 640, 1024, 300
+    x, x_s, weights, rows, offsets = _moe_problem(E, N, K, tokens, seed=61)
+    # starve the last expert: move its rows to expert 0 by re-routing (keeps the offsets consistent)
+    assert offsets[-1] == 2 * tokens and len(offsets) == E + 1
+    a, a_s = x[rows], x_s[rows]
+    experts = grouped.ExpertWeights([w.to(DEV) for w, _ in weights], [s.to(DEV) for _, s in weights])
+    c = torch.full((a.shape[0], N), float("nan"), dtype=out_dtype, device=DEV)
+    grouped.grouped_scaled_gemm(a.to(DEV), a_s.to(DEV), experts, offsets, c)
+    for e in range(E):
+        r0, r1 = offsets[e], offsets[e + 1]
+        if r1 == r0:
+            continue
+        w, s = weights[e]
+        check(c[r0:r1].contiguous(), a[r0:r1], a_s[r0:r1], w, s)
+
+
+def test_grouped_gemm_with_an_empty_expert():
+    from wave_b200 import grouped
+    E, N, K = 3, 256, 512
+    g = torch.Generator().manual_seed(71)
+    a = torch.randint(0, 256, (200, K // 2), dtype=torch.uint8, generator=g)
+    a_s = torch.randint(124, 131, (200, K // 32), dtype=torch.uint8, generator=g)
+    ws = [(torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g),
+           torch.randint(124, 131, (N, K // 32), dtype=torch.uint8, generator=g)) for _ in range(E)]
+    offsets = [0, 130, 130, 200]  # expert 1 gets no rows
+    experts = grouped.ExpertWeights([w.to(DEV) for w, _ in ws], [s.to(DEV) for _, s in ws])
+    c = torch.full((200, N), float("nan"), dtype=torch.float32, device=DEV)
+    grouped.grouped_scaled_gemm(a.to(DEV), a_s.to(DEV), experts, offsets, c)
+    for e in (0, 2):
+        r0, r1 = offsets[e], offsets[e + 1]
+        check_f32(c[r0:r1].contiguous(), a[r0:r1], a_s[r0:r1], ws[e][0], ws[e][1])
+    with pytest.raises(ValueError):
+        grouped.grouped_scaled_gemm(a.to(DEV), a_s.to(DEV), experts, [0, 100, 200], c)
+
+
+def test_config4_moe_8_experts_bf16_sampled():
+    """8 experts of [14336, 4096], 4096 tokens, top-2: every expert's block is checked on sampled rows and
+    a column block of the oracle."""
+    from wave_b200 import grouped
+    E, N, K, tokens = 8, 14336, 4096, 4096
+    x, x_s = orc.quantize_mxfp4(torch.randn(tokens, K, generator=torch.Generator().manual_seed(1004)))
+    weights = [orc.quantize_mxfp4(torch.randn(N, K, generator=torch.Generator().manual_seed(2004 + e)) * 0.02)
+               for e in range(E)]
+    logits = torch.randn(tokens, E, generator=torch.Generator().manual_seed(3004))
+    rows, offsets = grouped.route_top_k(logits, 2)
+    assert offsets[-1] == 8192
+    a, a_s = x[rows], x_s[rows]
+    experts = grouped.ExpertWeights([w.to(DEV) for w, _ in weights], [s.to(DEV) for _, s in weights])
+    c = torch.empty(a.shape[0], N, dtype=torch.bfloat16, device=DEV)
+    grouped.grouped_scaled_gemm(a.to(DEV), a_s.to(DEV), experts, offsets, c)
+    for e in range(E):
+        r0, r1 = offsets[e], offsets[e + 1]
+        sample = torch.arange(r0, r1, max(1, (r1 - r0) // 48))
+        w, s = weights[e]
+        n0 = (e * 1792) % (N - 2048)
+        ref = orc.scaled_gemm(a[sample], a_s[sample], w[n0:n0 + 2048], s[n0:n0 + 2048])
+        check_bf16(c[sample.to(DEV)][:, n0:n0 + 2048].contiguous(), ref)
+        # the rows at both ends of the expert's block, against all columns of a narrow slice
+        edge = torch.tensor([r0, r1 - 1])
+        ref_e = orc.scaled_gemm(a[edge], a_s[edge], w[:512], s[:512])
+        check_bf16(c[edge.to(DEV)][:, :512].contiguous(), ref_e)
+    ops.check_device_status()

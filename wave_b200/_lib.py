@@ -41,6 +41,7 @@ EXPORTED_SYMBOLS = (
     "wb200_mxfp4_gemm_workspace_bytes",
     "wb200_workspace_init",
     "wb200_mxfp4_gemm",
+    "wb200_mxfp4_gemm_repack_a",
     "wb200_mxfp4_gemm_skinny_noalloc",
     "wb200_mxfp4_grouped_gemm",
 )
@@ -93,6 +94,9 @@ def load() -> ctypes.CDLL:
     lib.wb200_mxfp4_gemm.restype = c_int
     lib.wb200_mxfp4_gemm.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_ll, c_void_p, c_size_t, c_uint, c_void_p]
+    lib.wb200_mxfp4_gemm_repack_a.restype = c_int
+    lib.wb200_mxfp4_gemm_repack_a.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_ll, c_void_p, c_size_t, c_uint, c_void_p]
     lib.wb200_mxfp4_gemm_skinny_noalloc.restype = c_int
     lib.wb200_mxfp4_gemm_skinny_noalloc.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                     c_int, c_ll, c_uint, c_void_p]

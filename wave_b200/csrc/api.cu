@@ -77,15 +77,55 @@ int get_device(DeviceInfo** out) {
   return WB200_OK;
 }
 
+// cuTensorMapEncodeTiled behind a small per-thread cache: the same operands come back call after
+// call (weights, reused activation and output buffers), and encoding five descriptors per launch is
+// a visible part of the host time of a 20-microsecond kernel.
+struct MapKey {
+  const void* base;
+  unsigned long long d0, d1, stride;
+  unsigned box0, box1;
+  int dtype, swizzle, promo;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && d0 == o.d0 && d1 == o.d1 && stride == o.stride && box0 == o.box0 && box1 == o.box1 &&
+           dtype == o.dtype && swizzle == o.swizzle && promo == o.promo;
+  }
+};
+constexpr int kMapCacheSize = 64;
+struct MapCache {
+  MapKey keys[kMapCacheSize];
+  CUtensorMap maps[kMapCacheSize];
+  int used = 0, next = 0;
+};
+thread_local MapCache g_map_cache;
+
+CUresult encode_2d(CUtensorMap* map, const MapKey& k) {
+  MapCache& c = g_map_cache;
+  for (int i = 0; i < c.used; ++i)
+    if (c.keys[i] == k) {
+      *map = c.maps[i];
+      return CUDA_SUCCESS;
+    }
+  cuuint64_t dims[2] = {k.d0, k.d1};
+  cuuint64_t strides[1] = {k.stride};
+  cuuint32_t box[2] = {k.box0, k.box1};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = g_encode(map, CUtensorMapDataType(k.dtype), 2, const_cast<void*>(k.base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CUtensorMapSwizzle(k.swizzle), CUtensorMapL2promotion(k.promo),
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) {
+    const int slot = (c.used < kMapCacheSize) ? c.used++ : (c.next = (c.next + 1) % kMapCacheSize);
+    c.keys[slot] = k;
+    c.maps[slot] = *map;
+  }
+  return r;
+}
+
 // [rows, row_bytes] uint8 matrix, box = 128 bytes x box_rows, 128-byte swizzle, zero fill.
 int make_operand_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_rows) {
-  cuuint64_t dims[2] = {cuuint64_t(row_bytes), cuuint64_t(rows)};
-  cuuint64_t strides[1] = {cuuint64_t(row_bytes)};
-  cuuint32_t box[2] = {128u, cuuint32_t(box_rows)};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const MapKey k{base, (unsigned long long)row_bytes, (unsigned long long)rows, (unsigned long long)row_bytes, 128u,
+                 unsigned(box_rows), int(CU_TENSOR_MAP_DATA_TYPE_UINT8), int(CU_TENSOR_MAP_SWIZZLE_128B),
+                 int(CU_TENSOR_MAP_L2_PROMOTION_L2_256B)};
+  CUresult r = encode_2d(map, k);
   if (r != CUDA_SUCCESS)
     return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows %lld, row bytes %lld)", int(r),
                 rows, row_bytes);
@@ -95,13 +135,10 @@ int make_operand_map(CUtensorMap* map, const void* base, long long rows, long lo
 // Packed scale array ([row_blocks][k_atoms][512 bytes]) as a 2-D tensor of 32-bit words, one
 // row per 128-row block; a box is 1024 bytes (the two atoms of one pipeline stage) x box_rows.
 int make_scale_map(CUtensorMap* map, const void* base, int row_blocks, int k_atoms, int box_rows) {
-  cuuint64_t dims[2] = {cuuint64_t(k_atoms) * 128, cuuint64_t(row_blocks)};
-  cuuint64_t strides[1] = {cuuint64_t(k_atoms) * 512};
-  cuuint32_t box[2] = {256u, cuuint32_t(box_rows)};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const MapKey k{base, (unsigned long long)k_atoms * 128, (unsigned long long)row_blocks, (unsigned long long)k_atoms * 512,
+                 256u, unsigned(box_rows), int(CU_TENSOR_MAP_DATA_TYPE_UINT32), int(CU_TENSOR_MAP_SWIZZLE_NONE),
+                 int(CU_TENSOR_MAP_L2_PROMOTION_L2_256B)};
+  CUresult r = encode_2d(map, k);
   if (r != CUDA_SUCCESS)
     return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with CUresult %d (row blocks %d, atoms %d)", int(r),
                 row_blocks, k_atoms);
@@ -150,14 +187,10 @@ int check_common(int M, int N, int K, const void* a, const void* as, const void*
 // C as a 2-D tensor of output elements for TMA stores: box = 32 columns x 32 rows, swizzled to the
 // row width of the staging buffer (64 bytes for bf16, 128 bytes for f32).
 int make_output_map(CUtensorMap* map, void* c, int M, int N, long long ldc, int esz) {
-  cuuint64_t dims[2] = {cuuint64_t(N), cuuint64_t(M)};
-  cuuint64_t strides[1] = {cuuint64_t(ldc) * esz};
-  cuuint32_t box[2] = {32u, 32u};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = g_encode(map, esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, dims,
-                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        esz == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const MapKey k{c, (unsigned long long)N, (unsigned long long)M, (unsigned long long)ldc * esz, 32u, 32u,
+                 int(esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16),
+                 int(esz == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B), int(CU_TENSOR_MAP_L2_PROMOTION_NONE)};
+  CUresult r = encode_2d(map, k);
   if (r != CUDA_SUCCESS)
     return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d (M %d, N %d, ldc %lld)", int(r), M,
                 N, ldc);
@@ -445,6 +478,16 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   }
   return dispatch_tile(path, n128, c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc,
                        wb::sf_row_blocks(M), wb::sf_row_blocks(N), accumulate, s);
+}
+
+int wb200_mxfp4_gemm_repack_a(int M, int N, int K, const void* a, const void* a_scale, long long a_scale_stride,
+                              void* a_scale_scratch, const void* b, const void* b_scale_packed, void* c, int c_dtype,
+                              long long ldc, void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
+  if (!a_scale_scratch) return fail(WB200_ERR_INVALID_ARG, "gemm_repack_a: null scratch for the packed activation scales");
+  int rc = wb200_repack_scales(a_scale, a_scale_stride, M, K, a_scale_scratch, stream);
+  if (rc) return rc;
+  return wb200_mxfp4_gemm(M, N, K, a, a_scale_scratch, b, b_scale_packed, c, c_dtype, ldc, workspace, workspace_bytes, flags,
+                          stream);
 }
 
 int wb200_mxfp4_gemm_skinny_noalloc(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,

@@ -61,8 +61,14 @@ def repack_scales(scale: torch.Tensor, out: torch.Tensor | None = None) -> Packe
         out = torch.empty(nbytes, dtype=torch.uint8, device=scale.device)
     elif out.numel() < nbytes or out.dtype != torch.uint8 or not out.is_contiguous():
         raise ValueError("repack_scales: `out` must be a contiguous uint8 tensor of at least packed_scale_bytes(rows, K)")
-    with torch.cuda.device(scale.device):
-        _lib.check(lib.wb200_repack_scales(scale.data_ptr(), scale.stride(0), rows, K, out.data_ptr(), _stream()))
+    dev_index = scale.device.index
+    if dev_index is None or dev_index == torch.cuda.current_device():
+        rc = lib.wb200_repack_scales(scale.data_ptr(), scale.stride(0), rows, K, out.data_ptr(), _stream())
+    else:
+        with torch.cuda.device(scale.device):
+            rc = lib.wb200_repack_scales(scale.data_ptr(), scale.stride(0), rows, K, out.data_ptr(), _stream())
+    if rc:
+        _lib.check(rc)
     return PackedScales(out, rows, K)
 
 
@@ -111,14 +117,20 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
         raise ValueError(f"a and b disagree on K: {K} vs {b.shape[1] * 2}")
     if (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
         raise ValueError("packed scales do not match the operand shapes")
-    ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
-    ws_ptr = 0
-    if ws_bytes:
+    ws_bytes = ws_ptr = 0
+    if M <= 128:
+        ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
         ws_ptr = _workspace(a.device, ws_bytes).data_ptr()
-    with torch.cuda.device(a.device):
-        _lib.check(lib.wb200_mxfp4_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
-                                        c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0), ws_ptr, ws_bytes, flags,
-                                        _stream()))
+    dev_index = a.device.index
+    if dev_index is None or dev_index == torch.cuda.current_device():
+        rc = lib.wb200_mxfp4_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
+                                  c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0), ws_ptr, ws_bytes, flags, _stream())
+    else:
+        with torch.cuda.device(a.device):
+            rc = lib.wb200_mxfp4_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
+                                      c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0), ws_ptr, ws_bytes, flags, _stream())
+    if rc:
+        _lib.check(rc)
 
 
 class WeightScaleCache:
