@@ -36,7 +36,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu
 # capture (profiles/), scaled to the full workload where the capture ran a smaller case.
-NCU_TRAFFIC_BYTES = {"c2": None, "c3": None}
+NCU_TRAFFIC_BYTES = {"c2": 208.6e6, "c3": 129.5e6}
 
 WORKLOADS = {
     "c2": dict(M=8192, N=8192, K=8192, std_b=1.0, seed_a=1002, seed_b=2002,
@@ -119,6 +119,8 @@ def cpu_reference_run(w, steps, warmup):
     """The reference's CPU path (torch oracle port) on a bounded slice: the first `rows` rows of a
     against all of b. Returns (TFLOP/s, seconds per step, description, threads)."""
     from oracle import mxfp4_oracle as orc
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
+    torch.set_num_threads(os.cpu_count() or 1)
     rows = min(w["M"], 512)
     a, a_s, b, b_s = make_operands(w)
     a, a_s = a[:rows], a_s[:rows]
