@@ -74,6 +74,13 @@ size_t wb200_packed_scale_bytes(int rows, int K);
 int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int K, void* dst,
                         void* stream);
 
+/* Grouped form for the per-expert GEMM: rows [row_offsets[g], row_offsets[g+1]) of src are group g;
+ * its packed scales start at 128-row block row_block_offsets[g] of dst (each group on a block boundary,
+ * row_block_offsets[g+1] - row_block_offsets[g] >= ceil(rows of g / 128)); one launch for up to 32
+ * groups. Offsets are HOST arrays. dst must hold row_block_offsets[num_groups] * wb200_packed_scale_bytes(128, K). */
+int wb200_repack_scales_grouped(const void* src, long long src_row_stride, int num_groups, const int* row_offsets,
+                                const int* row_block_offsets, int K, void* dst, void* stream);
+
 /* Test aid: out[r, k] = E2M1(q) * 2^(scale - 127) as f32, the dequantised operand of
  * mxfp4_to_f32 / e8m0_to_f32 (wave_lang/kernel/wave/utils/mxfp_utils.py:60-95). */
 int wb200_mxfp4_dequant(const void* q, const void* scale, int rows, int K, float* out, void* stream);

@@ -436,3 +436,27 @@ def test_config4_moe_8_experts_bf16_sampled():
         ref_e = orc.scaled_gemm(a[edge], a_s[edge], w[:512], s[:512])
         check_bf16(c[edge.to(DEV)][:, :512].contiguous(), ref_e)
     ops.check_device_status()
+
+
+def test_grouped_repack_matches_per_group_repack():
+    import ctypes
+    lib = _lib.load()
+    K = 1184  # 37 K-blocks: ragged along K too
+    offsets = [0, 130, 130, 131, 400, 1000]
+    s = torch.randint(0, 256, (offsets[-1], K // 32), dtype=torch.uint8)
+    blocks = [0]
+    for g in range(len(offsets) - 1):
+        blocks.append(blocks[-1] + (offsets[g + 1] - offsets[g] + 127) // 128)
+    per_block = ops.packed_scale_bytes(128, K)
+    out = torch.zeros(blocks[-1] * per_block, dtype=torch.uint8, device=DEV)
+    E = len(offsets) - 1
+    sd = s.to(DEV)
+    _lib.check(lib.wb200_repack_scales_grouped(sd.data_ptr(), sd.stride(0), E, (ctypes.c_int * (E + 1))(*offsets),
+                                               (ctypes.c_int * (E + 1))(*blocks), K, out.data_ptr(),
+                                               torch.cuda.current_stream().cuda_stream))
+    got = out.cpu()
+    for g in range(E):
+        r0, r1 = offsets[g], offsets[g + 1]
+        if r1 > r0:
+            exp = orc.pack_scales(s[r0:r1])
+            assert torch.equal(got[blocks[g] * per_block: blocks[g] * per_block + exp.numel()], exp), g

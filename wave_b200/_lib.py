@@ -37,6 +37,7 @@ EXPORTED_SYMBOLS = (
     "wb200_check_device_status",
     "wb200_packed_scale_bytes",
     "wb200_repack_scales",
+    "wb200_repack_scales_grouped",
     "wb200_mxfp4_dequant",
     "wb200_mxfp4_gemm_workspace_bytes",
     "wb200_workspace_init",
@@ -85,6 +86,9 @@ def load() -> ctypes.CDLL:
     lib.wb200_packed_scale_bytes.argtypes = [c_int, c_int]
     lib.wb200_repack_scales.restype = c_int
     lib.wb200_repack_scales.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p]
+    lib.wb200_repack_scales_grouped.restype = c_int
+    lib.wb200_repack_scales_grouped.argtypes = [c_void_p, c_ll, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int,
+                                                c_void_p, c_void_p]
     lib.wb200_mxfp4_dequant.restype = c_int
     lib.wb200_mxfp4_dequant.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
     lib.wb200_mxfp4_gemm_workspace_bytes.restype = c_size_t

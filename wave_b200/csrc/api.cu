@@ -202,14 +202,16 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
                 const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, int accumulate,
                 cudaStream_t stream) {
   using Cfg = wb::GemmCfg<CG, BN, int(sizeof(OutT))>;
-  CUtensorMap tmA, tmB, tmSFA, tmSFB, tmC;
-  int rc = make_operand_map(&tmA, a, M, K / 2, Cfg::BM);
+  wb::PlainMaps maps;
+  CUtensorMap& tmA = maps.m[0];
+  CUtensorMap& tmC = maps.m[4];
+  int rc = make_operand_map(&maps.m[0], a, M, K / 2, Cfg::BM);
   if (rc) return rc;
-  rc = make_operand_map(&tmB, b, N, K / 2, Cfg::B_ROWS);
+  rc = make_operand_map(&maps.m[1], b, N, K / 2, Cfg::B_ROWS);
   if (rc) return rc;
-  rc = make_scale_map(&tmSFA, as, sfa_row_blocks, wb::sf_k_atoms(K), 1);
+  rc = make_scale_map(&maps.m[2], as, sfa_row_blocks, wb::sf_k_atoms(K), 1);
   if (rc) return rc;
-  rc = make_scale_map(&tmSFB, bs, sfb_row_blocks, wb::sf_k_atoms(K), BN / 128);
+  rc = make_scale_map(&maps.m[3], bs, sfb_row_blocks, wb::sf_k_atoms(K), BN / 128);
   if (rc) return rc;
   wb::GemmParams p;
   p.sfa = static_cast<const uint8_t*>(as);
@@ -235,7 +237,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   }
   p.dbg = debug_knobs();
   p.status = dev.status_ptr;
-  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT>;
+  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT, wb::PlainMaps>;
   static bool smem_set[kMaxDevices] = {};
   rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
   if (rc) return rc;
@@ -254,7 +256,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, tmC, p));
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps, p));
   return WB200_OK;
 }
 
@@ -276,6 +278,75 @@ int dispatch_tile(unsigned path, bool n128, int c_dtype, const DeviceInfo& dev, 
   }
   if (n128) return launch_tile_dtype<1, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
   return launch_tile_dtype<1, 256>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+}
+
+// One persistent launch over the tiles of all groups (CTA pairs, 256 x 256 tiles, TMA-store epilogue).
+template <typename OutT>
+int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets, const int* row_block_offsets, int N, int K,
+                   const void* a, const void* a_sf, const void* const* b_ptrs, const void* const* b_sf_ptrs, void* c,
+                   long long ldc, cudaStream_t stream) {
+  constexpr int CG = 2, BN = 256;
+  using Cfg = wb::GemmCfg<CG, BN, int(sizeof(OutT))>;
+  static wb::GroupedMaps maps;  // ~21 KB: too large for comfort on the stack; guarded by the mutex below
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  const int esz = int(sizeof(OutT));
+  const int k_atoms = wb::sf_k_atoms(K);
+  const size_t atom_row_bytes = size_t(k_atoms) * 512;
+  const int tiles_n = (N + BN - 1) / BN;
+  maps.num_groups = num_groups;
+  maps.tile_start[0] = 0;
+  for (int g = 0; g < num_groups; ++g) {
+    const int r0 = row_offsets[g], Mg = row_offsets[g + 1] - r0;
+    maps.rows[g] = Mg;
+    maps.tile_start[g + 1] = maps.tile_start[g] + ((Mg + Cfg::BM * CG - 1) / (Cfg::BM * CG)) * tiles_n;
+    if (Mg == 0) continue;
+    const uint8_t* ag = static_cast<const uint8_t*>(a) + size_t(r0) * (K / 2);
+    const uint8_t* asg = static_cast<const uint8_t*>(a_sf) + size_t(row_block_offsets[g]) * atom_row_bytes;
+    uint8_t* cg = static_cast<uint8_t*>(c) + size_t(r0) * ldc * esz;
+    int rc = check_common(Mg, N, K, ag, asg, b_ptrs[g], b_sf_ptrs[g], cg, esz == 4 ? WB200_F32 : WB200_BF16, ldc);
+    if (rc) return rc;
+    CUtensorMap* m = &maps.m[g * 5];
+    if ((rc = make_operand_map(m + 0, ag, Mg, K / 2, Cfg::BM))) return rc;
+    if ((rc = make_operand_map(m + 1, b_ptrs[g], N, K / 2, Cfg::B_ROWS))) return rc;
+    if ((rc = make_scale_map(m + 2, asg, wb::sf_row_blocks(Mg), k_atoms, 1))) return rc;
+    if ((rc = make_scale_map(m + 3, b_sf_ptrs[g], wb::sf_row_blocks(N), k_atoms, BN / 128))) return rc;
+    if ((rc = make_output_map(m + 4, cg, Mg, N, ldc, esz))) return rc;
+  }
+  const int tiles = maps.tile_start[num_groups];
+  if (tiles == 0) return WB200_OK;
+  wb::GemmParams p = {};
+  p.c = c;
+  p.M = row_offsets[num_groups]; p.N = N; p.K = K;
+  p.ldc = int(ldc);
+  p.ka_atoms = k_atoms;
+  p.tiles_m = 0;
+  p.tiles_n = tiles_n;
+  p.group_n = 16;
+  p.vec_ok = 1;
+  p.tma_store = 1;
+  p.accumulate = 0;
+  p.dbg = debug_knobs();
+  p.status = dev.status_ptr;
+  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT, wb::GroupedMaps>;
+  static bool smem_set[kMaxDevices] = {};
+  int rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
+  if (rc) return rc;
+  const int units = dev.sm_count / CG;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((tiles < units ? tiles : units) * CG, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps, p));
+  return WB200_OK;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -410,6 +481,39 @@ int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int
   return WB200_OK;
 }
 
+int wb200_repack_scales_grouped(const void* src, long long src_row_stride, int num_groups, const int* row_offsets,
+                                const int* row_block_offsets, int K, void* dst, void* stream) {
+  if (num_groups <= 0 || num_groups > wb::kMaxRepackGroups || !row_offsets || !row_block_offsets)
+    return fail(WB200_ERR_INVALID_ARG, "repack_scales_grouped: 1..%d groups with offset arrays (got %d)", wb::kMaxRepackGroups,
+                num_groups);
+  if (K <= 0 || K % 32 != 0) return fail(WB200_ERR_INVALID_ARG, "repack_scales_grouped: K = %d must be a positive multiple of 32", K);
+  if (!src || !dst) return fail(WB200_ERR_INVALID_ARG, "repack_scales_grouped: null pointer");
+  if (src_row_stride < K / 32) return fail(WB200_ERR_INVALID_ARG, "repack_scales_grouped: row stride %lld < K/32", src_row_stride);
+  if (reinterpret_cast<uintptr_t>(dst) & 15) return fail(WB200_ERR_ALIGNMENT, "repack_scales_grouped: dst must be 16-byte aligned");
+  wb::RepackGroups tab;
+  tab.num_groups = num_groups;
+  for (int g = 0; g <= num_groups; ++g) {
+    tab.row_start[g] = row_offsets[g];
+    tab.block_start[g] = row_block_offsets[g];
+  }
+  for (int g = 0; g < num_groups; ++g) {
+    const int rows = row_offsets[g + 1] - row_offsets[g], blocks = row_block_offsets[g + 1] - row_block_offsets[g];
+    if (rows < 0 || blocks < (rows + 127) / 128)
+      return fail(WB200_ERR_INVALID_ARG, "repack_scales_grouped: group %d has %d rows but %d 128-row blocks", g, rows, blocks);
+  }
+  const int total_blocks = row_block_offsets[num_groups] - row_block_offsets[0];
+  if (total_blocks == 0) return WB200_OK;
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  const int k_atoms = wb::sf_k_atoms(K);
+  dim3 grid((k_atoms + 7) / 8, total_blocks);
+  wb::repack_scales_grouped_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), src_row_stride, tab, K / 32, k_atoms, static_cast<uint8_t*>(dst));
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
 int wb200_mxfp4_dequant(const void* q, const void* scale, int rows, int K, float* out, void* stream) {
   if (rows <= 0 || K <= 0 || K % 32 != 0)
     return fail(WB200_ERR_INVALID_ARG, "dequant: rows = %d, K = %d (K must be a positive multiple of 32)", rows, K);
@@ -530,7 +634,20 @@ int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* 
   DeviceInfo* dev;
   int rc = get_device(&dev);
   if (rc) return rc;
+  if (c_dtype != WB200_F32 && c_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "unknown output dtype %d", c_dtype);
   const int esz = (c_dtype == WB200_F32) ? 4 : 2;
+  for (int g = 0; g < num_groups; ++g)
+    if (row_offsets[g + 1] < row_offsets[g]) return fail(WB200_ERR_INVALID_ARG, "grouped gemm: row offsets decrease at group %d", g);
+  // One persistent launch when the groups fit the kernel's descriptor table and c can take TMA stores;
+  // otherwise one launch per group.
+  if (num_groups <= wb::kMaxGroups && c && (reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0 && ldc >= N &&
+      !(debug_knobs() & 512)) {
+    if (c_dtype == WB200_F32)
+      return launch_grouped<float>(*dev, num_groups, row_offsets, row_block_offsets, N, K, a, a_scale_packed, b_ptrs,
+                                   b_scale_ptrs, c, ldc, static_cast<cudaStream_t>(stream));
+    return launch_grouped<__nv_bfloat16>(*dev, num_groups, row_offsets, row_block_offsets, N, K, a, a_scale_packed, b_ptrs,
+                                         b_scale_ptrs, c, ldc, static_cast<cudaStream_t>(stream));
+  }
   const size_t atom_row_bytes = size_t(wb::sf_k_atoms(K)) * 512;
   for (int g = 0; g < num_groups; ++g) {
     const int r0 = row_offsets[g], r1 = row_offsets[g + 1];

@@ -83,6 +83,24 @@ struct GemmParams {
   int* status;
 };
 
+// The tensor maps of one launch, passed by value as a kernel parameter. Index: 0 = a, 1 = b,
+// 2 = packed a scales, 3 = packed b scales, 4 = c.
+struct PlainMaps {
+  static constexpr bool kGrouped = false;
+  CUtensorMap m[5];
+};
+// Grouped (per-expert) launch: five maps per group, each describing only that group's rows, so that
+// TMA zero-fills loads and clips stores at the group's end; tile_start is the running count of
+// tiles over the groups, rows the row count of each group.
+constexpr int kMaxGroups = 32;
+struct GroupedMaps {
+  static constexpr bool kGrouped = true;
+  CUtensorMap m[kMaxGroups * 5];
+  int tile_start[kMaxGroups + 1];
+  int rows[kMaxGroups];
+  int num_groups;
+};
+
 // Tile order: groups of `group_n` N tiles, each group swept down M with N fastest.
 __device__ __forceinline__ void raster_tile(int t, int tiles_m, int tiles_n, int group_n, int& mt,
                                             int& nt) {
@@ -93,6 +111,24 @@ __device__ __forceinline__ void raster_tile(int t, int tiles_m, int tiles_n, int
   const int gw = min(group_n, tiles_n - n0);
   mt = r / gw;
   nt = n0 + (r - mt * gw);
+}
+
+// Tile id -> (group, M tile, N tile, rows of the group) and the group's first tensor map.
+template <typename Maps>
+__device__ __forceinline__ const CUtensorMap* decode_tile(const Maps& maps, const GemmParams& p, int t, int& mt, int& nt,
+                                                          int& rows) {
+  if constexpr (!Maps::kGrouped) {
+    raster_tile(t, p.tiles_m, p.tiles_n, p.group_n, mt, nt);
+    rows = p.M;
+    return &maps.m[0];
+  } else {
+    int g = 0;
+    while (g + 1 < maps.num_groups && t >= maps.tile_start[g + 1]) ++g;
+    const int first = maps.tile_start[g];
+    raster_tile(t - first, (maps.tile_start[g + 1] - first) / p.tiles_n, p.tiles_n, p.group_n, mt, nt);
+    rows = maps.rows[g];
+    return &maps.m[g * 5];
+  }
 }
 
 // Adds the 32 values already in C (row pointer p) to r: the accumulate-into-C form the
@@ -184,11 +220,9 @@ __device__ __forceinline__ void stage_chunk32(uint32_t buf, int lane, const uint
   }
 }
 
-template <int CG, int BN, typename OutT>
+template <int CG, int BN, typename OutT, typename Maps>
 __global__ void __launch_bounds__(192, 1)
-mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
-                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
   using Cfg = GemmCfg<CG, BN, int(sizeof(OutT))>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -230,11 +264,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tmem_relinquish<CG>();
   }
   if (warp == 0 && lane == 0) {
-    prefetch_tensormap(&tmA);
-    prefetch_tensormap(&tmB);
-    prefetch_tensormap(&tmSFA);
-    prefetch_tensormap(&tmSFB);
-    prefetch_tensormap(&tmC);
+#pragma unroll
+    for (int i = 0; i < 5; ++i) prefetch_tensormap(&maps.m[i]);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -245,7 +276,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  int num_tiles = p.tiles_m * p.tiles_n;
+  if constexpr (Maps::kGrouped) num_tiles = maps.tile_start[maps.num_groups];
   const int first_tile = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_step = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
   const int num_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
@@ -255,8 +287,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // The whole warp walks the loop; one elected lane issues the copies.
     uint32_t stage = 0, phase = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step) {
-      int mt, nt;
-      raster_tile(t, p.tiles_m, p.tiles_n, p.group_n, mt, nt);
+      int mt, nt, rows;
+      const CUtensorMap* tm = decode_tile(maps, p, t, mt, nt, rows);
       const int a_row = (mt * CG + int(rank)) * Cfg::BM;
       const int b_row = nt * BN + int(rank) * Cfg::B_ROWS;
       const int sfa_rb = mt * CG + int(rank);
@@ -272,11 +304,11 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t fb = (CG == 2) ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
         if (elect_one()) {
           if (leader) mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES * CG);
-          tma_load_2d<CG>(sA, &tmA, kb * 128, a_row, fb);
-          tma_load_2d<CG>(sB, &tmB, kb * 128, b_row, fb);
+          tma_load_2d<CG>(sA, tm + 0, kb * 128, a_row, fb);
+          tma_load_2d<CG>(sB, tm + 1, kb * 128, b_row, fb);
           // scale factors: 1024 bytes (two atoms) per 128-row block and stage
-          tma_load_2d<CG>(sSFA, &tmSFA, kb * 256, sfa_rb, fb);
-          tma_load_2d<CG>(sSFB, &tmSFB, kb * 256, sfb_rb, fb);
+          tma_load_2d<CG>(sSFA, tm + 2, kb * 256, sfa_rb, fb);
+          tma_load_2d<CG>(sSFB, tm + 3, kb * 256, sfb_rb, fb);
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -363,8 +395,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t stg = staging_base + uint32_t(warp - 2) * 2 * Cfg::CHUNK_BYTES;
     int it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
-      int mt, nt;
-      raster_tile(t, p.tiles_m, p.tiles_n, p.group_n, mt, nt);
+      int mt, nt, rows;
+      const CUtensorMap* tm = decode_tile(maps, p, t, mt, nt, rows);
       const int as = it & 1;
       mbar_wait(acc_full_bar(as), uint32_t(it >> 1) & 1u, ctx, WB_DEV_TIMEOUT_EPILOGUE);
       tc_fence_after_sync();
@@ -410,10 +442,10 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             // rows and columns past M, N are clipped by the store; a chunk that lies outside C
             // altogether still commits an (empty) group, because the buffer hand-over above
             // counts groups: one group per chunk, whether or not it stored anything
-            if (row0 < p.M && col < p.N && !(p.dbg & 32)) tma_store_2d(&tmC, buf, col, row0);
+            if (row0 < rows && col < p.N && !(p.dbg & 32)) tma_store_2d(tm + 4, buf, col, row0);
             bulk_commit_group();
           }
-        } else if (row < p.M && col < p.N && !(p.dbg & 32)) {
+        } else if (row < rows && col < p.N && !(p.dbg & 32)) {
           OutT* dst = C + size_t(row) * p.ldc + col;
           const int ncols = min(32, p.N - col);
           if (p.accumulate) add_old_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);

@@ -25,22 +25,21 @@ __host__ __device__ inline size_t sf_packed_bytes(int rows, int K) {
   return size_t(sf_row_blocks(rows)) * sf_k_atoms(K) * 512;
 }
 
-// grid (ceil(k_atoms / 8), row_blocks), 256 threads. One block moves 128 rows x 32 K-blocks
-// through shared memory: reads are 16 bytes per thread along K, writes are 4 KiB contiguous.
-__global__ void __launch_bounds__(256)
-repack_scales_kernel(const uint8_t* __restrict__ src, long long src_row_stride, int rows, int kblocks,
-                     int k_atoms, uint8_t* __restrict__ dst) {
+// One thread block moves 128 rows x 32 K-blocks through shared memory: reads are 16 bytes per
+// thread along K, writes are 4 KiB contiguous. Rows [row_base, row_base + 128) of src, clipped at
+// row_limit, go to the 128-row block whose first atom is at dst_block.
+__device__ __forceinline__ void repack_tile(const uint8_t* __restrict__ src, long long src_row_stride, int row_base,
+                                            int row_limit, int kblocks, int k_atoms, int atom0,
+                                            uint8_t* __restrict__ dst_block) {
   __shared__ __align__(16) uint8_t tile[128][32 + 4];  // +4 keeps 32-bit reads aligned and spreads banks
-  const int rb = blockIdx.y;
-  const int atom0 = blockIdx.x * 8;
   const int t = threadIdx.x;
   {
     const int r = t >> 1;
     const int half = t & 1;
-    const int row = rb * 128 + r;
+    const int row = row_base + r;
     const int kb0 = atom0 * 4 + half * 16;
     const uint8_t* s = src + (long long)row * src_row_stride + kb0;
-    const bool row_ok = row < rows;
+    const bool row_ok = row < row_limit;
     if (row_ok && kb0 + 16 <= kblocks && ((reinterpret_cast<uintptr_t>(s) & 15) == 0)) {
       const uint4 v = *reinterpret_cast<const uint4*>(s);
       uint32_t* d = reinterpret_cast<uint32_t*>(&tile[r][half * 16]);
@@ -61,10 +60,38 @@ repack_scales_kernel(const uint8_t* __restrict__ src, long long src_row_stride, 
       v.y = *reinterpret_cast<const uint32_t*>(&tile[32 + r32][a * 4]);
       v.z = *reinterpret_cast<const uint32_t*>(&tile[64 + r32][a * 4]);
       v.w = *reinterpret_cast<const uint32_t*>(&tile[96 + r32][a * 4]);
-      uint8_t* d = dst + (size_t(rb) * k_atoms + atom0 + a) * 512 + r32 * 16;
+      uint8_t* d = dst_block + size_t(atom0 + a) * 512 + r32 * 16;
       *reinterpret_cast<uint4*>(d) = v;
     }
   }
+}
+
+// grid (ceil(k_atoms / 8), row_blocks), 256 threads.
+__global__ void __launch_bounds__(256)
+repack_scales_kernel(const uint8_t* __restrict__ src, long long src_row_stride, int rows, int kblocks,
+                     int k_atoms, uint8_t* __restrict__ dst) {
+  const int rb = blockIdx.y;
+  repack_tile(src, src_row_stride, rb * 128, rows, kblocks, k_atoms, blockIdx.x * 8, dst + size_t(rb) * k_atoms * 512);
+}
+
+// Grouped form: the rows of group g are src rows [row_start[g], row_start[g+1]) and its packed block
+// starts at 128-row block block_start[g] of dst (every group starts on a block boundary, because
+// a scale-factor atom covers 128 consecutive rows of ONE GEMM). grid (ceil(k_atoms / 8), total blocks).
+constexpr int kMaxRepackGroups = 32;
+struct RepackGroups {
+  int num_groups;
+  int row_start[kMaxRepackGroups + 1];
+  int block_start[kMaxRepackGroups + 1];
+};
+__global__ void __launch_bounds__(256)
+repack_scales_grouped_kernel(const uint8_t* __restrict__ src, long long src_row_stride, const RepackGroups tab,
+                             int kblocks, int k_atoms, uint8_t* __restrict__ dst) {
+  const int rb = blockIdx.y;
+  int g = 0;
+  while (g + 1 < tab.num_groups && rb >= tab.block_start[g + 1]) ++g;
+  const int row_base = tab.row_start[g] + (rb - tab.block_start[g]) * 128;
+  repack_tile(src, src_row_stride, row_base, tab.row_start[g + 1], kblocks, k_atoms, blockIdx.x * 8,
+              dst + size_t(rb) * k_atoms * 512);
 }
 
 // out[r, k] = E2M1(code(r, k)) * 2^(scale(r, k / 32) - 127), the dequantised operand of

@@ -86,13 +86,20 @@ def grouped_scaled_gemm(a: torch.Tensor, a_scale: torch.Tensor, experts: ExpertW
         block_offsets.append(block_offsets[-1] + (row_offsets[e + 1] - row_offsets[e] + 127) // 128)
     atom_row_bytes = ops.packed_scale_bytes(128, K)
     a_sf = torch.empty(max(block_offsets[-1], 1) * atom_row_bytes, dtype=torch.uint8, device=a.device)
-    for e in range(E):
-        r0, r1 = row_offsets[e], row_offsets[e + 1]
-        if r1 > r0:
-            ops.repack_scales(a_scale[r0:r1], out=a_sf[block_offsets[e] * atom_row_bytes:])
     offs = (ctypes.c_int * (E + 1))(*row_offsets)
     boffs = (ctypes.c_int * (E + 1))(*block_offsets)
+    if a_scale.stride(1) != 1:
+        a_scale = a_scale.contiguous()
     with torch.cuda.device(a.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        if E <= 32:  # one launch packs every expert's block
+            _lib.check(lib.wb200_repack_scales_grouped(a_scale.data_ptr(), a_scale.stride(0), E, offs, boffs, K,
+                                                       a_sf.data_ptr(), stream))
+        else:
+            for e in range(E):
+                r0, r1 = row_offsets[e], row_offsets[e + 1]
+                if r1 > r0:
+                    ops.repack_scales(a_scale[r0:r1], out=a_sf[block_offsets[e] * atom_row_bytes:])
         _lib.check(lib.wb200_mxfp4_grouped_gemm(E, offs, boffs, N, K, a.data_ptr(), a_sf.data_ptr(), experts._b_ptrs,
                                                 experts._sf_ptrs, c.data_ptr(), ops._DTYPE_CODE[c.dtype], c.stride(0),
                                                 torch.cuda.current_stream().cuda_stream))
