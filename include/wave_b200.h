@@ -81,6 +81,17 @@ int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int
 int wb200_repack_scales_grouped(const void* src, long long src_row_stride, int num_groups, const int* row_offsets,
                                 const int* row_block_offsets, int K, void* dst, void* stream);
 
+/* Activation quantiser: x [rows, K] (f32 when x_dtype == WB200_F32, bf16 when WB200_BF16, row pitch ldx
+ * elements, 16-byte aligned rows) -> packed E2M1 codes q [rows, K/2] and E8M0 scales, written row-major
+ * (scale_rowmajor [rows, K/32], may be NULL) and/or in the packed layout the GEMM reads (scale_packed,
+ * wb200_packed_scale_bytes(rows, K) bytes, may be NULL; padding bytes are filled too). Per 32-element
+ * block: scale exponent floor(log2(amax)) - 2, values rounded to the nearest E2M1 value, ties to the even
+ * code. The reference names this step as its direction ("fused dynamic quantization",
+ * wave_lang/kernel/wave/templates/test_kernels.py:74) but ships no quantiser; its tests feed random
+ * codes (wave_lang/kernel/wave/utils/mxfp_utils.py:20-57). */
+int wb200_quantize_mxfp4(const void* x, int x_dtype, long long ldx, int rows, int K, void* q, void* scale_rowmajor,
+                         void* scale_packed, void* stream);
+
 /* Test aid: out[r, k] = E2M1(q) * 2^(scale - 127) as f32, the dequantised operand of
  * mxfp4_to_f32 / e8m0_to_f32 (wave_lang/kernel/wave/utils/mxfp_utils.py:60-95). */
 int wb200_mxfp4_dequant(const void* q, const void* scale, int rows, int K, float* out, void* stream);

@@ -460,3 +460,36 @@ def test_grouped_repack_matches_per_group_repack():
         if r1 > r0:
             exp = orc.pack_scales(s[r0:r1])
             assert torch.equal(got[blocks[g] * per_block: blocks[g] * per_block + exp.numel()], exp), g
+
+
+# ---------------------------------------------------------------------------------------------
+# activation quantiser and the linear module built on it
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,K", [(128, 256), (100, 96), (300, 8192), (1, 32), (257, 1184)])
+def test_quantizer_bit_exact_against_oracle(rows, K, dtype):
+    g = torch.Generator().manual_seed(rows + K)
+    x = torch.randn(rows, K, generator=g) * torch.exp(torch.randn(rows, 1, generator=g) * 3)  # wide range of row scales
+    x[0, :32] = 0.0                                                 # an all-zero block
+    x[-1, :32] = 0.0
+    x[-1, :8] = torch.tensor([6.0, 0.25, 0.75, 2.5, 5.0, -0.25, -1.25, 3.5]) * 4  # midpoints (ties) after scaling by 4
+    x = x.to(dtype)
+    q, s, packed = wb.quantize_mxfp4(x.to(DEV))
+    eq, es = orc.quantize_mxfp4(x.float())
+    assert torch.equal(s.cpu(), es)
+    assert torch.equal(q.cpu(), eq)
+    assert torch.equal(packed.data.cpu(), orc.pack_scales(es))
+
+
+def test_mxfp4_linear_module_matches_oracle():
+    torch.manual_seed(5)
+    N, K = 768, 1024
+    w = torch.randn(N, K) * 0.02
+    x = torch.randn(3, 50, K)
+    layer = wb.MXFP4Linear.from_float(w.to(DEV), output_dtype=torch.bfloat16)
+    y = layer(x.to(DEV))
+    assert y.shape == (3, 50, N) and y.dtype == torch.bfloat16
+    wq, ws = orc.quantize_mxfp4(w)
+    xq, xs = orc.quantize_mxfp4(x.reshape(-1, K))
+    assert torch.equal(layer.weight_codes.cpu(), wq) and torch.equal(layer.weight_scales.cpu(), ws)
+    check_bf16(y.reshape(-1, N), orc.scaled_gemm(xq, xs, wq, ws))

@@ -14,7 +14,7 @@ from .compile import (SchedulingType, ScaledGemmKernel, WaveCompileOptions, get_
 from .constraints import ScaledMMAType  # noqa: F401
 from .lang import (GLOBAL_ADDRESS_SPACE, SHARED_ADDRESS_SPACE, TORCH_DTYPE_TO_WAVE, bf16, f32, i8)  # noqa: F401
 from .mxfp_utils import (SCALE_GROUP_SIZE, PackedScales, b_preshuffle, e8m0_shuffle,  # noqa: F401
-                         generate_gemm_afp4wfp4_inputs, mxfp4_dequant)
+                         generate_gemm_afp4wfp4_inputs, mxfp4_dequant, quantize_mxfp4)
 from .schedules import (get_mxfp4_asymmetric_schedule, get_mxfp4_dbuf_mixed_pingpong_schedule,  # noqa: F401
                         get_mxfp4_dbuf_mixed_pingpong_shuffle_schedule, get_mxfp4_dbuf_pingpong_schedule,
                         get_mxfp4_dbuf_pingpong_schedule_Bshuffled, get_mxfp4_dbuf_pingpong_schedule_Bshuffled_lds,
@@ -23,5 +23,7 @@ from .templates import (get_scaled_gemm_kernel, get_tagged_mxfp4_gemm, get_tagge
                         get_tagged_mxfp4_gemm_preshuffle_b_wide_store, get_tagged_mxfp4_gemm_preshuffle_scales,
                         get_tagged_mxfp4_gemm_preshuffle_scales_and_B, get_tagged_splitk_mxfp4_gemm,
                         get_tagged_splitk_mxfp4_gemm_preshuffle_b, get_tagged_splitk_mxfp4_gemm_preshuffle_scales)
+
+from .nn import MXFP4Linear  # noqa: F401,E402
 
 __version__ = "0.1.0"

@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "wb200_packed_scale_bytes",
     "wb200_repack_scales",
     "wb200_repack_scales_grouped",
+    "wb200_quantize_mxfp4",
     "wb200_mxfp4_dequant",
     "wb200_mxfp4_gemm_workspace_bytes",
     "wb200_workspace_init",
@@ -89,6 +90,8 @@ def load() -> ctypes.CDLL:
     lib.wb200_repack_scales_grouped.restype = c_int
     lib.wb200_repack_scales_grouped.argtypes = [c_void_p, c_ll, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int,
                                                 c_void_p, c_void_p]
+    lib.wb200_quantize_mxfp4.restype = c_int
+    lib.wb200_quantize_mxfp4.argtypes = [c_void_p, c_int, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.wb200_mxfp4_dequant.restype = c_int
     lib.wb200_mxfp4_dequant.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
     lib.wb200_mxfp4_gemm_workspace_bytes.restype = c_size_t

@@ -3,6 +3,7 @@
 // (wave_lang/kernel/wave/runtime/runtime.cpp:123-263) for the MXFP4 scaled-GEMM kernels.
 #include "../../include/wave_b200.h"
 #include "gemm_sm100.cuh"
+#include "quantize.cuh"
 #include "scales.cuh"
 #include "skinny_sm100.cuh"
 
@@ -510,6 +511,41 @@ int wb200_repack_scales_grouped(const void* src, long long src_row_stride, int n
   dim3 grid((k_atoms + 7) / 8, total_blocks);
   wb::repack_scales_grouped_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_row_stride, tab, K / 32, k_atoms, static_cast<uint8_t*>(dst));
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+int wb200_quantize_mxfp4(const void* x, int x_dtype, long long ldx, int rows, int K, void* q, void* scale_rowmajor,
+                         void* scale_packed, void* stream) {
+  if (rows <= 0 || K <= 0 || K % 32 != 0)
+    return fail(WB200_ERR_INVALID_ARG, "quantize: rows = %d, K = %d (K must be a positive multiple of 32)", rows, K);
+  if (!x || !q || (!scale_rowmajor && !scale_packed)) return fail(WB200_ERR_INVALID_ARG, "quantize: null pointer");
+  if (x_dtype != WB200_F32 && x_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "quantize: unknown input dtype %d", x_dtype);
+  if (ldx < K) return fail(WB200_ERR_INVALID_ARG, "quantize: ldx = %lld is smaller than K = %d", ldx, K);
+  const int esz = (x_dtype == WB200_F32) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(q) & 1))
+    return fail(WB200_ERR_ALIGNMENT, "quantize: x rows must be 16-byte aligned and q 2-byte aligned");
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int k_atoms = wb::sf_k_atoms(K);
+  if (scale_packed && (rows % 128 != 0 || (K / 32) % 8 != 0)) {
+    const int rbs = wb::sf_row_blocks(rows);
+    const long long total = (long long)rbs * k_atoms * 512;
+    wb::fill_scale_padding_kernel<<<unsigned((total + 255) / 256), 256, 0, s>>>(static_cast<uint8_t*>(scale_packed), rows,
+                                                                                  K / 32, k_atoms, rbs);
+  }
+  const long long threads = (long long)rows * (K / 32) * 8;
+  const unsigned blocks = unsigned((threads + 255) / 256);
+  if (x_dtype == WB200_F32)
+    wb::quantize_mxfp4_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), ldx, rows, K, static_cast<uint8_t*>(q),
+                                                            static_cast<uint8_t*>(scale_rowmajor),
+                                                            static_cast<uint8_t*>(scale_packed), k_atoms);
+  else
+    wb::quantize_mxfp4_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), ldx, rows, K, static_cast<uint8_t*>(q), static_cast<uint8_t*>(scale_rowmajor),
+        static_cast<uint8_t*>(scale_packed), k_atoms);
   WB_CUDA(cudaGetLastError());
   return WB200_OK;
 }

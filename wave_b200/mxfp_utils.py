@@ -54,3 +54,8 @@ def b_preshuffle(b: Tensor) -> Tensor:
 def mxfp4_dequant(q: Tensor, scale: Tensor) -> Tensor:
     """E2M1 x 2^(scale-127) as f32 on the GPU: the dequantised operand of mxfp_utils.py:60-95,135-142."""
     return ops.dequant_mxfp4(q, scale)
+
+
+def quantize_mxfp4(x: Tensor):
+    """f32 / bf16 [rows, K] -> (codes, row-major scales, PackedScales) on the GPU; see ops.quantize_mxfp4."""
+    return ops.quantize_mxfp4(x)

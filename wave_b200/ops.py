@@ -161,3 +161,28 @@ def check_device_status() -> None:
     """Synchronise the current stream and raise DeviceTimeoutError if a kernel's bounded wait gave up."""
     detail = ctypes.c_int(0)
     _lib.check(_lib.load().wb200_check_device_status(_stream(), ctypes.byref(detail)))
+
+
+def quantize_mxfp4(x: torch.Tensor, want_rowmajor: bool = True, want_packed: bool = True):
+    """f32 or bf16 [rows, K] -> (codes [rows, K/2] uint8, scales [rows, K/32] uint8 or None, PackedScales or None),
+    one pass on the current stream. The packed scales feed the GEMM directly, without a repack."""
+    lib = _lib.load()
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor; wave_b200 has no CPU path")
+    if x.dtype not in _DTYPE_CODE or x.dim() != 2:
+        raise ValueError(f"x must be a 2-D float32 or bfloat16 tensor, got {x.dtype} {tuple(x.shape)}")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    rows, K = x.shape
+    if K % SCALE_GROUP_SIZE:
+        raise ValueError(f"K = {K} is not a multiple of {SCALE_GROUP_SIZE}")
+    if not (want_rowmajor or want_packed):
+        raise ValueError("ask for at least one scale layout")
+    q = torch.empty(rows, K // 2, dtype=torch.uint8, device=x.device)
+    s_rm = torch.empty(rows, K // SCALE_GROUP_SIZE, dtype=torch.uint8, device=x.device) if want_rowmajor else None
+    s_pk = torch.empty(packed_scale_bytes(rows, K), dtype=torch.uint8, device=x.device) if want_packed else None
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wb200_quantize_mxfp4(x.data_ptr(), _DTYPE_CODE[x.dtype], x.stride(0), rows, K, q.data_ptr(),
+                                            s_rm.data_ptr() if want_rowmajor else None,
+                                            s_pk.data_ptr() if want_packed else None, _stream()))
+    return q, s_rm, (PackedScales(s_pk, rows, K) if want_packed else None)
