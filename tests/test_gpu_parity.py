@@ -493,3 +493,22 @@ def test_mxfp4_linear_module_matches_oracle():
     xq, xs = orc.quantize_mxfp4(x.reshape(-1, K))
     assert torch.equal(layer.weight_codes.cpu(), wq) and torch.equal(layer.weight_scales.cpu(), ws)
     check_bf16(y.reshape(-1, N), orc.scaled_gemm(xq, xs, wq, ws))
+
+
+def test_host_pipelined_gemm_on_pinned_buffers():
+    """Five calls through the three-stream host pipeline with three device buffer sets: every result
+    must belong to its own call's operands (no buffer reused before its result left the device)."""
+    from wave_b200.host_pipeline import HostScaledGemm
+    M, N, K = 200, 384, 512
+    pipe = HostScaledGemm(M, N, K, wb.bf16, device=DEV, depth=3)
+    problems = [random_problem(M, N, K, seed=80 + i) for i in range(5)]
+    pinned = [[t.pin_memory() for t in p] for p in problems]
+    outs = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _ in problems]
+    for (a, a_s, b, b_s), c in zip(pinned, outs):
+        pipe.submit(a, a_s, b, b_s, c)
+    pipe.drain()
+    for (a, a_s, b, b_s), c in zip(problems, outs):
+        check_bf16(c, orc.scaled_gemm(a, a_s, b, b_s))
+    with pytest.raises(ValueError, match="pinned"):
+        pipe.submit(*problems[0], outs[0])
+    ops.check_device_status()
