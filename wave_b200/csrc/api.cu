@@ -160,11 +160,6 @@ int set_smem(K kernel, int bytes, bool* done) {
   return WB200_OK;
 }
 
-int debug_knobs() {
-  static int v = -1;
-  if (v < 0) { const char* e = getenv("WB200_DBG"); v = e ? atoi(e) : 0; }
-  return v;
-}
 
 int check_common(int M, int N, int K, const void* a, const void* as, const void* b, const void* bs, const void* c,
                  int c_dtype, long long ldc) {
@@ -236,7 +231,6 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   } else {
     tmC = tmA;  // never dereferenced by the kernel on the direct-store path
   }
-  p.dbg = debug_knobs();
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT, wb::PlainMaps>;
   static bool smem_set[kMaxDevices] = {};
@@ -327,7 +321,6 @@ int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets
   p.vec_ok = 1;
   p.tma_store = 1;
   p.accumulate = 0;
-  p.dbg = debug_knobs();
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT, wb::GroupedMaps>;
   static bool smem_set[kMaxDevices] = {};
@@ -385,7 +378,6 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   p.tiles_n = (N + 127) / 128;
   p.num_kb = (K + 255) / 256;
   p.accumulate = accumulate;
-  p.dbg = debug_knobs();
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_skinny_kernel<NP, STAGES, OutT>;
   static bool smem_set[kMaxDevices] = {};
@@ -676,8 +668,7 @@ int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* 
     if (row_offsets[g + 1] < row_offsets[g]) return fail(WB200_ERR_INVALID_ARG, "grouped gemm: row offsets decrease at group %d", g);
   // One persistent launch when the groups fit the kernel's descriptor table and c can take TMA stores;
   // otherwise one launch per group.
-  if (num_groups <= wb::kMaxGroups && c && (reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0 && ldc >= N &&
-      !(debug_knobs() & 512)) {
+  if (num_groups <= wb::kMaxGroups && c && (reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0 && ldc >= N) {
     if (c_dtype == WB200_F32)
       return launch_grouped<float>(*dev, num_groups, row_offsets, row_block_offsets, N, K, a, a_scale_packed, b_ptrs,
                                    b_scale_ptrs, c, ldc, static_cast<cudaStream_t>(stream));

@@ -55,10 +55,14 @@ struct GemmCfg {
   // Scale factors live in a small ring of column sets so that the tcgen05.cp of one K block does
   // not have to wait for the MMAs of the previous block to finish reading theirs.
   static constexpr int SF_SET_COLS = 8 + BN / 16;  // A: 2 atoms x 4 columns, B: (BN/128) x 2 atoms x 4
-  static constexpr int SF_SETS = OVERLAP ? 2 : 4;
-  static constexpr int SF_COL = OVERLAP ? 464 : 256;
-  static constexpr int OVERLAP_CHUNKS = 2;         // 32-column chunks shared by the two accumulators (48 columns)
-  static constexpr int ACC_COL1 = OVERLAP ? 208 : BN;
+#ifndef WB_OVERLAP_SF_SETS
+#define WB_OVERLAP_SF_SETS 2
+#endif
+  static constexpr int SF_SETS = OVERLAP ? WB_OVERLAP_SF_SETS : 4;
+  static constexpr int SF_COL = OVERLAP ? 512 - SF_SETS * SF_SET_COLS : 256;
+  // 32-column chunks shared by the two accumulators: accumulator 1 ends where the scale factors begin
+  static constexpr int OVERLAP_CHUNKS = (2 * 256 - SF_COL + 31) / 32;
+  static constexpr int ACC_COL1 = OVERLAP ? SF_COL - 256 : BN;
   static_assert(SF_COL + SF_SETS * SF_SET_COLS <= 512, "scale-factor ring does not fit in tensor memory");
   static constexpr int THREADS = 192;
   static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
@@ -79,7 +83,6 @@ struct GemmParams {
   int vec_ok;         // C base and row pitch allow 16-byte stores
   int tma_store;      // write C with TMA stores from swizzled shared memory (needs vec_ok, no accumulate)
   int accumulate;     // add to the values already in C instead of overwriting them
-  int dbg;
   int* status;
 };
 
@@ -328,7 +331,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
         if constexpr (Cfg::OVERLAP) {
           // Needs the previous tile's epilogue to have drained the 48 shared columns
           // (which also means the tile before that is fully drained).
-          if (it > 0 && !(p.dbg & 64)) {
+          if (it > 0) {
             const int ps = (it - 1) & 1;
             mbar_wait<CG == 2>(acc_empty_bar(ps), uint32_t((it - 1) >> 1) & 1u, ctx, WB_DEV_TIMEOUT_MMA_ACC);
           }
@@ -355,7 +358,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
           if (elect_one()) {
             // scale factors: smem atoms -> tensor memory (4 columns per atom); +32 in the
             // descriptor's address field = +512 bytes = the next atom
-            if (!(p.dbg & 2) || kb == 0) {
+            {
 #pragma unroll
               for (int a = 0; a < 2; ++a) utccp_sf_atom<CG>(t_sfa + a * 4, sfa_desc + uint64_t(a * 32));
 #pragma unroll
@@ -364,7 +367,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
                 for (int a = 0; a < 2; ++a)
                   utccp_sf_atom<CG>(t_sfb + a * (BN / 32) + j * 4, sfb_desc + uint64_t(j * 64 + a * 32));
             }
-            if (!(p.dbg & 8)) {
+            {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
                 // K = 64 per instruction = 32 bytes inside the 128-byte swizzle row
@@ -442,10 +445,10 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
             // rows and columns past M, N are clipped by the store; a chunk that lies outside C
             // altogether still commits an (empty) group, because the buffer hand-over above
             // counts groups: one group per chunk, whether or not it stored anything
-            if (row0 < rows && col < p.N && !(p.dbg & 32)) tma_store_2d(tm + 4, buf, col, row0);
+            if (row0 < rows && col < p.N) tma_store_2d(tm + 4, buf, col, row0);
             bulk_commit_group();
           }
-        } else if (row < rows && col < p.N && !(p.dbg & 32)) {
+        } else if (row < rows && col < p.N) {
           OutT* dst = C + size_t(row) * p.ldc + col;
           const int ncols = min(32, p.N - col);
           if (p.accumulate) add_old_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);

@@ -55,7 +55,6 @@ struct SkinnyParams {
   int tiles_n;   // ceil(N / 128)
   int num_kb;    // ceil(K / 256)
   int accumulate;  // add to the values already in C instead of overwriting them
-  int dbg;
   int* status;
 };
 
@@ -109,51 +108,57 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     *abort_flag = 0u;
     fence_mbar_init();
   }
+  const long long total_units = (long long)p.tiles_n * p.num_kb;
+  int u0, u1;
+  skinny_range(total_units, gridDim.x, blockIdx.x, u0, u1);
+
+  // Producer state. Warp 0 has just initialised the barriers, so it starts the first ring of loads
+  // right away, before the CTA-wide synchronisation that waits for the tensor-memory allocation:
+  // the weight stream is what bounds this kernel, and its first bytes need not wait for that.
+  uint32_t p_stage = 0, p_phase = 0;
+  int p_tile = u0 / p.num_kb;
+  int p_kb = u0 - p_tile * p.num_kb;
+  int p_u = u0;
+  uint64_t stream_policy = 0, keep_policy = 0;
+  auto produce = [&](int u_end, bool wait_for_slot) {
+    for (; p_u < u_end; ++p_u) {
+      if (wait_for_slot) mbar_wait(empty_bar(p_stage), p_phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
+      const uint32_t sW = smem_base + p_stage * Cfg::STAGE_BYTES;
+      const uint32_t sX = sW + Cfg::W_BYTES;
+      const uint32_t sSFW = sX + Cfg::X_BYTES;
+      const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
+      const uint32_t fb = full_bar(p_stage);
+      if (elect_one()) {
+        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+        tma_load_2d_hint(sW, &tmW, p_kb * 128, p_tile * 128, fb, stream_policy);
+        tma_load_2d_hint(sX, &tmX, p_kb * 128, 0, fb, keep_policy);
+        tma_load_2d(sSFW, &tmSFW, p_kb * 256, p_tile, fb);
+        tma_load_2d(sSFX, &tmSFX, p_kb * 256, 0, fb);
+      }
+      __syncwarp();
+      if (++p_kb == p.num_kb) { p_kb = 0; ++p_tile; }
+      if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
+    }
+  };
+  if (warp == 0) {
+    __syncwarp();  // lane 0 initialised the barriers above
+    stream_policy = l2_policy_evict_first();  // weights are read once
+    keep_policy = l2_policy_evict_last();     // activations are re-read by every CTA
+    produce(min(u1, u0 + STAGES), false);     // the first pass over the ring needs no free-slot wait
+  }
   if (warp == 1) {
     tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish<1>();
-  }
-  if (warp == 0 && lane == 0) {
-    prefetch_tensormap(&tmW);
-    prefetch_tensormap(&tmX);
-    prefetch_tensormap(&tmSFW);
-    prefetch_tensormap(&tmSFX);
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const long long total_units = (long long)p.tiles_n * p.num_kb;
-  int u0, u1;
-  skinny_range(total_units, gridDim.x, blockIdx.x, u0, u1);
-
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the loop; one elected lane issues the copies.
-    const uint64_t stream_policy = l2_policy_evict_first();  // weights are read once
-    const uint64_t keep_policy = l2_policy_evict_last();     // activations are re-read by every CTA
-    uint32_t stage = 0, phase = 0;
-    int tile = u0 / p.num_kb;
-    int kb = u0 - tile * p.num_kb;
-    for (int u = u0; u < u1; ++u) {
-      mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
-      const uint32_t sW = smem_base + stage * Cfg::STAGE_BYTES;
-      const uint32_t sX = sW + Cfg::W_BYTES;
-      const uint32_t sSFW = sX + Cfg::X_BYTES;
-      const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
-      const uint32_t fb = full_bar(stage);
-      if (elect_one()) {
-        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-        tma_load_2d_hint(sW, &tmW, kb * 128, tile * 128, fb, stream_policy);
-        tma_load_2d_hint(sX, &tmX, kb * 128, 0, fb, keep_policy);
-        tma_load_2d(sSFW, &tmSFW, kb * 256, tile, fb);
-        tma_load_2d(sSFX, &tmSFX, kb * 256, 0, fb);
-      }
-      __syncwarp();
-      if (++kb == p.num_kb) { kb = 0; ++tile; }
-      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-    }
+    produce(u1, true);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = make_idesc_mxf4(128, NP);
