@@ -512,3 +512,71 @@ def test_host_pipelined_gemm_on_pinned_buffers():
     with pytest.raises(ValueError, match="pinned"):
         pipe.submit(*problems[0], outs[0])
     ops.check_device_status()
+
+
+# ---------------------------------------------------------------------------------------------
+# the reference's own test shapes, and a seeded sweep of odd shapes
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(1024, 1024, 8192), (1024, 1600, 8192), (1024, 1920, 8192), (1024, 3072, 8192)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_reference_macrotile_shapes_seed5(shape, out_dtype):
+    """Shapes of testScaledGemmMXFP4ManualDoubleBuf / ...PreshuffleMacrotiles / ...8WavePingpong
+    (wave_gemm_mxfp_test.py:637-680, 778-1085, 1088-1260), inputs from the reference's seed-5 generator,
+    compared as the reference compares (default assert_close) and with this library's tolerances."""
+    x, w, xs, ws = orc.generate_gemm_afp4wfp4_inputs(shape)
+    w_t = w.T.contiguous()
+    ref = orc.torch_scaled_gemm_mxfp4(x, w, xs, ws)
+    kernel, options = wb.get_tagged_mxfp4_gemm_preshuffle_b(shape, (128, 256, 256), wave_shape=(1, 4),
+                                                            output_dtype=wb.TORCH_DTYPE_TO_WAVE[out_dtype])
+    gemm = wb.wave_compile(wb.set_default_run_config(options), kernel, wb.get_mxfp4_asymmetric_schedule())
+    out = torch.zeros(shape[0], shape[1], dtype=out_dtype, device=DEV)
+    gemm(x.to(DEV), wb.e8m0_shuffle(xs.to(DEV)), wb.b_preshuffle(w_t.to(DEV)), wb.e8m0_shuffle(ws.to(DEV)), out)
+    torch.testing.assert_close(ref, out.cpu(), check_dtype=False)
+    check(out, x, xs, w_t, ws, ref=ref)
+
+
+def test_seeded_sweep_of_odd_shapes():
+    """40 random (M, N, K) with K a multiple of 32 and nothing else aligned, automatic path choice,
+    alternating output types; scales over a wider range than the fixed tests."""
+    rng = torch.Generator().manual_seed(2024)
+    for i in range(40):
+        M = int(torch.randint(1, 700, (1,), generator=rng))
+        N = int(torch.randint(1, 900, (1,), generator=rng))
+        K = 32 * int(torch.randint(1, 40, (1,), generator=rng))
+        a, a_s, b, b_s = random_problem(M, N, K, seed=1000 + i, lo=118, hi=136)
+        out_dtype = torch.float32 if i % 2 else torch.bfloat16
+        kernel, options = wb.get_tagged_mxfp4_gemm((M, N, K), output_dtype=wb.TORCH_DTYPE_TO_WAVE[out_dtype])
+        c = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        wb.wave_compile(options, kernel)(a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV), c)
+        ref = orc.scaled_gemm(a, a_s, b, b_s)
+        if out_dtype == torch.float32:
+            try:
+                check_f32(c, a, a_s, b, b_s, ref)
+            except AssertionError as e:
+                raise AssertionError(f"shape {(M, N, K)} f32: {e}") from e
+        else:
+            # With scales spread over 18 binades some outputs are sums that cancel to far below their
+            # terms; there the f32 bound (which has an absolute part) governs, and the bf16 result may
+            # sit more than one ulp from the rounded reference. Everywhere else: 1 ulp.
+            ulp = orc.bf16_ulp_distance(c, ref)
+            tol = orc.f32_tolerance(orc.dequant_mxfp4(a, a_s), orc.dequant_mxfp4(b, b_s), ref, K)
+            half_ulp = ref.abs() * 2.0 ** -8
+            bad = (ulp > 1) & ~((c.float().cpu() - ref).abs() <= tol + half_ulp)
+            assert not bool(bad.any()), f"shape {(M, N, K)} bf16: {int(bad.sum())} outside both bounds"
+            assert float((ulp > 1).float().mean()) < 1e-3, f"shape {(M, N, K)} bf16: too many entries beyond 1 ulp"
+        ops.check_device_status()
+
+
+def test_nan_scale_propagates_like_the_reference():
+    """Scale code 255 is NaN in the reference (mxfp_utils.py:92-94): the rows and columns it touches are
+    NaN in the output, everything else is unaffected."""
+    M, N, K = 64, 96, 256
+    a, a_s, b, b_s = random_problem(M, N, K, seed=3)
+    a_s[5, 2] = 255
+    b_s[7, 0] = 255
+    ref = orc.scaled_gemm(a, a_s, b, b_s)
+    c = run(a, a_s, b, b_s, torch.float32).cpu()
+    assert torch.equal(c.isnan(), ref.isnan()) and bool(ref.isnan()[5].all()) and bool(ref.isnan()[:, 7].all())
+    ok = ~ref.isnan()
+    tol = orc.f32_tolerance(orc.dequant_mxfp4(a, a_s).nan_to_num(0), orc.dequant_mxfp4(b, b_s).nan_to_num(0), ref.nan_to_num(0), K)
+    assert bool(((c - ref).abs()[ok] <= tol[ok]).all())
