@@ -396,6 +396,8 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     const uint32_t acc_empty_leader0 = (CG == 2) ? mapa_shared(acc_empty_bar(0), 0) : 0u;
     const uint32_t acc_empty_leader1 = (CG == 2) ? mapa_shared(acc_empty_bar(1), 0) : 0u;
     const uint32_t stg = staging_base + uint32_t(warp - 2) * 2 * Cfg::CHUNK_BYTES;
+    // C is written once and not read again by this kernel: keep it from pushing A and B out of L2
+    const uint64_t store_policy = l2_policy_evict_first();
     int it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mt, nt, rows;
@@ -445,7 +447,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
             // rows and columns past M, N are clipped by the store; a chunk that lies outside C
             // altogether still commits an (empty) group, because the buffer hand-over above
             // counts groups: one group per chunk, whether or not it stored anything
-            if (row0 < rows && col < p.N) tma_store_2d(tm + 4, buf, col, row0);
+            if (row0 < rows && col < p.N) tma_store_2d_hint(tm + 4, buf, col, row0, store_policy);
             bulk_commit_group();
           }
         } else if (row < rows && col < p.N) {

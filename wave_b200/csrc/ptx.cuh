@@ -205,6 +205,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t s
       "r"(src_smem), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* tmap, uint32_t src_smem, int x, int y,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(tmap),
+      "r"(src_smem), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
