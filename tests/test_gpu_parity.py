@@ -580,3 +580,21 @@ def test_nan_scale_propagates_like_the_reference():
     ok = ~ref.isnan()
     tol = orc.f32_tolerance(orc.dequant_mxfp4(a, a_s).nan_to_num(0), orc.dequant_mxfp4(b, b_s).nan_to_num(0), ref.nan_to_num(0), K)
     assert bool(((c - ref).abs()[ok] <= tol[ok]).all())
+
+
+def test_cuda_graph_replay_of_a_decode_call():
+    from wave_b200.graphs import GraphedScaledGemm
+    M, N, K = 16, 2048, 1024
+    a, a_s, b, b_s = random_problem(M, N, K, seed=91)
+    a2, a2_s, _, _ = random_problem(M, N, K, seed=92)
+    kernel, options = wb.get_tagged_mxfp4_gemm((M, N, K), output_dtype=wb.bf16)
+    gemm = wb.wave_compile(options, kernel)
+    ad, asd, bd, bsd = a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    g = GraphedScaledGemm(gemm, ad, asd, bd, bsd, c)
+    g.replay()
+    check_bf16(c, orc.scaled_gemm(a, a_s, b, b_s))
+    ad.copy_(a2.to(DEV)); asd.copy_(a2_s.to(DEV))          # new activations in the same buffers
+    g.replay()
+    check_bf16(c, orc.scaled_gemm(a2, a2_s, b, b_s))
+    ops.check_device_status()
