@@ -65,6 +65,12 @@ const char* wb200_last_error(void);
  * (low byte: which wait gave up; upper bits: block index). */
 int wb200_check_device_status(void* stream, int* detail);
 
+/* Self-test of the bounded device-side waits: launches one tiny kernel that waits, for at most
+ * limit_cycles SM cycles (<= 2e8, about 0.1 s), on a barrier nothing signals. The wait gives up, the kernel
+ * ends normally, and the next wb200_check_device_status reports WB200_ERR_DEVICE_TIMEOUT with detail code 7.
+ * The reference has no device-side waits to bound (its errors are host exceptions, runtime.cpp:96-109). */
+int wb200_selftest_wait_timeout(long long limit_cycles, void* stream);
+
 /* Bytes of the packed scale array for a [rows, K/32] scale matrix. */
 size_t wb200_packed_scale_bytes(int rows, int K);
 

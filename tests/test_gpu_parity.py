@@ -598,3 +598,17 @@ def test_cuda_graph_replay_of_a_decode_call():
     g.replay()
     check_bf16(c, orc.scaled_gemm(a2, a2_s, b, b_s))
     ops.check_device_status()
+
+
+def test_bounded_wait_reports_timeout_and_context_stays_usable():
+    """A wait that nothing satisfies gives up after its limit, the kernel ends normally, the status word
+    carries the code, and the next GEMM on the same context is correct."""
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.wb200_selftest_wait_timeout(2_000_000, stream))  # ~1 ms
+    with pytest.raises(_lib.DeviceTimeoutError, match="wait 7"):
+        ops.check_device_status()
+    ops.check_device_status()  # the word was cleared
+    assert lib.wb200_selftest_wait_timeout(10 ** 12, stream) == _lib.WB200_ERR_INVALID_ARG
+    a, a_s, b, b_s = random_problem(256, 256, 512, seed=17)
+    check(run(a, a_s, b, b_s, torch.float32), a, a_s, b, b_s)

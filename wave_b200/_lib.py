@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "wb200_version",
     "wb200_last_error",
     "wb200_check_device_status",
+    "wb200_selftest_wait_timeout",
     "wb200_packed_scale_bytes",
     "wb200_repack_scales",
     "wb200_repack_scales_grouped",
@@ -83,6 +84,8 @@ def load() -> ctypes.CDLL:
     lib.wb200_last_error.argtypes = []
     lib.wb200_check_device_status.restype = c_int
     lib.wb200_check_device_status.argtypes = [c_void_p, ctypes.POINTER(c_int)]
+    lib.wb200_selftest_wait_timeout.restype = c_int
+    lib.wb200_selftest_wait_timeout.argtypes = [c_ll, c_void_p]
     lib.wb200_packed_scale_bytes.restype = c_size_t
     lib.wb200_packed_scale_bytes.argtypes = [c_int, c_int]
     lib.wb200_repack_scales.restype = c_int

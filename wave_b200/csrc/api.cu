@@ -210,14 +210,9 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   rc = make_scale_map(&maps.m[3], bs, sfb_row_blocks, wb::sf_k_atoms(K), BN / 128);
   if (rc) return rc;
   wb::GemmParams p;
-  p.sfa = static_cast<const uint8_t*>(as);
-  p.sfb = static_cast<const uint8_t*>(bs);
   p.c = c;
   p.M = M; p.N = N; p.K = K;
   p.ldc = int(ldc);
-  p.ka_atoms = wb::sf_k_atoms(K);
-  p.sfa_row_blocks = sfa_row_blocks;
-  p.sfb_row_blocks = sfb_row_blocks;
   p.tiles_m = (M + Cfg::BM * CG - 1) / (Cfg::BM * CG);
   p.tiles_n = (N + BN - 1) / BN;
   p.group_n = 16;
@@ -314,7 +309,6 @@ int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets
   p.c = c;
   p.M = row_offsets[num_groups]; p.N = N; p.K = K;
   p.ldc = int(ldc);
-  p.ka_atoms = k_atoms;
   p.tiles_m = 0;
   p.tiles_n = tiles_n;
   p.group_n = 16;
@@ -366,15 +360,11 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   rc = make_scale_map(&tmSFX, as, 1, wb::sf_k_atoms(K), 1);
   if (rc) return rc;
   wb::SkinnyParams p;
-  p.sfw = static_cast<const uint8_t*>(bs);
-  p.sfx = static_cast<const uint8_t*>(as);
   p.c = c;
   p.counters = static_cast<unsigned int*>(ws);
   p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kCounterBytes);
   p.M = M; p.N = N; p.K = K;
   p.ldc = int(ldc);
-  p.ka_atoms = wb::sf_k_atoms(K);
-  p.sfw_row_blocks = wb::sf_row_blocks(N);
   p.tiles_n = (N + 127) / 128;
   p.num_kb = (K + 255) / 256;
   p.accumulate = accumulate;
@@ -427,6 +417,21 @@ int noalloc_scratch(void** out) {
   return WB200_OK;
 }
 
+// Self-test of the bounded-wait machinery: one CTA waits on a barrier that nothing will ever signal,
+// with a short limit. The wait gives up, records WB_DEV_TIMEOUT_SELFTEST in the status word and the
+// kernel ends normally; no fault, trap or endless loop is involved.
+__global__ void selftest_wait_timeout_kernel(int* status, long long limit_cycles) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0u;
+    wb::mbar_init(wb::smem_u32(&bar), 1);
+    wb::fence_mbar_init();
+    wb::WaitCtx ctx{&abort_flag, status, limit_cycles};
+    wb::mbar_wait(wb::smem_u32(&bar), 0u, ctx, wb::WB_DEV_TIMEOUT_SELFTEST);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -449,6 +454,17 @@ int wb200_check_device_status(void* stream, int* detail) {
     return fail(WB200_ERR_DEVICE_TIMEOUT, "device-side wait %d gave up in block %d; results of the last launches are invalid",
                 word & 0xff, word >> 8);
   }
+  return WB200_OK;
+}
+
+int wb200_selftest_wait_timeout(long long limit_cycles, void* stream) {
+  if (limit_cycles <= 0 || limit_cycles > 200000000LL)
+    return fail(WB200_ERR_INVALID_ARG, "selftest: limit of %lld cycles is outside (0, 2e8]", limit_cycles);
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  selftest_wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(dev->status_ptr, limit_cycles);
+  WB_CUDA(cudaGetLastError());
   return WB200_OK;
 }
 

@@ -70,14 +70,9 @@ struct GemmCfg {
 };
 
 struct GemmParams {
-  const uint8_t* sfa;  // A scales, atom layout
-  const uint8_t* sfb;  // B scales, atom layout
   void* c;
   int M, N, K;
   int ldc;            // elements
-  int ka_atoms;       // 512-byte atoms per 128-row block (2 per 256 K elements)
-  int sfa_row_blocks;  // 128-row blocks in the A scale array
-  int sfb_row_blocks;
   int tiles_m, tiles_n;
   int group_n;        // N tiles per raster group
   int vec_ok;         // C base and row pitch allow 16-byte stores

@@ -23,8 +23,7 @@ enum : int {
   WB_DEV_TIMEOUT_MMA_FULL = 2,   // MMA issuer waited too long for a filled stage
   WB_DEV_TIMEOUT_MMA_ACC = 3,    // MMA issuer waited too long for a drained accumulator
   WB_DEV_TIMEOUT_EPILOGUE = 4,   // epilogue waited too long for a finished accumulator
-  WB_DEV_TIMEOUT_PEER = 5,       // CTA pair hand-shake ran out of time
-  WB_DEV_TIMEOUT_FIXUP = 6,      // split-K fix-up waited too long
+  WB_DEV_TIMEOUT_SELFTEST = 7,   // the self-test kernel's wait on a barrier nobody signals
 };
 
 // About one second at 1.9 GHz. Generous next to the longest kernel here (a few ms).
@@ -32,12 +31,6 @@ static constexpr long long WB_WAIT_LIMIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ uint32_t lane_id() {
-  uint32_t l;
-  asm volatile("mov.u32 %0, %%laneid;" : "=r"(l));
-  return l;
 }
 
 // True in exactly one lane of a converged warp. The role loops below are executed by whole warps
@@ -132,6 +125,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster_acquire(uint32_t bar, uint
 struct WaitCtx {
   volatile uint32_t* abort_flag;  // shared memory, one per CTA
   int* status;                    // global memory, one per device
+  long long limit_cycles = WB_WAIT_LIMIT_CYCLES;
 };
 
 // Bounded wait. Returns true when the barrier phase completed, false when the wait was
@@ -149,7 +143,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   while (!poll()) {
     if ((++it & 15u) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (clock64() - t0 > WB_WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > ctx.limit_cycles) {
         *ctx.abort_flag = 1u;
         atomicCAS(ctx.status, 0, code | (int(blockIdx.x) << 8));
         return false;

@@ -43,15 +43,11 @@ struct SkinnyCfg {
 };
 
 struct SkinnyParams {
-  const uint8_t* sfw;  // weight (b) scales, atom layout
-  const uint8_t* sfx;  // activation (a) scales, atom layout (one 128-row block)
   void* c;
   float* partials;         // [2 * gridDim.x][M][128] f32
   unsigned int* counters;  // [tiles_n], zero before the first launch; the kernel re-zeroes them
   int M, N, K;
   int ldc;
-  int ka_atoms;
-  int sfw_row_blocks;
   int tiles_n;   // ceil(N / 128)
   int num_kb;    // ceil(K / 256)
   int accumulate;  // add to the values already in C instead of overwriting them
