@@ -180,12 +180,12 @@ int check_common(int M, int N, int K, const void* a, const void* as, const void*
 // ------------------------------------------------------------------------------------------
 // tile paths
 // ------------------------------------------------------------------------------------------
-// C as a 2-D tensor of output elements for TMA stores: box = 32 columns x 32 rows, swizzled to the
-// row width of the staging buffer (64 bytes for bf16, 128 bytes for f32).
+// C as a 2-D tensor of output elements for TMA stores: box = 128 bytes (32 f32 or 64 bf16 columns) x 32
+// rows with the 128-byte swizzle, the layout of the kernel's staging buffers.
 int make_output_map(CUtensorMap* map, void* c, int M, int N, long long ldc, int esz) {
-  const MapKey k{c, (unsigned long long)N, (unsigned long long)M, (unsigned long long)ldc * esz, 32u, 32u,
+  const MapKey k{c, (unsigned long long)N, (unsigned long long)M, (unsigned long long)ldc * esz, unsigned(128 / esz), 32u,
                  int(esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16),
-                 int(esz == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B), int(CU_TENSOR_MAP_L2_PROMOTION_NONE)};
+                 int(CU_TENSOR_MAP_SWIZZLE_128B), int(CU_TENSOR_MAP_L2_PROMOTION_NONE)};
   CUresult r = encode_2d(map, k);
   if (r != CUDA_SUCCESS)
     return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d (M %d, N %d, ldc %lld)", int(r), M,

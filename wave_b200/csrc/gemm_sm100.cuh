@@ -40,8 +40,10 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   // Epilogue staging: each of the 4 epilogue warps owns two buffers of 32 rows x 32 columns of C,
   // written with the TMA store swizzle (64-byte rows for bf16, 128-byte rows for f32).
-  static constexpr int CHUNK_BYTES = 32 * 32 * OUT_BYTES;
-  static constexpr int STAGING_BYTES = 4 * 2 * CHUNK_BYTES;
+  // A buffer is 32 rows of 128 bytes: one 32-column chunk of f32, or two neighbouring chunks of bf16
+  // (stored together, so that every TMA store writes whole 128-byte lines).
+  static constexpr int STORE_BUF_BYTES = 32 * 128;
+  static constexpr int STAGING_BYTES = 4 * 2 * STORE_BUF_BYTES;
   static constexpr int SMEM_LIMIT = 232448;  // largest dynamic shared memory a CTA may ask for on sm_100
   static constexpr int STAGES_FIT = (SMEM_LIMIT - 1024 - STAGING_BYTES - 512) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
@@ -55,15 +57,13 @@ struct GemmCfg {
   // Scale factors live in a small ring of column sets so that the tcgen05.cp of one K block does
   // not have to wait for the MMAs of the previous block to finish reading theirs.
   static constexpr int SF_SET_COLS = 8 + BN / 16;  // A: 2 atoms x 4 columns, B: (BN/128) x 2 atoms x 4
-#ifndef WB_OVERLAP_SF_SETS
-#define WB_OVERLAP_SF_SETS 2
-#endif
-  static constexpr int SF_SETS = OVERLAP ? WB_OVERLAP_SF_SETS : 4;
+  static constexpr int SF_SETS = OVERLAP ? 2 : 4;
   static constexpr int SF_COL = OVERLAP ? 512 - SF_SETS * SF_SET_COLS : 256;
   // 32-column chunks shared by the two accumulators: accumulator 1 ends where the scale factors begin
   static constexpr int OVERLAP_CHUNKS = (2 * 256 - SF_COL + 31) / 32;
   static constexpr int ACC_COL1 = OVERLAP ? SF_COL - 256 : BN;
   static_assert(SF_COL + SF_SETS * SF_SET_COLS <= 512, "scale-factor ring does not fit in tensor memory");
+  static_assert(OVERLAP_CHUNKS % 2 == 0, "bf16 stores pair neighbouring chunks; the shared columns must be whole pairs");
   static constexpr int THREADS = 192;
   static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
@@ -196,21 +196,20 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 }
 
 // Lane `lane` holds 32 consecutive columns of output row `lane` of a 32 x 32 chunk. Write them to
-// the staging buffer in the layout a TMA store with a 32-column box reads: rows of 64 bytes with
-// the 64-byte swizzle (bf16) or rows of 128 bytes with the 128-byte swizzle (f32). The swizzle
-// also spreads the 32 lanes' 16-byte pieces over all banks.
+// the staging buffer in the layout a TMA store with 128-byte rows and the 128-byte swizzle reads:
+// an f32 chunk fills a row; a bf16 chunk fills half of it (`half` = 0 / 1 for the left / right
+// chunk of a pair). The swizzle also spreads the 32 lanes' 16-byte pieces over all banks.
 template <typename OutT>
-__device__ __forceinline__ void stage_chunk32(uint32_t buf, int lane, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void stage_chunk32(uint32_t buf, int lane, int half, const uint32_t (&r)[32]) {
+  const uint32_t row = buf + lane * 128;
   if constexpr (sizeof(OutT) == 4) {
-    const uint32_t row = buf + lane * 128;
 #pragma unroll
     for (int j = 0; j < 8; ++j)
       st_shared_v4(row + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
   } else {
-    const uint32_t row = buf + lane * 64;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
-      st_shared_v4(row + ((j ^ ((lane >> 1) & 3)) << 4),
+      st_shared_v4(row + (((half * 4 + j) ^ (lane & 7)) << 4),
                    pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1])),
                    pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
                    pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
@@ -390,7 +389,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
     const uint32_t acc_empty_leader0 = (CG == 2) ? mapa_shared(acc_empty_bar(0), 0) : 0u;
     const uint32_t acc_empty_leader1 = (CG == 2) ? mapa_shared(acc_empty_bar(1), 0) : 0u;
-    const uint32_t stg = staging_base + uint32_t(warp - 2) * 2 * Cfg::CHUNK_BYTES;
+    const uint32_t stg = staging_base + uint32_t(warp - 2) * 2 * Cfg::STORE_BUF_BYTES;
     // C is written once and not read again by this kernel: keep it from pushing A and B out of L2
     const uint64_t store_policy = l2_policy_evict_first();
     int it = 0;
@@ -431,19 +430,28 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
         }
         const int col = col0 + chunk * 32;
         if (p.tma_store) {
-          // two staging buffers per warp: the store issued two chunks ago must have read its buffer
-          const uint32_t buf = stg + uint32_t(ci & 1) * Cfg::CHUNK_BYTES;
-          if (lane == 0) bulk_wait_group_read<1>();
-          __syncwarp();
-          stage_chunk32<OutT>(buf, lane, r);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            // rows and columns past M, N are clipped by the store; a chunk that lies outside C
-            // altogether still commits an (empty) group, because the buffer hand-over above
-            // counts groups: one group per chunk, whether or not it stored anything
-            if (row0 < rows && col < p.N) tma_store_2d_hint(tm + 4, buf, col, row0, store_policy);
-            bulk_commit_group();
+          // Two staging buffers per warp; a store covers one f32 chunk or a pair of bf16 chunks (the
+          // chunk order above keeps pairs together). Before a buffer is refilled, the store issued
+          // two stores ago must have read it.
+          constexpr int PER_STORE = (sizeof(OutT) == 2) ? 2 : 1;
+          const int si = ci / PER_STORE, half = ci % PER_STORE;
+          const uint32_t buf = stg + uint32_t(si & 1) * Cfg::STORE_BUF_BYTES;
+          if (half == 0) {
+            if (lane == 0) bulk_wait_group_read<1>();
+            __syncwarp();
+          }
+          stage_chunk32<OutT>(buf, lane, half, r);
+          if (half == PER_STORE - 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              // Rows and columns past M, N are clipped by the store. A store that lies outside C
+              // altogether still commits an (empty) group, because the buffer hand-over above counts
+              // groups: one group per store, whether or not it wrote anything.
+              const int scol = col - (PER_STORE - 1) * 32;
+              if (row0 < rows && scol < p.N) tma_store_2d_hint(tm + 4, buf, scol, row0, store_policy);
+              bulk_commit_group();
+            }
           }
         } else if (row < rows && col < p.N) {
           OutT* dst = C + size_t(row) * p.ldc + col;
