@@ -612,3 +612,19 @@ def test_bounded_wait_reports_timeout_and_context_stays_usable():
     assert lib.wb200_selftest_wait_timeout(10 ** 12, stream) == _lib.WB200_ERR_INVALID_ARG
     a, a_s, b, b_s = random_problem(256, 256, 512, seed=17)
     check(run(a, a_s, b, b_s, torch.float32), a, a_s, b, b_s)
+
+
+def test_single_row_operands_with_arbitrary_size_one_stride():
+    """M = 1 through the reference's generator: `x_scales.T.contiguous()` of a [K/32, 1] tensor is a
+    [1, K/32] tensor whose row stride is 1, not K/32."""
+    shape = (1, 512, 1024)
+    x, w, xs, ws = orc.generate_gemm_afp4wfp4_inputs(shape)
+    assert xs.shape == (1, 32)
+    w_t = w.T.contiguous()
+    kernel, options = wb.get_tagged_mxfp4_gemm(shape, output_dtype=wb.bf16)
+    gemm = wb.wave_compile(options, kernel)
+    c = torch.empty(1, 512, dtype=torch.bfloat16, device=DEV)
+    xs_dev = xs.to(DEV).T.contiguous().T  # keeps the odd stride on the device
+    for _ in range(2):  # first call: checked path; second: remembered-signature path
+        gemm(x.to(DEV), xs_dev, w_t.to(DEV), ws.to(DEV), c)
+        check_bf16(c, orc.torch_scaled_gemm_mxfp4(x, w, xs, ws))

@@ -137,14 +137,14 @@ class ScaledGemmKernel:
         b_sf = self._weight_scales.get(b_scale)
         lib = self._lib
         if dev_index == torch.cuda.current_device():
-            rc = lib.wb200_mxfp4_gemm_repack_a(M, N, K, a.data_ptr(), a_scale.data_ptr(), a_scale.stride(0), a_buf.data_ptr(),
-                                               b.data_ptr(), b_sf.data.data_ptr(), c.data_ptr(), dtype_code, c.stride(0),
+            rc = lib.wb200_mxfp4_gemm_repack_a(M, N, K, a.data_ptr(), a_scale.data_ptr(), a_scale.stride(0) if M > 1 else K // 32, a_buf.data_ptr(),
+                                               b.data_ptr(), b_sf.data.data_ptr(), c.data_ptr(), dtype_code, c.stride(0) if M > 1 else N,
                                                ws_ptr, ws_bytes, flags, torch.cuda.current_stream().cuda_stream)
         else:
             with torch.cuda.device(dev_index):
-                rc = lib.wb200_mxfp4_gemm_repack_a(M, N, K, a.data_ptr(), a_scale.data_ptr(), a_scale.stride(0),
+                rc = lib.wb200_mxfp4_gemm_repack_a(M, N, K, a.data_ptr(), a_scale.data_ptr(), a_scale.stride(0) if M > 1 else K // 32,
                                                    a_buf.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(), c.data_ptr(),
-                                                   dtype_code, c.stride(0), ws_ptr, ws_bytes, flags,
+                                                   dtype_code, c.stride(0) if M > 1 else N, ws_ptr, ws_bytes, flags,
                                                    torch.cuda.current_stream().cuda_stream)
         if rc:
             _lib.check(rc)

@@ -108,16 +108,31 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   int u0, u1;
   skinny_range(total_units, gridDim.x, blockIdx.x, u0, u1);
 
+  // This CTA's run of units, cut into segments: one per tile it touches, in ascending tile order. A
+  // run may start and end in the middle of a tile; those partial segments need the cross-CTA fix-up.
+  // (Processing the partial segments first, so that the fix-up overlaps the streaming of the whole
+  // tiles, was measured and is slower: 27.1 us against 25.0 us at M = 16, N = 28672, K = 8192.)
+  const int nkb = p.num_kb;
+  const int first_tile = u0 / nkb;
+  const int last_tile = (u1 > u0) ? (u1 - 1) / nkb : first_tile;
+  const int nseg = (u1 > u0) ? last_tile - first_tile + 1 : 0;
+  const int head_kbs = u0 - first_tile * nkb;
+  const int tail_kbe = u1 - last_tile * nkb;
+  auto segment = [&](int j, int& tile, int& kbs, int& kbe) {
+    tile = first_tile + j;
+    kbs = (j == 0) ? head_kbs : 0;
+    kbe = (j == nseg - 1) ? tail_kbe : nkb;
+  };
+
   // Producer state. Warp 0 has just initialised the barriers, so it starts the first ring of loads
   // right away, before the CTA-wide synchronisation that waits for the tensor-memory allocation:
   // the weight stream is what bounds this kernel, and its first bytes need not wait for that.
   uint32_t p_stage = 0, p_phase = 0;
-  int p_tile = u0 / p.num_kb;
-  int p_kb = u0 - p_tile * p.num_kb;
-  int p_u = u0;
+  int p_seg = 0, p_tile = 0, p_kb = 0, p_kbe = 0, p_issued = 0;
+  if (nseg > 0) segment(0, p_tile, p_kb, p_kbe);
   uint64_t stream_policy = 0, keep_policy = 0;
-  auto produce = [&](int u_end, bool wait_for_slot) {
-    for (; p_u < u_end; ++p_u) {
+  auto produce = [&](int max_units, bool wait_for_slot) {
+    while (p_seg < nseg && p_issued < max_units) {
       if (wait_for_slot) mbar_wait(empty_bar(p_stage), p_phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
       const uint32_t sW = smem_base + p_stage * Cfg::STAGE_BYTES;
       const uint32_t sX = sW + Cfg::W_BYTES;
@@ -132,7 +147,10 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         tma_load_2d(sSFX, &tmSFX, p_kb * 256, 0, fb);
       }
       __syncwarp();
-      if (++p_kb == p.num_kb) { p_kb = 0; ++p_tile; }
+      ++p_issued;
+      if (++p_kb == p_kbe) {
+        if (++p_seg < nseg) segment(p_seg, p_tile, p_kb, p_kbe);
+      }
       if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
     }
   };
@@ -140,7 +158,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     __syncwarp();  // lane 0 initialised the barriers above
     stream_policy = l2_policy_evict_first();  // weights are read once
     keep_policy = l2_policy_evict_last();     // activations are re-read by every CTA
-    produce(min(u1, u0 + STAGES), false);     // the first pass over the ring needs no free-slot wait
+    produce(STAGES, false);                   // the first pass over the ring needs no free-slot wait
   }
   if (warp == 1) {
     tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -154,16 +172,14 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the loop; one elected lane issues the copies.
-    produce(u1, true);
+    produce(0x7fffffff, true);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = make_idesc_mxf4(128, NP);
     uint32_t stage = 0, phase = 0, sf_set = 0;
-    int seg = 0;
-    for (int u = u0; u < u1; ++seg) {
-      const int tile = u / p.num_kb;
-      const int kbs = u - tile * p.num_kb;
-      const int kbe = min(p.num_kb, kbs + (u1 - u));
+    for (int seg = 0; seg < nseg; ++seg) {
+      int tile, kbs, kbe;
+      segment(seg, tile, kbs, kbe);
       const int as = seg & 1;
       if (seg >= 2)
         mbar_wait(acc_empty_bar(as), uint32_t((seg - 2) >> 1) & 1u, ctx, WB_DEV_TIMEOUT_MMA_ACC);
@@ -201,19 +217,15 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
-      u += kbe - kbs;
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps 2..5
     const int quad = warp & 3;
     const int nl = quad * 32 + lane;  // weight row inside the tile
     OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
-    const int first_tile = u0 / p.num_kb;
-    int seg = 0;
-    for (int u = u0; u < u1; ++seg) {
-      const int tile = u / p.num_kb;
-      const int kbs = u - tile * p.num_kb;
-      const int kbe = min(p.num_kb, kbs + (u1 - u));
+    for (int seg = 0; seg < nseg; ++seg) {
+      int tile, kbs, kbe;
+      segment(seg, tile, kbs, kbe);
       const int as = seg & 1;
       const int n = tile * 128 + nl;
       const bool whole = (kbs == 0 && kbe == p.num_kb);
@@ -318,7 +330,6 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is reused by the next segment
       }
-      u += kbe - kbs;
     }
   }
 

@@ -56,6 +56,7 @@ def repack_scales(scale: torch.Tensor, out: torch.Tensor | None = None) -> Packe
         scale = scale.contiguous()
     rows, kb = scale.shape
     K = kb * SCALE_GROUP_SIZE
+    row_stride = scale.stride(0) if rows > 1 else kb  # the stride of a size-1 dimension is arbitrary
     nbytes = packed_scale_bytes(rows, K)
     if out is None:
         out = torch.empty(nbytes, dtype=torch.uint8, device=scale.device)
@@ -63,10 +64,10 @@ def repack_scales(scale: torch.Tensor, out: torch.Tensor | None = None) -> Packe
         raise ValueError("repack_scales: `out` must be a contiguous uint8 tensor of at least packed_scale_bytes(rows, K)")
     dev_index = scale.device.index
     if dev_index is None or dev_index == torch.cuda.current_device():
-        rc = lib.wb200_repack_scales(scale.data_ptr(), scale.stride(0), rows, K, out.data_ptr(), _stream())
+        rc = lib.wb200_repack_scales(scale.data_ptr(), row_stride, rows, K, out.data_ptr(), _stream())
     else:
         with torch.cuda.device(scale.device):
-            rc = lib.wb200_repack_scales(scale.data_ptr(), scale.stride(0), rows, K, out.data_ptr(), _stream())
+            rc = lib.wb200_repack_scales(scale.data_ptr(), row_stride, rows, K, out.data_ptr(), _stream())
     if rc:
         _lib.check(rc)
     return PackedScales(out, rows, K)
@@ -117,6 +118,7 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
         raise ValueError(f"a and b disagree on K: {K} vs {b.shape[1] * 2}")
     if (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
         raise ValueError("packed scales do not match the operand shapes")
+    ldc = c.stride(0) if M > 1 else N  # the stride of a size-1 dimension is arbitrary
     ws_bytes = ws_ptr = 0
     if M <= 128:
         ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
@@ -124,11 +126,11 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
     dev_index = a.device.index
     if dev_index is None or dev_index == torch.cuda.current_device():
         rc = lib.wb200_mxfp4_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
-                                  c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0), ws_ptr, ws_bytes, flags, _stream())
+                                  c.data_ptr(), _DTYPE_CODE[c.dtype], ldc, ws_ptr, ws_bytes, flags, _stream())
     else:
         with torch.cuda.device(a.device):
             rc = lib.wb200_mxfp4_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
-                                      c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0), ws_ptr, ws_bytes, flags, _stream())
+                                      c.data_ptr(), _DTYPE_CODE[c.dtype], ldc, ws_ptr, ws_bytes, flags, _stream())
     if rc:
         _lib.check(rc)
 
@@ -182,7 +184,7 @@ def quantize_mxfp4(x: torch.Tensor, want_rowmajor: bool = True, want_packed: boo
     s_rm = torch.empty(rows, K // SCALE_GROUP_SIZE, dtype=torch.uint8, device=x.device) if want_rowmajor else None
     s_pk = torch.empty(packed_scale_bytes(rows, K), dtype=torch.uint8, device=x.device) if want_packed else None
     with torch.cuda.device(x.device):
-        _lib.check(lib.wb200_quantize_mxfp4(x.data_ptr(), _DTYPE_CODE[x.dtype], x.stride(0), rows, K, q.data_ptr(),
+        _lib.check(lib.wb200_quantize_mxfp4(x.data_ptr(), _DTYPE_CODE[x.dtype], x.stride(0) if rows > 1 else K, rows, K, q.data_ptr(),
                                             s_rm.data_ptr() if want_rowmajor else None,
                                             s_pk.data_ptr() if want_packed else None, _stream()))
     return q, s_rm, (PackedScales(s_pk, rows, K) if want_packed else None)

@@ -1,0 +1,85 @@
+"""Shape-sweep benchmark of the MXFP4 scaled GEMM: `python -m wave_b200.perf [--validate] [--csv out.csv]`.
+
+Same bookkeeping as the reference's benchmark driver (wave_lang/kernel/wave/perf/benchmark_mxfp4.py):
+flops = 2 M N K (:78-79), bytes = M K/2 + M K/32 + N K/2 + N K/32 + M N sizeof(c) (:82-85), TFLOP/s from the
+mean device time of `iters` back-to-back launches between two CUDA events (:117-138), optional
+validation of every shape against a reference GEMM before timing (:163-177). The reference sweeps a
+CSV of 167 shapes with K = 16000; here the grid is generated: M in {512 .. 8192}, N in {512 .. 32768},
+K = 16000 (not a multiple of the 256-element pipeline stage, so every shape exercises the K tail),
+plus the decode and square shapes used elsewhere in this repository. Inputs are the seeded random
+codes of `generate_gemm_afp4wfp4_inputs`.
+"""
+
+from __future__ import annotations
+
+import argparse
+import csv
+import sys
+
+import torch
+
+
+def get_flops(M: int, N: int, K: int) -> int:
+    return 2 * M * N * K
+
+
+def get_byte_count_mxfp4(M: int, N: int, K: int, c_bytes: int = 2) -> int:
+    return M * K // 2 + M * K // 32 + N * K // 2 + N * K // 32 + M * N * c_bytes
+
+
+def runtime_us_to_tflops(M: int, N: int, K: int, us: float) -> float:
+    return get_flops(M, N, K) / (us * 1e-6) / 1e12
+
+
+def default_shapes():
+    shapes = [(M, N, 16000) for M in (512, 1024, 2048, 4096, 8192) for N in (512, 2048, 8192, 32768)]
+    shapes += [(1024, 1024, 1024), (4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384)]
+    shapes += [(M, 28672, 8192) for M in (1, 16, 64, 128)]
+    return shapes
+
+
+def time_shape(M, N, K, out_dtype=torch.bfloat16, iters: int = 20, validate: bool = False, device="cuda:0"):
+    """Mean device microseconds per launch of the GEMM alone (scales packed beforehand)."""
+    from . import generate_gemm_afp4wfp4_inputs, ops
+    x, w, xs, ws = generate_gemm_afp4wfp4_inputs((M, N, K), device=torch.device(device))
+    w_t = w.T.contiguous()
+    a_sf, b_sf = ops.repack_scales(xs), ops.repack_scales(ws)
+    c = torch.empty(M, N, dtype=out_dtype, device=device)
+    for _ in range(3):
+        ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c)
+    if validate:
+        # row-sampled check against the dequantised f32 product computed by torch on the GPU
+        rows = torch.arange(0, M, max(1, M // 64), device=device)
+        ref = ops.dequant_mxfp4(x[rows].contiguous(), xs[rows].contiguous()) @ ops.dequant_mxfp4(w_t, ws).T
+        torch.testing.assert_close(c[rows].float(), ref, rtol=2e-2, atol=1e-2 * float(ref.abs().max()))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c)
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--validate", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--csv", default=None)
+    args = ap.parse_args(argv)
+    rows = []
+    for M, N, K in default_shapes():
+        us = time_shape(M, N, K, iters=args.iters, validate=args.validate)
+        rows.append(dict(M=M, N=N, K=K, runtime_us=round(us, 2), tflops=round(runtime_us_to_tflops(M, N, K, us), 1),
+                         gbytes_per_s=round(get_byte_count_mxfp4(M, N, K) / us / 1e3, 1)))
+        print(rows[-1], flush=True)
+    if args.csv:
+        with open(args.csv, "w", newline="") as f:
+            wr = csv.DictWriter(f, fieldnames=list(rows[0]))
+            wr.writeheader()
+            wr.writerows(rows)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
