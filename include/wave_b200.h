@@ -50,6 +50,7 @@ extern "C" {
 #define WB200_PATH_SKINNY 3u      /* M <= 128: swapped operands, stream-K, needs a workspace */
 #define WB200_PATH_MASK 0xFu
 #define WB200_TILE_N128 0x10u     /* force BN = 128 (default 256 for the tile paths) */
+#define WB200_TILE_N192 0x40u     /* force BN = 192: both accumulators fit tensor memory without sharing columns */
 #define WB200_ACCUMULATE 0x20u    /* c += a * b^T: the split-K templates' contract, which adds into a
                                      caller-initialised c (tagged_mxfp4_gemm.py:780-781, 830-831) */
 

@@ -162,7 +162,8 @@ def test_config1_1024_cubed_wide_scales_f32():
 # every kernel path, ragged and aligned shapes, both output types
 # ---------------------------------------------------------------------------------------------
 TILE_PATHS = [_lib.PATH_TILE_1CTA, _lib.PATH_TILE_1CTA | _lib.TILE_N128, _lib.PATH_TILE_2CTA,
-              _lib.PATH_TILE_2CTA | _lib.TILE_N128]
+              _lib.PATH_TILE_2CTA | _lib.TILE_N128, _lib.PATH_TILE_1CTA | _lib.TILE_N192,
+              _lib.PATH_TILE_2CTA | _lib.TILE_N192]
 
 
 @pytest.mark.parametrize("flags", TILE_PATHS)
@@ -196,9 +197,13 @@ def test_many_tiles_per_cta_and_accumulator_reuse():
     M, N, K = 2048, 6144, 512
     a, a_s, b, b_s = random_problem(M, N, K, seed=99)
     ref = orc.scaled_gemm(a, a_s, b, b_s)
+    ad, bd = a.to(DEV), b.to(DEV)
+    asp, bsp = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
     for flags in TILE_PATHS:
-        c = run(a, a_s, b, b_s, torch.bfloat16, path=flags & 0xF)
-        check(c, a, a_s, b, b_s, ref=ref)
+        for out_dtype in (torch.bfloat16, torch.float32):
+            c = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+            ops.scaled_gemm_packed(ad, asp, bd, bsp, c, flags)
+            check(c, a, a_s, b, b_s, ref=ref)
 
 
 def test_output_column_block_with_row_pitch():

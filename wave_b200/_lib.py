@@ -28,6 +28,7 @@ PATH_TILE_1CTA = 1
 PATH_TILE_2CTA = 2
 PATH_SKINNY = 3
 TILE_N128 = 0x10
+TILE_N192 = 0x40
 ACCUMULATE = 0x20
 
 # Every symbol include/wave_b200.h declares; tests check that the built library exports them all.

@@ -207,7 +207,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   if (rc) return rc;
   rc = make_scale_map(&maps.m[2], as, sfa_row_blocks, wb::sf_k_atoms(K), 1);
   if (rc) return rc;
-  rc = make_scale_map(&maps.m[3], bs, sfb_row_blocks, wb::sf_k_atoms(K), BN / 128);
+  rc = make_scale_map(&maps.m[3], bs, sfb_row_blocks, wb::sf_k_atoms(K), Cfg::SFB_BLOCKS);
   if (rc) return rc;
   wb::GemmParams p;
   p.c = c;
@@ -259,14 +259,16 @@ int launch_tile_dtype(int c_dtype, const DeviceInfo& dev, int M, int N, int K, c
   return launch_tile<CG, BN, __nv_bfloat16>(dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
 }
 
-int dispatch_tile(unsigned path, bool n128, int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a,
+int dispatch_tile(unsigned path, int bn, int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a,
                   const void* as, const void* b, const void* bs, void* c, long long ldc, int sfa_rb, int sfb_rb,
                   int accumulate, cudaStream_t stream) {
   if (path == WB200_PATH_TILE_2CTA) {
-    if (n128) return launch_tile_dtype<2, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    if (bn == 128) return launch_tile_dtype<2, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    if (bn == 192) return launch_tile_dtype<2, 192>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
     return launch_tile_dtype<2, 256>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
   }
-  if (n128) return launch_tile_dtype<1, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+  if (bn == 128) return launch_tile_dtype<1, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+  if (bn == 192) return launch_tile_dtype<1, 192>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
   return launch_tile_dtype<1, 256>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
 }
 
@@ -598,9 +600,9 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   unsigned path = flags & WB200_PATH_MASK;
-  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE)) != 0) return fail(WB200_ERR_INVALID_ARG, "unknown flag bits %#x", flags);
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_TILE_N192 | WB200_ACCUMULATE)) != 0) return fail(WB200_ERR_INVALID_ARG, "unknown flag bits %#x", flags);
   if (path > WB200_PATH_SKINNY) return fail(WB200_ERR_INVALID_ARG, "unknown path flag %u", path);
-  const bool n128_forced = (flags & WB200_TILE_N128) != 0;
+  if ((flags & WB200_TILE_N128) && (flags & WB200_TILE_N192)) return fail(WB200_ERR_INVALID_ARG, "two tile widths forced at once");
   const int accumulate = (flags & WB200_ACCUMULATE) ? 1 : 0;
   if (path == WB200_PATH_AUTO) {
     const bool ws_ok = workspace && workspace_bytes >= skinny_workspace_bytes(dev->sm_count, M);
@@ -619,12 +621,21 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
     return dispatch_skinny<__nv_bfloat16>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, accumulate, s);
   }
   // Narrow problems fill more SMs with 128-wide tiles.
-  bool n128 = n128_forced;
-  if (!n128_forced && (flags & WB200_PATH_MASK) == WB200_PATH_AUTO) {
+  int bn = (flags & WB200_TILE_N128) ? 128 : (flags & WB200_TILE_N192) ? 192 : 256;
+  if (!(flags & (WB200_TILE_N128 | WB200_TILE_N192)) && (flags & WB200_PATH_MASK) == WB200_PATH_AUTO) {
     const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
-    if (tiles256 < dev->sm_count) n128 = true;
+    if (tiles256 < dev->sm_count) {
+      bn = 128;
+    } else if (path == WB200_PATH_TILE_2CTA) {
+      // 192-wide tiles cost ~4 % more per column (more operand traffic per flop, measured on
+      // large shapes) but can fill the last wave of CTA pairs better: compare whole waves.
+      const long long units = dev->sm_count / 2, tm = (M + 255) / 256;
+      const long long w256 = (tm * ((N + 255) / 256) + units - 1) / units * 256;
+      const long long w192 = (tm * ((N + 191) / 192) + units - 1) / units * 192;
+      if (w192 * 1045 < w256 * 1000) bn = 192;
+    }
   }
-  return dispatch_tile(path, n128, c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc,
+  return dispatch_tile(path, bn, c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc,
                        wb::sf_row_blocks(M), wb::sf_row_blocks(N), accumulate, s);
 }
 
@@ -703,7 +714,7 @@ int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* 
     rc = check_common(Mg, N, K, ag, asg, b_ptrs[g], b_scale_ptrs[g], cg, c_dtype, ldc);
     if (rc) return rc;
     const unsigned path = (Mg > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
-    rc = dispatch_tile(path, false, c_dtype, *dev, Mg, N, K, ag, asg, b_ptrs[g], b_scale_ptrs[g], cg, ldc,
+    rc = dispatch_tile(path, 256, c_dtype, *dev, Mg, N, K, ag, asg, b_ptrs[g], b_scale_ptrs[g], cg, ldc,
                        wb::sf_row_blocks(Mg), wb::sf_row_blocks(N), 0, static_cast<cudaStream_t>(stream));
     if (rc) return rc;
   }

@@ -17,7 +17,8 @@
 //   * two accumulators live in tensor memory so that the epilogue of tile i overlaps the main
 //     loop of tile i+1. With BN = 256 the two accumulators overlap by 48 columns (512 columns
 //     cannot hold 2 x 256 plus the scale factors); the epilogue drains the shared columns first
-//     and releases the next main loop as soon as they are free;
+//     and releases the next main loop as soon as they are free. With BN = 192 both accumulators
+//     and the scale factors fit side by side and no hand-over wait remains;
 //   * CG = 2 pairs two CTAs of a cluster on one 256-row tile (cta_group::2): each CTA loads its
 //     own 128 rows of A and its half of the B rows with plain TMA loads (no multicast); the loads
 //     of both CTAs complete on the leader CTA's barrier, and the leader issues the MMAs.
@@ -36,7 +37,12 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * 128;
   static constexpr int B_BYTES = B_ROWS * 128;
   static constexpr int SFA_BYTES = 2 * 512;               // 128 rows x 8 K-blocks
-  static constexpr int SFB_BYTES = (BN / 128) * 2 * 512;  // BN rows x 8 K-blocks
+  // Packed scales come in blocks of 128 rows = 4 tensor-memory columns of 32 rows each. A 192-row
+  // tile starts at column 0 or 2 of a block and ends inside the next one: the kernel loads both
+  // blocks and points the MMA at the column the tile starts with. (The MMA takes even column
+  // offsets only: an odd one, as a 224-row tile would need, raises a misaligned-address fault.)
+  static constexpr int SFB_BLOCKS = (BN % 128 == 0) ? BN / 128 : (BN + 64 + 127) / 128;
+  static constexpr int SFB_BYTES = SFB_BLOCKS * 2 * 512;  // blocks x 8 K-blocks
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   // Epilogue staging: each of the 4 epilogue warps owns two buffers of 32 rows x 32 columns of C,
   // written with the TMA store swizzle (64-byte rows for bf16, 128-byte rows for f32).
@@ -56,16 +62,17 @@ struct GemmCfg {
   static constexpr int ACC_COL0 = 0;
   // Scale factors live in a small ring of column sets so that the tcgen05.cp of one K block does
   // not have to wait for the MMAs of the previous block to finish reading theirs.
-  static constexpr int SF_SET_COLS = 8 + BN / 16;  // A: 2 atoms x 4 columns, B: (BN/128) x 2 atoms x 4
+  static constexpr int SF_SET_COLS = 8 + SFB_BLOCKS * 8;  // A: 2 atoms x 4 columns, B: blocks x 2 atoms x 4
   static constexpr int SF_SETS = OVERLAP ? 2 : 4;
-  static constexpr int SF_COL = OVERLAP ? 512 - SF_SETS * SF_SET_COLS : 256;
+  static constexpr int SF_COL = OVERLAP ? 512 - SF_SETS * SF_SET_COLS : 2 * BN;
   // 32-column chunks shared by the two accumulators: accumulator 1 ends where the scale factors begin
   static constexpr int OVERLAP_CHUNKS = (2 * 256 - SF_COL + 31) / 32;
   static constexpr int ACC_COL1 = OVERLAP ? SF_COL - 256 : BN;
   static_assert(SF_COL + SF_SETS * SF_SET_COLS <= 512, "scale-factor ring does not fit in tensor memory");
-  static_assert(OVERLAP_CHUNKS % 2 == 0, "bf16 stores pair neighbouring chunks; the shared columns must be whole pairs");
+  static_assert(!OVERLAP || OVERLAP_CHUNKS % 2 == 0, "bf16 stores pair neighbouring chunks; the shared columns must be whole pairs");
   static constexpr int THREADS = 192;
-  static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
+  static_assert(BN == 128 || BN == 192 || BN == 256, "BN must be 128, 192 or 256");
+  static_assert(BN % 64 == 0, "tiles start on even scale columns and are stored as whole pairs of 32-column chunks");
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 };
 
@@ -289,7 +296,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
       const int a_row = (mt * CG + int(rank)) * Cfg::BM;
       const int b_row = nt * BN + int(rank) * Cfg::B_ROWS;
       const int sfa_rb = mt * CG + int(rank);
-      const int sfb_rb = nt * (BN / 128);
+      const int sfb_rb = (nt * BN) / 128;
       for (int kb = 0; kb < num_kb; ++kb) {
         mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
         const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
@@ -321,6 +328,13 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
       int it = 0;
       for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
         const int as = it & 1;
+        // first 32-row group of this tile inside its first 128-row scale block = first scale column (0 or 2)
+        uint32_t sfb_group = 0;
+        if constexpr (BN % 128 != 0) {
+          int mt, nt, rows;
+          decode_tile(maps, p, t, mt, nt, rows);
+          sfb_group = uint32_t((nt * BN) % 128) / 32u;
+        }
         // accumulator availability
         if constexpr (Cfg::OVERLAP) {
           // Needs the previous tile's epilogue to have drained the 48 shared columns
@@ -356,10 +370,10 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
 #pragma unroll
               for (int a = 0; a < 2; ++a) utccp_sf_atom<CG>(t_sfa + a * 4, sfa_desc + uint64_t(a * 32));
 #pragma unroll
-              for (int j = 0; j < BN / 128; ++j)
+              for (int j = 0; j < Cfg::SFB_BLOCKS; ++j)
 #pragma unroll
                 for (int a = 0; a < 2; ++a)
-                  utccp_sf_atom<CG>(t_sfb + a * (BN / 32) + j * 4, sfb_desc + uint64_t(j * 64 + a * 32));
+                  utccp_sf_atom<CG>(t_sfb + a * (Cfg::SFB_BLOCKS * 4) + j * 4, sfb_desc + uint64_t(j * 64 + a * 32));
             }
             {
 #pragma unroll
@@ -367,7 +381,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
                 // K = 64 per instruction = 32 bytes inside the 128-byte swizzle row
                 mma_mxf4<CG>(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2),
                              idesc_with_sf_id(idesc, (k & 1) * 2), t_sfa + (k >> 1) * 4,
-                             t_sfb + (k >> 1) * (BN / 32), (kb > 0 || k > 0) ? 1u : 0u);
+                             t_sfb + (k >> 1) * (Cfg::SFB_BLOCKS * 4) + sfb_group, (kb > 0 || k > 0) ? 1u : 0u);
               }
             }
             // free the stage in both CTAs once these MMAs have read it
@@ -393,6 +407,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     // C is written once and not read again by this kernel: keep it from pushing A and B out of L2
     const uint64_t store_policy = l2_policy_evict_first();
     int it = 0;
+    uint32_t store_count = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       int mt, nt, rows;
       const CUtensorMap* tm = decode_tile(maps, p, t, mt, nt, rows);
@@ -434,8 +449,8 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
           // chunk order above keeps pairs together). Before a buffer is refilled, the store issued
           // two stores ago must have read it.
           constexpr int PER_STORE = (sizeof(OutT) == 2) ? 2 : 1;
-          const int si = ci / PER_STORE, half = ci % PER_STORE;
-          const uint32_t buf = stg + uint32_t(si & 1) * Cfg::STORE_BUF_BYTES;
+          const int half = ci % PER_STORE;
+          const uint32_t buf = stg + (store_count & 1u) * Cfg::STORE_BUF_BYTES;
           if (half == 0) {
             if (lane == 0) bulk_wait_group_read<1>();
             __syncwarp();
@@ -452,6 +467,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
               if (row0 < rows && scol < p.N) tma_store_2d_hint(tm + 4, buf, scol, row0, store_policy);
               bulk_commit_group();
             }
+            ++store_count;  // the buffers alternate store by store, across tiles too
           }
         } else if (row < rows && col < p.N) {
           OutT* dst = C + size_t(row) * p.ldc + col;
