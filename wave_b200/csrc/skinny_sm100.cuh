@@ -15,7 +15,8 @@
 //     once at full bandwidth;
 //   * a CTA whose run covers a whole tile writes C directly; otherwise it writes an f32 partial
 //     to the workspace and bumps the tile's counter; the CTA that arrives last adds the partials
-//     in CTA order, converts once and writes C. Nobody spins on another CTA.
+//     in CTA order, converts once and writes C. A CTA that finds all other contributions already
+//     published skips the write of its own. Nobody spins on another CTA.
 #pragma once
 #include "ptx.cuh"
 #include <cuda_bf16.h>
@@ -90,6 +91,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::NUM_BARRIERS * 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* last_flag = tmem_slot + 2;
+  volatile uint32_t* known_last_flag = tmem_slot + 3;
   WaitCtx ctx{abort_flag, p.status};
 
   if (threadIdx.x == 0) {
@@ -223,17 +225,75 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const int quad = warp & 3;
     const int nl = quad * 32 + lane;  // weight row inside the tile
     OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
+    auto store_out = [&](int m, int n, float v) {
+      OutT* dst = C + size_t(m) * p.ldc + n;
+      if constexpr (sizeof(OutT) == 4) {
+        if (p.accumulate) v += *dst;
+        *dst = v;
+      } else {
+        if (p.accumulate) v += __bfloat162float(*dst);
+        *dst = __float2bfloat16_rn(v);
+      }
+    };
+    // workspace slot of contributor CTA c for `tile`: slot 0 of a CTA holds its first tile, slot 1 its last
+    auto slot_of = [&](int c, int tile) {
+      int a0, a1;
+      skinny_range(total_units, gridDim.x, c, a0, a1);
+      return 2 * c + ((a0 / p.num_kb) == tile ? 0 : 1);
+    };
     for (int seg = 0; seg < nseg; ++seg) {
       int tile, kbs, kbe;
       segment(seg, tile, kbs, kbe);
       const int as = seg & 1;
       const int n = tile * 128 + nl;
       const bool whole = (kbs == 0 && kbe == p.num_kb);
+      float* part = p.partials + (size_t(2 * blockIdx.x + (tile == first_tile ? 0 : 1)) * p.M) * 128 + nl;
+
+      // A partial segment: who else contributes to this tile, and have they all published already?
+      // If so this CTA is certainly the last one: it keeps its own partial in registers, adds the
+      // others' (fetched while the MMAs of this segment still run) and writes C, without the round
+      // trip of publishing its own partial first. That is the usual case for the segment a CTA
+      // ends with, whose other half was finished early in the neighbour's run.
+      int c_lo = 0, ncontrib = 1;
+      bool known_last = false;
+      // the first two other contributors' first 16 rows are fetched ahead
+      float pre0[16], pre1[16];
+      int other0 = -1, other1 = -1;
+      if (!whole) {
+        const int t_lo = tile * p.num_kb;
+        c_lo = skinny_owner(total_units, gridDim.x, t_lo);
+        ncontrib = skinny_owner(total_units, gridDim.x, t_lo + p.num_kb - 1) - c_lo + 1;
+        if (threadIdx.x == 64) {
+          unsigned int seen;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile) : "memory");
+          *known_last_flag = (seen == (unsigned int)(ncontrib - 1)) ? 1u : 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        known_last = (*known_last_flag != 0u);
+        if (known_last) {
+          __threadfence();
+          for (int i = 0; i < ncontrib; ++i) {
+            const int c = c_lo + i;
+            if (c == int(blockIdx.x)) continue;
+            if (other0 < 0) other0 = c;
+            else if (other1 < 0) other1 = c;
+          }
+          if (other0 >= 0) {
+            const float* src = p.partials + size_t(slot_of(other0, tile)) * p.M * 128 + nl;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) pre0[j] = (j < p.M) ? __ldcg(src + size_t(j) * 128) : 0.f;
+          }
+          if (other1 >= 0) {
+            const float* src = p.partials + size_t(slot_of(other1, tile)) * p.M * 128 + nl;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) pre1[j] = (j < p.M) ? __ldcg(src + size_t(j) * 128) : 0.f;
+          }
+        }
+      }
+
       mbar_wait(acc_full_bar(as), uint32_t(seg >> 1) & 1u, ctx, WB_DEV_TIMEOUT_EPILOGUE);
       tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (uint32_t(quad * 32) << 16) + (as ? Cfg::ACC_COL1 : 0);
-      float* part = p.partials +
-                    (size_t(2 * blockIdx.x + (tile == first_tile ? 0 : 1)) * p.M) * 128 + nl;
 #pragma unroll 1
       for (int c0 = 0; c0 < NP; c0 += 16) {
         uint32_t r[16];
@@ -247,20 +307,38 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (whole) {
           if (n < p.N) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = c0 + j;
-              if (m < p.M) {
-                OutT* dst = C + size_t(m) * p.ldc + n;
-                float v = __uint_as_float(r[j]);
-                if constexpr (sizeof(OutT) == 4) {
-                  if (p.accumulate) v += *dst;
-                  *dst = v;
-                } else {
-                  if (p.accumulate) v += __bfloat162float(*dst);
-                  *dst = __float2bfloat16_rn(v);
-                }
+            for (int j = 0; j < 16; ++j)
+              if (c0 + j < p.M) store_out(c0 + j, n, __uint_as_float(r[j]));
+          }
+        } else if (known_last) {
+          // contributions are added in CTA order, this CTA's own from registers
+          if (n < p.N && c0 < p.M) {
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+            for (int i = 0; i < ncontrib; ++i) {
+              const int c = c_lo + i;
+              if (c == int(blockIdx.x)) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] += __uint_as_float(r[j]);
+              } else if (c0 == 0 && c == other0) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] += pre0[j];
+              } else if (c0 == 0 && c == other1) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] += pre1[j];
+              } else {
+                const float* src = p.partials + (size_t(slot_of(c, tile)) * p.M + c0) * 128 + nl;
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = (c0 + j < p.M) ? __ldcg(src + size_t(j) * 128) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] += v[j];
               }
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c0 + j < p.M) store_out(c0 + j, n, acc[j]);
           }
         } else {
 #pragma unroll
@@ -270,16 +348,17 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           }
         }
       }
-      if (!whole) {
+      if (!whole && known_last) {
+        // every other contributor has come and gone: leave the counter clean for the next launch
+        if (threadIdx.x == 64) p.counters[tile] = 0u;
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // known_last_flag is reused by the next segment
+      } else if (!whole) {
         // publish the partial, then find out whether this CTA completes the tile
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int t_lo = tile * p.num_kb;
-        const int c_lo = skinny_owner(total_units, gridDim.x, t_lo);
-        const int c_hi = skinny_owner(total_units, gridDim.x, t_lo + p.num_kb - 1);
         if (threadIdx.x == 64) {
           const unsigned int prev = atomicAdd(p.counters + tile, 1u);
-          *last_flag = (prev == (unsigned int)(c_hi - c_lo)) ? 1u : 0u;
+          *last_flag = (prev == (unsigned int)(ncontrib - 1)) ? 1u : 0u;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
@@ -287,21 +366,15 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           if (n < p.N) {
             // Partials are added in CTA order (fixed, so the sum does not depend on who arrived
             // when), 16 output rows at a time so that the loads of one batch are all in flight.
-            auto slot_of = [&](int c) {
-              int a0, a1;
-              skinny_range(total_units, gridDim.x, c, a0, a1);
-              return 2 * c + ((a0 / p.num_kb) == tile ? 0 : 1);
-            };
-            const int ncontrib = c_hi - c_lo + 1;
             int slots[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) slots[i] = (i < ncontrib) ? slot_of(c_lo + i) : 0;
+            for (int i = 0; i < 4; ++i) slots[i] = (i < ncontrib) ? slot_of(c_lo + i, tile) : 0;
             for (int m0 = 0; m0 < p.M; m0 += 16) {
               float acc[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) acc[j] = 0.f;
               for (int i = 0; i < ncontrib; ++i) {
-                const int slot = (i < 4) ? slots[i & 3] : slot_of(c_lo + i);
+                const int slot = (i < 4) ? slots[i & 3] : slot_of(c_lo + i, tile);
                 const float* src = p.partials + (size_t(slot) * p.M + m0) * 128 + nl;
                 float v[16];
 #pragma unroll
@@ -310,20 +383,8 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 for (int j = 0; j < 16; ++j) acc[j] += v[j];
               }
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int m = m0 + j;
-                if (m < p.M) {
-                  OutT* dst = C + size_t(m) * p.ldc + n;
-                  float r = acc[j];
-                  if constexpr (sizeof(OutT) == 4) {
-                    if (p.accumulate) r += *dst;
-                    *dst = r;
-                  } else {
-                    if (p.accumulate) r += __bfloat162float(*dst);
-                    *dst = __float2bfloat16_rn(r);
-                  }
-                }
-              }
+              for (int j = 0; j < 16; ++j)
+                if (m0 + j < p.M) store_out(m0 + j, n, acc[j]);
             }
           }
           if (threadIdx.x == 64) p.counters[tile] = 0u;
