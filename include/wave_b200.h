@@ -81,6 +81,13 @@ size_t wb200_packed_scale_bytes(int rows, int K);
 int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int K, void* dst,
                         void* stream);
 
+/* One scale per ROW (src [rows], element pitch src_row_stride bytes, 1 when contiguous), used for every K
+ * block of that row: the a_scale [M] argument of the reference's broadcast-scale kernel
+ * get_broadcasted_scale_gemm_mxfp4 (wave_lang/kernel/wave/templates/test_kernels.py:75-140), which
+ * broadcasts it to [M, K/32] before the scaled MMA (:112-113). Output as wb200_repack_scales. */
+int wb200_repack_scales_broadcast(const void* src, long long src_row_stride, int rows, int K, void* dst,
+                                  void* stream);
+
 /* Grouped form for the per-expert GEMM: rows [row_offsets[g], row_offsets[g+1]) of src are group g;
  * its packed scales start at 128-row block row_block_offsets[g] of dst (each group on a block boundary,
  * row_block_offsets[g+1] - row_block_offsets[g] >= ceil(rows of g / 128)); one launch for up to 32
@@ -98,6 +105,39 @@ int wb200_repack_scales_grouped(const void* src, long long src_row_stride, int n
  * codes (wave_lang/kernel/wave/utils/mxfp_utils.py:20-57). */
 int wb200_quantize_mxfp4(const void* x, int x_dtype, long long ldx, int rows, int K, void* q, void* scale_rowmajor,
                          void* scale_packed, void* stream);
+
+/* ---- mixture-of-experts steps either side of wb200_mxfp4_grouped_gemm ------------------------- */
+
+/* Sort routed (token, slot) pairs by expert and pad every expert to whole blocks: the outputs of the
+ * reference's moe_align_block_size_pytorch (tests/kernel/moe/torch_kernels.py:10-97). topk_ids: DEVICE
+ * array [num_ids] of expert ids in flat (token-major) order, int32 or int64. sorted_ids [sorted_capacity]:
+ * flat indices grouped by expert, ascending inside an expert, each expert's run padded with the value
+ * num_ids to a multiple of block_size, the unused rest filled with num_ids too. expert_ids: expert of every
+ * block_size-row block. num_tokens_post_pad [1]: padded total. inverse [num_ids] (may be NULL, not in the
+ * reference): position of flat index i in sorted_ids. Capacities must cover the worst case
+ * num_ids + num_experts * (block_size - 1) entries (:116-119 of the reference's test). At most 256 experts. */
+int wb200_moe_align_block_size(const void* topk_ids, int ids_are_int64, int num_ids, int num_experts, int block_size,
+                               int* sorted_ids, int sorted_capacity, int* expert_ids, int expert_ids_capacity,
+                               int* num_tokens_post_pad, int* inverse, void* stream);
+
+/* dst[p, :] = src[sorted_ids[p] / top_k, :] when sorted_ids[p] < num_ids, else zeros: brings the packed
+ * codes (or scales) of each routed token to its sorted row. Byte rows of row_bytes; 16-byte accesses when
+ * bases, pitches and row_bytes are multiples of 16. */
+int wb200_moe_gather_rows(const void* src, long long src_pitch, int row_bytes, const int* sorted_ids, int num_rows,
+                          int num_ids, int top_k, void* dst, long long dst_pitch, void* stream);
+
+/* out = x1 / (1 + exp(-x1)) * x2 elementwise on [rows, n] matrices of f32 or bf16 (pitches in elements):
+ * get_silu_and_mul_kernel (wave_lang/kernel/wave/templates/moe.py:89-145). out may be NULL when q is
+ * given: q [rows, n/2] and the scale outputs (as wb200_quantize_mxfp4) receive the f32 result quantised
+ * to MXFP4 in the same pass, ready for the down-projection GEMM. */
+int wb200_silu_and_mul(const void* x1, const void* x2, long long ld1, long long ld2, int dtype, int rows, int n, void* out,
+                       long long ldo, void* q, void* scale_rowmajor, void* scale_packed, void* stream);
+
+/* out[t, :] = sum over j < top_k of weight[t * top_k + j] * y[row_of[t * top_k + j], :], f32 accumulation in
+ * slot order, pairs with row_of < 0 skipped: the weighted sum that ends the reference's MoE
+ * (tests/kernel/moe_test.py:123-127). y, out: f32 or bf16. */
+int wb200_moe_combine(const void* y, long long ldy, int dtype, const int* row_of, const float* weight, int tokens, int top_k,
+                      int cols, void* out, long long ldo, void* stream);
 
 /* Test aid: out[r, k] = E2M1(q) * 2^(scale - 127) as f32, the dequantised operand of
  * mxfp4_to_f32 / e8m0_to_f32 (wave_lang/kernel/wave/utils/mxfp_utils.py:60-95). */

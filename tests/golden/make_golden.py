@@ -4,9 +4,9 @@ Run in the build container, where the reference tree is mounted read-only:
 
     python tests/golden/make_golden.py /root/reference
 
-It imports the reference's own module `wave_lang/kernel/wave/utils/mxfp_utils.py` (pure torch; it
-runs on the CPU without the reference's compiler stack) and stores its outputs on seeded inputs as
-small .npz files. The tests compare the oracle in `oracle/` and, on a GPU, the CUDA kernels
+It imports the reference's own module `wave_lang/kernel/wave/utils/mxfp_utils.py` and the torch
+helper `tests/kernel/moe/torch_kernels.py` (both pure torch; they run on the CPU without the
+reference's compiler stack) and stores their outputs on seeded inputs as small .npz files. The tests compare the oracle in `oracle/` and, on a GPU, the CUDA kernels
 against these files, so the pin travels to machines that do not have the reference.
 """
 
@@ -72,6 +72,30 @@ def main(ref_root: str) -> None:
               for k, v in dict(x=x, w=w, x_scales=xs, w_scales=ws).items()}
     np.savez_compressed(HERE / "gemm_seed5_1024_sample.npz", out_sample=out[::64, ::64].numpy(),
                         **{f"sha256_{k}": np.array(v) for k, v in digest.items()})
+    # 6. Block alignment of routed tokens: the reference's own torch function
+    #    (tests/kernel/moe/torch_kernels.py, pure torch), on the shapes its test sweeps
+    #    (tests/kernel/moe/moe_align_block_size_test.py:14-17) plus a case with empty experts.
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ref_moe_torch_kernels", Path(ref_root) / "tests/kernel/moe/torch_kernels.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    store = {}
+    gen = torch.Generator().manual_seed(0)
+    cases = [(1, 2, 16, 4), (33, 2, 32, 8), (256, 2, 64, 64), (33, 2, 16, 64), (256, 2, 128, 8), (7, 3, 16, 5)]
+    for ci, (tokens, topk, block, experts) in enumerate(cases):
+        scores = torch.rand(tokens, experts, generator=gen)
+        _, topk_ids = torch.topk(scores, k=topk, dim=1)
+        cap = topk_ids.numel() + experts * (block - 1)
+        sorted_ids = torch.empty(cap, dtype=torch.int32)
+        expert_ids = torch.full((-(cap // -block),), -1, dtype=torch.int32)
+        post = torch.empty(1, dtype=torch.int32)
+        mod.moe_align_block_size_pytorch(topk_ids, experts, block, sorted_ids, expert_ids, post)
+        store[f"case{ci}_params"] = np.array([tokens, topk, block, experts])
+        store[f"case{ci}_topk_ids"] = topk_ids.numpy()
+        store[f"case{ci}_sorted_ids"] = sorted_ids.numpy()
+        store[f"case{ci}_expert_ids"] = expert_ids.numpy()
+        store[f"case{ci}_post_pad"] = post.numpy()
+    np.savez_compressed(HERE / "moe_align.npz", **store)
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 

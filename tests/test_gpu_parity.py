@@ -633,3 +633,27 @@ def test_single_row_operands_with_arbitrary_size_one_stride():
     for _ in range(2):  # first call: checked path; second: remembered-signature path
         gemm(x.to(DEV), xs_dev, w_t.to(DEV), ws.to(DEV), c)
         check_bf16(c, orc.torch_scaled_gemm_mxfp4(x, w, xs, ws))
+
+
+def test_broadcasted_scale_gemm_as_the_reference_tests_it():
+    """testBroadcastedScaleGemmMXFP4 (tests/kernel/wave_gemm_mxfp_test.py:594-634): a_scale is the first
+    column of the generated scales, shape [M]; the oracle gets it repeated along K."""
+    shape = (512, 512, 512)
+    kernel, hyper = wb.get_broadcasted_scale_gemm_mxfp4(shape, wb.ScaledMMAType.F32_16x16x128_F8F6F4)
+    options = wb.WaveCompileOptions(subs=hyper, canonicalize=True, schedule=wb.SchedulingType.NONE)
+    gemm = wb.wave_compile(wb.set_default_run_config(options), kernel)
+    x, w, x_scales, w_scales = orc.generate_gemm_afp4wfp4_inputs(shape)
+    compact = x_scales[:, 0].contiguous()
+    out = torch.zeros(shape[0], shape[1], dtype=torch.float32, device=DEV)
+    w_t = w.T.contiguous()
+    gemm(x.to(DEV), compact.to(DEV), w_t.to(DEV), w_scales.to(DEV), out)
+    full = compact.view(-1, 1).repeat(1, x_scales.shape[-1]).contiguous()
+    torch_out = orc.torch_scaled_gemm_mxfp4(x, w, full, w_scales)
+    torch.testing.assert_close(torch_out, out.cpu(), check_dtype=False)
+    check(out, x, full, w_t, w_scales, ref=torch_out)
+    # the packed form is bit-identical to packing the repeated scales, also for a strided, ragged source
+    wide = torch.randint(0, 256, (300, 3), dtype=torch.uint8)
+    got = ops.repack_scales_broadcast(wide.to(DEV)[:, 1], 1184)
+    assert torch.equal(got.data.cpu(), orc.pack_scales(wide[:, 1:2].repeat(1, 1184 // 32).contiguous()))
+    with pytest.raises(ValueError):
+        gemm(x.to(DEV), x_scales.to(DEV), w_t.to(DEV), w_scales.to(DEV), out)

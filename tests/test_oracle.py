@@ -123,3 +123,20 @@ def test_tolerance_helpers():
     assert int(orc.bf16_ulp_distance(c, ref).max()) == 0
     up = torch.tensor([[1.0078125, -2.0, -0.0]]).to(torch.bfloat16)  # 1 ulp above 1.0; -0.0 equals +0.0
     assert orc.bf16_ulp_distance(up, ref).flatten().tolist() == [1, 0, 0]
+
+
+def test_moe_align_block_size_oracle_matches_reference_outputs():
+    """oracle/moe_oracle.py against the stored outputs of the reference's moe_align_block_size_pytorch."""
+    from oracle import moe_oracle
+    g = np.load(GOLDEN / "moe_align.npz")
+    ncases = sum(1 for k in g.files if k.endswith("_params"))
+    assert ncases >= 6
+    for ci in range(ncases):
+        tokens, topk, block, experts = (int(v) for v in g[f"case{ci}_params"])
+        ref_sorted, ref_experts = g[f"case{ci}_sorted_ids"], g[f"case{ci}_expert_ids"]
+        sorted_ids, expert_ids, total, inverse = moe_oracle.moe_align_block_size(
+            g[f"case{ci}_topk_ids"], experts, block, ref_sorted.size, ref_experts.size)
+        assert total == int(g[f"case{ci}_post_pad"][0])
+        assert np.array_equal(sorted_ids, ref_sorted)
+        assert np.array_equal(expert_ids, ref_experts)
+        assert np.array_equal(sorted_ids[inverse], np.arange(tokens * topk))

@@ -39,6 +39,7 @@ EXPORTED_SYMBOLS = (
     "wb200_selftest_wait_timeout",
     "wb200_packed_scale_bytes",
     "wb200_repack_scales",
+    "wb200_repack_scales_broadcast",
     "wb200_repack_scales_grouped",
     "wb200_quantize_mxfp4",
     "wb200_mxfp4_dequant",
@@ -48,6 +49,10 @@ EXPORTED_SYMBOLS = (
     "wb200_mxfp4_gemm_repack_a",
     "wb200_mxfp4_gemm_skinny_noalloc",
     "wb200_mxfp4_grouped_gemm",
+    "wb200_moe_align_block_size",
+    "wb200_moe_gather_rows",
+    "wb200_silu_and_mul",
+    "wb200_moe_combine",
 )
 
 
@@ -91,6 +96,8 @@ def load() -> ctypes.CDLL:
     lib.wb200_packed_scale_bytes.argtypes = [c_int, c_int]
     lib.wb200_repack_scales.restype = c_int
     lib.wb200_repack_scales.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p]
+    lib.wb200_repack_scales_broadcast.restype = c_int
+    lib.wb200_repack_scales_broadcast.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p]
     lib.wb200_repack_scales_grouped.restype = c_int
     lib.wb200_repack_scales_grouped.argtypes = [c_void_p, c_ll, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int,
                                                 c_void_p, c_void_p]
@@ -115,6 +122,17 @@ def load() -> ctypes.CDLL:
     lib.wb200_mxfp4_grouped_gemm.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, c_int,
                                              c_void_p, c_void_p, ctypes.POINTER(c_void_p),
                                              ctypes.POINTER(c_void_p), c_void_p, c_int, c_ll, c_void_p]
+    lib.wb200_moe_align_block_size.restype = c_int
+    lib.wb200_moe_align_block_size.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                               c_void_p, c_void_p, c_void_p]
+    lib.wb200_moe_gather_rows.restype = c_int
+    lib.wb200_moe_gather_rows.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_ll, c_void_p]
+    lib.wb200_silu_and_mul.restype = c_int
+    lib.wb200_silu_and_mul.argtypes = [c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p,
+                                       c_void_p, c_void_p, c_void_p]
+    lib.wb200_moe_combine.restype = c_int
+    lib.wb200_moe_combine.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_ll,
+                                      c_void_p]
     _lib = lib
     return lib
 

@@ -174,6 +174,11 @@ class ScaledGemmKernel:
         M, N, K = a.shape[0], b.shape[0], a.shape[1] * 2
         if self._static is not None and self._static != (M, N, K):
             raise ValueError(f"kernel was built for (M, N, K) = {self._static}, called with {(M, N, K)}")
+        if t.broadcast_a_scale:
+            ops._as_u8(a_scale, "a_scale")
+            if tuple(a_scale.shape) != (M,):
+                raise ValueError(f"a_scale must be [{M}] (one scale per row), got {tuple(a_scale.shape)}")
+            a_scale = ops.repack_scales_broadcast(a_scale, K, out=self._a_scale_buffer(a.device, M, K))
         if t.preshuffled_scales and not (isinstance(a_scale, ops.PackedScales) and isinstance(b_scale, ops.PackedScales)):
             raise ValueError(f"{t.name} takes pre-shuffled scales: pass mxfp_utils.e8m0_shuffle(scale) for a_scale and b_scale")
         flags = self.options.kernel_path
@@ -230,8 +235,12 @@ class ScaledGemmKernel:
 def wave_compile(options: WaveCompileOptions, kernel, schedule=None) -> ScaledGemmKernel:
     """wave_lang/kernel/wave/compile.py:1021: (options, kernel[, schedule]) -> callable.
     `schedule` objects from wave_b200.schedules are accepted and have no effect."""
+    from .moe import SiluAndMulKernel, SiluAndMulTemplate
     from .templates import ScaledGemmTemplate
 
+    if isinstance(kernel, SiluAndMulTemplate):
+        _lib.load()
+        return SiluAndMulKernel(kernel, options)
     if not isinstance(kernel, ScaledGemmTemplate):
         raise TypeError("wave_compile here only compiles the MXFP4 scaled-GEMM templates of wave_b200.templates")
     validate_options(options)

@@ -3,6 +3,7 @@
 // (wave_lang/kernel/wave/runtime/runtime.cpp:123-263) for the MXFP4 scaled-GEMM kernels.
 #include "../../include/wave_b200.h"
 #include "gemm_sm100.cuh"
+#include "moe.cuh"
 #include "quantize.cuh"
 #include "scales.cuh"
 #include "skinny_sm100.cuh"
@@ -475,11 +476,13 @@ size_t wb200_packed_scale_bytes(int rows, int K) {
   return wb::sf_packed_bytes(rows, K);
 }
 
-int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int K, void* dst, void* stream) {
+static int repack_scales_impl(const void* src, long long src_row_stride, int rows, int K, void* dst, void* stream,
+                              bool broadcast) {
   if (rows <= 0 || K <= 0 || K % 32 != 0)
     return fail(WB200_ERR_INVALID_ARG, "repack_scales: rows = %d, K = %d (K must be a positive multiple of 32)", rows, K);
   if (!src || !dst) return fail(WB200_ERR_INVALID_ARG, "repack_scales: null pointer");
-  if (src_row_stride < K / 32) return fail(WB200_ERR_INVALID_ARG, "repack_scales: row stride %lld < K/32 = %d", src_row_stride, K / 32);
+  if (src_row_stride < (broadcast ? 1 : K / 32))
+    return fail(WB200_ERR_INVALID_ARG, "repack_scales: row stride %lld < %d", src_row_stride, broadcast ? 1 : K / 32);
   if (reinterpret_cast<uintptr_t>(dst) & 15) return fail(WB200_ERR_ALIGNMENT, "repack_scales: dst must be 16-byte aligned");
   DeviceInfo* dev;
   int rc = get_device(&dev);
@@ -487,9 +490,17 @@ int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int
   const int k_atoms = wb::sf_k_atoms(K);
   dim3 grid((k_atoms + 7) / 8, wb::sf_row_blocks(rows));
   wb::repack_scales_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint8_t*>(src), src_row_stride, rows, K / 32, k_atoms, static_cast<uint8_t*>(dst));
+      static_cast<const uint8_t*>(src), src_row_stride, rows, K / 32, k_atoms, static_cast<uint8_t*>(dst), broadcast);
   WB_CUDA(cudaGetLastError());
   return WB200_OK;
+}
+
+int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int K, void* dst, void* stream) {
+  return repack_scales_impl(src, src_row_stride, rows, K, dst, stream, false);
+}
+
+int wb200_repack_scales_broadcast(const void* src, long long src_row_stride, int rows, int K, void* dst, void* stream) {
+  return repack_scales_impl(src, src_row_stride, rows, K, dst, stream, true);
 }
 
 int wb200_repack_scales_grouped(const void* src, long long src_row_stride, int num_groups, const int* row_offsets,
@@ -556,6 +567,129 @@ int wb200_quantize_mxfp4(const void* x, int x_dtype, long long ldx, int rows, in
     wb::quantize_mxfp4_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(x), ldx, rows, K, static_cast<uint8_t*>(q), static_cast<uint8_t*>(scale_rowmajor),
         static_cast<uint8_t*>(scale_packed), k_atoms);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+int wb200_moe_align_block_size(const void* topk_ids, int ids_are_int64, int num_ids, int num_experts, int block_size,
+                               int* sorted_ids, int sorted_capacity, int* expert_ids, int expert_ids_capacity,
+                               int* num_tokens_post_pad, int* inverse, void* stream) {
+  if (num_ids < 0 || num_experts <= 0 || block_size <= 0)
+    return fail(WB200_ERR_INVALID_ARG, "moe_align_block_size: num_ids = %d, num_experts = %d, block_size = %d", num_ids,
+                num_experts, block_size);
+  if (num_experts > wb::kMoeMaxExperts)
+    return fail(WB200_ERR_UNSUPPORTED, "moe_align_block_size: at most %d experts (got %d)", wb::kMoeMaxExperts, num_experts);
+  if ((!topk_ids && num_ids > 0) || !sorted_ids || !expert_ids || !num_tokens_post_pad)
+    return fail(WB200_ERR_INVALID_ARG, "moe_align_block_size: null pointer");
+  const long long worst = (long long)num_ids + (long long)num_experts * (block_size - 1);
+  if (sorted_capacity < worst || (long long)expert_ids_capacity * block_size < worst)
+    return fail(WB200_ERR_INVALID_ARG,
+                "moe_align_block_size: sorted_ids needs %lld entries and expert_ids %lld (got %d and %d)", worst,
+                (worst + block_size - 1) / block_size, sorted_capacity, expert_ids_capacity);
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (ids_are_int64)
+    wb::moe_align_block_size_kernel<long long><<<1, 1024, 0, s>>>(static_cast<const long long*>(topk_ids), num_ids, num_experts,
+                                                                  block_size, sorted_capacity, sorted_ids, expert_ids,
+                                                                  num_tokens_post_pad, inverse);
+  else
+    wb::moe_align_block_size_kernel<int><<<1, 1024, 0, s>>>(static_cast<const int*>(topk_ids), num_ids, num_experts, block_size,
+                                                            sorted_capacity, sorted_ids, expert_ids, num_tokens_post_pad,
+                                                            inverse);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+int wb200_moe_gather_rows(const void* src, long long src_pitch, int row_bytes, const int* sorted_ids, int num_rows,
+                          int num_ids, int top_k, void* dst, long long dst_pitch, void* stream) {
+  if (num_rows < 0 || row_bytes <= 0 || top_k <= 0 || num_ids < 0)
+    return fail(WB200_ERR_INVALID_ARG, "moe_gather_rows: num_rows = %d, row_bytes = %d, top_k = %d", num_rows, row_bytes, top_k);
+  if (num_rows == 0) return WB200_OK;
+  if (!src || !sorted_ids || !dst) return fail(WB200_ERR_INVALID_ARG, "moe_gather_rows: null pointer");
+  const int vec = !(row_bytes % 16 || src_pitch % 16 || dst_pitch % 16 || (reinterpret_cast<uintptr_t>(src) & 15) ||
+                    (reinterpret_cast<uintptr_t>(dst) & 15));
+  if (src_pitch < row_bytes || dst_pitch < row_bytes) return fail(WB200_ERR_INVALID_ARG, "moe_gather_rows: pitch smaller than a row");
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  wb::moe_gather_rows_kernel<<<(num_rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), src_pitch, row_bytes, sorted_ids, num_rows, num_ids, top_k,
+      static_cast<uint8_t*>(dst), dst_pitch, vec);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+extern "C++" {
+template <typename T>
+static int launch_silu(const void* x1, const void* x2, long long ld1, long long ld2, int rows, int n, void* out, long long ldo,
+                       void* q, void* scale_rm, void* scale_packed, int k_atoms, cudaStream_t s) {
+  auto ok = [&](const void* p, long long ld) { return (reinterpret_cast<uintptr_t>(p) % (4 * sizeof(T))) == 0 && ld % 4 == 0; };
+  const bool vec = ok(x1, ld1) && ok(x2, ld2) && (!out || ok(out, ldo));
+  const long long threads = (long long)rows * ((n + 31) / 32) * 8;
+  const unsigned blocks = unsigned((threads + 255) / 256);
+  if (vec)
+    wb::silu_and_mul_kernel<T, true><<<blocks, 256, 0, s>>>(static_cast<const T*>(x1), static_cast<const T*>(x2), ld1, ld2, rows,
+                                                            n, static_cast<T*>(out), ldo, static_cast<uint8_t*>(q),
+                                                            static_cast<uint8_t*>(scale_rm),
+                                                            static_cast<uint8_t*>(scale_packed), k_atoms);
+  else
+    wb::silu_and_mul_kernel<T, false><<<blocks, 256, 0, s>>>(static_cast<const T*>(x1), static_cast<const T*>(x2), ld1, ld2,
+                                                             rows, n, static_cast<T*>(out), ldo, static_cast<uint8_t*>(q),
+                                                             static_cast<uint8_t*>(scale_rm),
+                                                             static_cast<uint8_t*>(scale_packed), k_atoms);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+}  // extern "C++"
+
+int wb200_silu_and_mul(const void* x1, const void* x2, long long ld1, long long ld2, int dtype, int rows, int n, void* out,
+                       long long ldo, void* q, void* scale_rowmajor, void* scale_packed, void* stream) {
+  if (rows <= 0 || n <= 0) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: rows = %d, n = %d", rows, n);
+  if (!x1 || !x2 || (!out && !q)) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: null pointer");
+  if (dtype != WB200_F32 && dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: unknown dtype %d", dtype);
+  if (ld1 < n || ld2 < n || (out && ldo < n)) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: a row pitch is smaller than n = %d", n);
+  if (q) {
+    if (n % 32 != 0) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: quantised output needs n %% 32 == 0 (got %d)", n);
+    if (!scale_rowmajor && !scale_packed) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: q given without a scale output");
+    if (reinterpret_cast<uintptr_t>(q) & 1) return fail(WB200_ERR_ALIGNMENT, "silu_and_mul: q must be 2-byte aligned");
+  }
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int k_atoms = q ? wb::sf_k_atoms(n) : 0;
+  if (q && scale_packed && (rows % 128 != 0 || (n / 32) % 8 != 0)) {
+    const int rbs = wb::sf_row_blocks(rows);
+    const long long total = (long long)rbs * k_atoms * 512;
+    wb::fill_scale_padding_kernel<<<unsigned((total + 255) / 256), 256, 0, s>>>(static_cast<uint8_t*>(scale_packed), rows,
+                                                                                  n / 32, k_atoms, rbs);
+  }
+  if (dtype == WB200_F32)
+    return launch_silu<float>(x1, x2, ld1, ld2, rows, n, out, ldo, q, scale_rowmajor, scale_packed, k_atoms, s);
+  return launch_silu<__nv_bfloat16>(x1, x2, ld1, ld2, rows, n, out, ldo, q, scale_rowmajor, scale_packed, k_atoms, s);
+}
+
+int wb200_moe_combine(const void* y, long long ldy, int dtype, const int* row_of, const float* weight, int tokens, int top_k,
+                      int cols, void* out, long long ldo, void* stream) {
+  if (tokens <= 0 || top_k <= 0 || cols <= 0)
+    return fail(WB200_ERR_INVALID_ARG, "moe_combine: tokens = %d, top_k = %d, cols = %d", tokens, top_k, cols);
+  if (!y || !row_of || !weight || !out) return fail(WB200_ERR_INVALID_ARG, "moe_combine: null pointer");
+  if (dtype != WB200_F32 && dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "moe_combine: unknown dtype %d", dtype);
+  if (ldy < cols || ldo < cols) return fail(WB200_ERR_INVALID_ARG, "moe_combine: a row pitch is smaller than cols = %d", cols);
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long threads = (long long)tokens * ((cols + 3) / 4);
+  const unsigned blocks = unsigned((threads + 255) / 256);
+  if (dtype == WB200_F32)
+    wb::moe_combine_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(y), ldy, row_of, weight, tokens, top_k, cols,
+                                                         static_cast<float*>(out), ldo);
+  else
+    wb::moe_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(y), ldy, row_of, weight,
+                                                                 tokens, top_k, cols, static_cast<__nv_bfloat16*>(out), ldo);
   WB_CUDA(cudaGetLastError());
   return WB200_OK;
 }

@@ -25,30 +25,12 @@ __device__ __forceinline__ uint32_t e2m1_code(float y) {
   return idx | ((__float_as_uint(y) >> 31) << 3);
 }
 
-template <typename InT>
-__global__ void __launch_bounds__(256)
-quantize_mxfp4_kernel(const InT* __restrict__ x, long long ldx, int rows, int K, uint8_t* __restrict__ q,
-                      uint8_t* __restrict__ scale_rm, uint8_t* __restrict__ scale_packed, int k_atoms) {
-  // one group of 8 lanes per 32-element block; blocks of a row are consecutive groups
-  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
-  const int sub = threadIdx.x & 7;
-  const int kblocks = K >> 5;
-  const long long total = (long long)rows * kblocks;
-  const bool active = group < total;
-  const int r = active ? int(group / kblocks) : 0;
-  const int kb = active ? int(group - (long long)r * kblocks) : 0;
-  float v[4] = {0.f, 0.f, 0.f, 0.f};
-  if (active) {
-    const InT* src = x + (long long)r * ldx + kb * 32 + sub * 4;
-    if constexpr (sizeof(InT) == 4) {
-      const float4 t = *reinterpret_cast<const float4*>(src);
-      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-    } else {
-      const uint2 t = *reinterpret_cast<const uint2*>(src);
-      v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
-      v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
-    }
-  }
+// Quantises the 32 values held by a group of 8 lanes (v: 4 consecutive values of lane `sub`) of row r,
+// K block kb, and stores codes and scale. All 8 lanes of a group must call it together (shuffles);
+// inactive groups pass active = false and store nothing.
+__device__ __forceinline__ void mxfp4_encode_group(const float (&v)[4], bool active, int r, int kb, int sub, int K,
+                                                   int kblocks, int k_atoms, uint8_t* __restrict__ q,
+                                                   uint8_t* __restrict__ scale_rm, uint8_t* __restrict__ scale_packed) {
   float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
   for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -77,6 +59,33 @@ quantize_mxfp4_kernel(const InT* __restrict__ x, long long ldx, int rows, int K,
       scale_packed[off] = uint8_t(sb);
     }
   }
+}
+
+template <typename InT>
+__global__ void __launch_bounds__(256)
+quantize_mxfp4_kernel(const InT* __restrict__ x, long long ldx, int rows, int K, uint8_t* __restrict__ q,
+                      uint8_t* __restrict__ scale_rm, uint8_t* __restrict__ scale_packed, int k_atoms) {
+  // one group of 8 lanes per 32-element block; blocks of a row are consecutive groups
+  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+  const int sub = threadIdx.x & 7;
+  const int kblocks = K >> 5;
+  const long long total = (long long)rows * kblocks;
+  const bool active = group < total;
+  const int r = active ? int(group / kblocks) : 0;
+  const int kb = active ? int(group - (long long)r * kblocks) : 0;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    const InT* src = x + (long long)r * ldx + kb * 32 + sub * 4;
+    if constexpr (sizeof(InT) == 4) {
+      const float4 t = *reinterpret_cast<const float4*>(src);
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+      const uint2 t = *reinterpret_cast<const uint2*>(src);
+      v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+      v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+    }
+  }
+  mxfp4_encode_group(v, active, r, kb, sub, K, kblocks, k_atoms, q, scale_rm, scale_packed);
 }
 
 // Fills the padding bytes of a packed scale array (rows past `rows` in the last 128-row block, K blocks

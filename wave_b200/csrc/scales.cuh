@@ -27,10 +27,12 @@ __host__ __device__ inline size_t sf_packed_bytes(int rows, int K) {
 
 // One thread block moves 128 rows x 32 K-blocks through shared memory: reads are 16 bytes per
 // thread along K, writes are 4 KiB contiguous. Rows [row_base, row_base + 128) of src, clipped at
-// row_limit, go to the 128-row block whose first atom is at dst_block.
+// row_limit, go to the 128-row block whose first atom is at dst_block. With `broadcast` src holds one
+// scale per row, used for every K block of that row (the a_scale [M] argument of the reference's
+// broadcast-scale kernel, wave_lang/kernel/wave/templates/test_kernels.py:98-116).
 __device__ __forceinline__ void repack_tile(const uint8_t* __restrict__ src, long long src_row_stride, int row_base,
                                             int row_limit, int kblocks, int k_atoms, int atom0,
-                                            uint8_t* __restrict__ dst_block) {
+                                            uint8_t* __restrict__ dst_block, bool broadcast = false) {
   __shared__ __align__(16) uint8_t tile[128][32 + 4];  // +4 keeps 32-bit reads aligned and spreads banks
   const int t = threadIdx.x;
   {
@@ -38,16 +40,16 @@ __device__ __forceinline__ void repack_tile(const uint8_t* __restrict__ src, lon
     const int half = t & 1;
     const int row = row_base + r;
     const int kb0 = atom0 * 4 + half * 16;
-    const uint8_t* s = src + (long long)row * src_row_stride + kb0;
+    const uint8_t* s = src + (long long)row * src_row_stride + (broadcast ? 0 : kb0);
     const bool row_ok = row < row_limit;
-    if (row_ok && kb0 + 16 <= kblocks && ((reinterpret_cast<uintptr_t>(s) & 15) == 0)) {
+    if (!broadcast && row_ok && kb0 + 16 <= kblocks && ((reinterpret_cast<uintptr_t>(s) & 15) == 0)) {
       const uint4 v = *reinterpret_cast<const uint4*>(s);
       uint32_t* d = reinterpret_cast<uint32_t*>(&tile[r][half * 16]);
       d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
     } else {
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        tile[r][half * 16 + j] = (row_ok && kb0 + j < kblocks) ? s[j] : WB_SF_PAD;
+        tile[r][half * 16 + j] = (row_ok && kb0 + j < kblocks) ? s[broadcast ? 0 : j] : WB_SF_PAD;
     }
   }
   __syncthreads();
@@ -69,9 +71,10 @@ __device__ __forceinline__ void repack_tile(const uint8_t* __restrict__ src, lon
 // grid (ceil(k_atoms / 8), row_blocks), 256 threads.
 __global__ void __launch_bounds__(256)
 repack_scales_kernel(const uint8_t* __restrict__ src, long long src_row_stride, int rows, int kblocks,
-                     int k_atoms, uint8_t* __restrict__ dst) {
+                     int k_atoms, uint8_t* __restrict__ dst, bool broadcast) {
   const int rb = blockIdx.y;
-  repack_tile(src, src_row_stride, rb * 128, rows, kblocks, k_atoms, blockIdx.x * 8, dst + size_t(rb) * k_atoms * 512);
+  repack_tile(src, src_row_stride, rb * 128, rows, kblocks, k_atoms, blockIdx.x * 8, dst + size_t(rb) * k_atoms * 512,
+              broadcast);
 }
 
 // Grouped form: the rows of group g are src rows [row_start[g], row_start[g+1]) and its packed block

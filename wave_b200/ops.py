@@ -73,6 +73,26 @@ def repack_scales(scale: torch.Tensor, out: torch.Tensor | None = None) -> Packe
     return PackedScales(out, rows, K)
 
 
+def repack_scales_broadcast(scale: torch.Tensor, K: int, out: torch.Tensor | None = None) -> PackedScales:
+    """One E8M0 scale per row ([rows] uint8), used for every K block of the row -> PackedScales.
+    The a_scale argument of the reference's broadcast-scale kernel
+    (wave_lang/kernel/wave/templates/test_kernels.py:98-116)."""
+    lib = _lib.load()
+    _as_u8(scale, "scale")
+    if scale.dim() != 1:
+        raise ValueError(f"scale must be 1-D [rows], got shape {tuple(scale.shape)}")
+    rows = scale.shape[0]
+    nbytes = packed_scale_bytes(rows, K)
+    if out is None:
+        out = torch.empty(nbytes, dtype=torch.uint8, device=scale.device)
+    elif out.numel() < nbytes or out.dtype != torch.uint8 or not out.is_contiguous():
+        raise ValueError("repack_scales_broadcast: `out` must be a contiguous uint8 tensor of at least packed_scale_bytes(rows, K)")
+    stride = scale.stride(0) if rows > 1 else 1
+    with torch.cuda.device(scale.device):
+        _lib.check(lib.wb200_repack_scales_broadcast(scale.data_ptr(), stride, rows, K, out.data_ptr(), _stream()))
+    return PackedScales(out, rows, K)
+
+
 def dequant_mxfp4(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """[R, K/2] codes, [R, K/32] scales -> [R, K] f32 on the GPU (test aid)."""
     lib = _lib.load()

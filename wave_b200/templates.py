@@ -31,6 +31,7 @@ class ScaledGemmTemplate:
     num_splits: int = 1
     preshuffled_scales: bool = False       # scale arguments are PackedScales from e8m0_shuffle
     preshuffled_b: bool = False            # b went through b_preshuffle (identity on B200)
+    broadcast_a_scale: bool = False        # a_scale is [M]: one scale per row for all of K
     hints: dict = field(default_factory=dict)
 
 
@@ -58,6 +59,16 @@ def get_scaled_gemm_kernel(shape, mfma_variant: ScaledMMAType, block_shape=None,
                              hints={"mfma_variant": mfma_variant, "block_shape": tuple(block_shape),
                                     "waves_per_block": tuple(waves_per_block)})
     return tpl, _hyperparams(shape, block_shape, {"ADDRESS_SPACE": SHARED_ADDRESS_SPACE})
+
+
+def get_broadcasted_scale_gemm_mxfp4(shape, mfma_variant: ScaledMMAType):
+    """(kernel, hyperparams) for the kernel whose a_scale is [M], broadcast along K before the scaled MMA —
+    wave_lang/kernel/wave/templates/test_kernels.py:75-140 (tested by tests/kernel/wave_gemm_mxfp_test.py:594-634)."""
+    if not isinstance(mfma_variant, ScaledMMAType):
+        raise TypeError("mfma_variant must be a ScaledMMAType")
+    tpl = ScaledGemmTemplate("broadcasted_scale_scaled_mma", tuple(shape), f32, broadcast_a_scale=True,
+                             hints={"mfma_variant": mfma_variant, "block_shape": (32, 32, 256)})
+    return tpl, _hyperparams(shape, (32, 32, 256), {"ADDRESS_SPACE": SHARED_ADDRESS_SPACE})
 
 
 def _tagged(name, shape, block_shape, wave_shape, mfma_variant, output_dtype, **flags):
