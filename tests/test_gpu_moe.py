@@ -96,9 +96,10 @@ def test_silu_and_mul_as_the_reference_tests_it(m, n, dtype):
     silu(gate.to(DEV), up.to(DEV), out)
     ref = moe_oracle.silu_and_mul(gate, up)
     torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-1, atol=1e-2)
-    # and much tighter: a few f32 ulps of the f32 formula, then one rounding to the output type
+    # and much tighter: the kernel's fast exponential and division are good to ~1e-6 relative, then one
+    # rounding to the output type
     if dtype == torch.float32:
-        torch.testing.assert_close(out.cpu(), ref, rtol=2e-6, atol=1e-7)
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-5, atol=1e-6)
     else:
         assert int(orc.bf16_ulp_distance(out, ref).max()) <= 1
 

@@ -544,8 +544,8 @@ int wb200_quantize_mxfp4(const void* x, int x_dtype, long long ldx, int rows, in
   if (x_dtype != WB200_F32 && x_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "quantize: unknown input dtype %d", x_dtype);
   if (ldx < K) return fail(WB200_ERR_INVALID_ARG, "quantize: ldx = %lld is smaller than K = %d", ldx, K);
   const int esz = (x_dtype == WB200_F32) ? 4 : 2;
-  if ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(q) & 1))
-    return fail(WB200_ERR_ALIGNMENT, "quantize: x rows must be 16-byte aligned and q 2-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(q) & 3))
+    return fail(WB200_ERR_ALIGNMENT, "quantize: x rows must be 16-byte aligned and q 4-byte aligned");
   DeviceInfo* dev;
   int rc = get_device(&dev);
   if (rc) return rc;
@@ -557,8 +557,7 @@ int wb200_quantize_mxfp4(const void* x, int x_dtype, long long ldx, int rows, in
     wb::fill_scale_padding_kernel<<<unsigned((total + 255) / 256), 256, 0, s>>>(static_cast<uint8_t*>(scale_packed), rows,
                                                                                   K / 32, k_atoms, rbs);
   }
-  const long long threads = (long long)rows * (K / 32) * 8;
-  const unsigned blocks = unsigned((threads + 255) / 256);
+  const dim3 blocks(rows, (K / 32 + 63) / 64);
   if (x_dtype == WB200_F32)
     wb::quantize_mxfp4_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), ldx, rows, K, static_cast<uint8_t*>(q),
                                                             static_cast<uint8_t*>(scale_rowmajor),
@@ -625,10 +624,9 @@ extern "C++" {
 template <typename T>
 static int launch_silu(const void* x1, const void* x2, long long ld1, long long ld2, int rows, int n, void* out, long long ldo,
                        void* q, void* scale_rm, void* scale_packed, int k_atoms, cudaStream_t s) {
-  auto ok = [&](const void* p, long long ld) { return (reinterpret_cast<uintptr_t>(p) % (4 * sizeof(T))) == 0 && ld % 4 == 0; };
+  auto ok = [&](const void* p, long long ld) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * sizeof(T)) % 16 == 0; };
   const bool vec = ok(x1, ld1) && ok(x2, ld2) && (!out || ok(out, ldo));
-  const long long threads = (long long)rows * ((n + 31) / 32) * 8;
-  const unsigned blocks = unsigned((threads + 255) / 256);
+  const dim3 blocks(rows, ((n + 31) / 32 + 64 * wb::kSiluUnroll - 1) / (64 * wb::kSiluUnroll));
   if (vec)
     wb::silu_and_mul_kernel<T, true><<<blocks, 256, 0, s>>>(static_cast<const T*>(x1), static_cast<const T*>(x2), ld1, ld2, rows,
                                                             n, static_cast<T*>(out), ldo, static_cast<uint8_t*>(q),
@@ -653,7 +651,7 @@ int wb200_silu_and_mul(const void* x1, const void* x2, long long ld1, long long 
   if (q) {
     if (n % 32 != 0) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: quantised output needs n %% 32 == 0 (got %d)", n);
     if (!scale_rowmajor && !scale_packed) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: q given without a scale output");
-    if (reinterpret_cast<uintptr_t>(q) & 1) return fail(WB200_ERR_ALIGNMENT, "silu_and_mul: q must be 2-byte aligned");
+    if (reinterpret_cast<uintptr_t>(q) & 3) return fail(WB200_ERR_ALIGNMENT, "silu_and_mul: q must be 4-byte aligned");
   }
   DeviceInfo* dev;
   int rc = get_device(&dev);

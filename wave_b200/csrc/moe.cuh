@@ -123,75 +123,74 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-// y = x1 / (1 + exp(-x1)) * x2 in f32. Eight lanes share 32 consecutive columns (4 each), as in the
-// quantiser; `out` (same type as the inputs, may be null) gets y rounded once; q / scales (may be
-// null; need n % 32 == 0) get y quantised to MXFP4 from the f32 value, not from the rounded one.
-template <typename T>
-__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
-template <>
-__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
-  const float4 t = *reinterpret_cast<const float4*>(p);
-  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
 }
-template <>
-__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
-  const uint2 t = *reinterpret_cast<const uint2*>(p);
-  v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
-  v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
-}
-template <typename T>
-__device__ __forceinline__ void store4(T* p, const float (&v)[4]);
-template <>
-__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-}
-template <>
-__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
-  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                            pack_bf16x2(v[6], v[7]));
 }
 
-// VEC: all three matrices have 4-element-aligned bases and pitches, so whole groups of 4 move as one access.
+// y = x1 / (1 + exp(-x1)) * x2 in f32. Four lanes share 32 consecutive columns (8 each), as in the
+// quantiser; `out` (same type as the inputs, may be null) gets y rounded once; q / scales (may be
+// null; need n % 32 == 0) get y quantised to MXFP4 from the f32 value, not from the rounded one.
+// VEC: all three matrices have 16-byte aligned bases and pitches, so 8 values move as one or two accesses.
+// Every group of 4 lanes works on kSiluUnroll consecutive blocks of 32 columns and issues all their
+// loads before any arithmetic. grid (rows, ceil(nblocks / (64 U))): a CTA covers 64 U blocks of one row.
+constexpr int kSiluUnroll = 2;
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 silu_and_mul_kernel(const T* __restrict__ x1, const T* __restrict__ x2, long long ld1, long long ld2, int rows, int n,
                     T* __restrict__ out, long long ldo, uint8_t* __restrict__ q, uint8_t* __restrict__ scale_rm,
                     uint8_t* __restrict__ scale_packed, int k_atoms) {
-  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
-  const int sub = threadIdx.x & 7;
+  constexpr int U = kSiluUnroll;
+  const int g0 = blockIdx.y * 64 + (threadIdx.x >> 2);
+  const int sub = threadIdx.x & 3;
   const int nblocks = (n + 31) >> 5;
-  const long long total = (long long)rows * nblocks;
-  const bool active = group < total;
-  const int r = active ? int(group / nblocks) : 0;
-  const int kb = active ? int(group - (long long)r * nblocks) : 0;
-  const int c0 = kb * 32 + sub * 4;
-  float y[4] = {0.f, 0.f, 0.f, 0.f};
-  if (active) {
-    float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
-    const T* p1 = x1 + (long long)r * ld1 + c0;
-    const T* p2 = x2 + (long long)r * ld2 + c0;
-    const bool full = VEC && c0 + 4 <= n;
-    if (full) {
-      load4<T>(p1, g);
-      load4<T>(p2, u);
-    } else {
+  const int r = blockIdx.x;
+  bool active[U], full[U];
+  float g[U][8], u[U][8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (c0 + j < n) { g[j] = to_f32<T>(p1[j]); u[j] = to_f32<T>(p2[j]); }
-    }
+  for (int i = 0; i < U; ++i) {
+    const int kb = g0 * U + i;
+    active[i] = r < rows && kb < nblocks;
+    const int c0 = kb * 32 + sub * 8;
+    full[i] = VEC && c0 + 8 <= n;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) y[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
-    if (out) {
-      T* po = out + (long long)r * ldo + c0;
-      if (full) {
-        store4<T>(po, y);
+    for (int j = 0; j < 8; ++j) g[i][j] = u[i][j] = 0.f;
+    if (active[i]) {
+      const T* p1 = x1 + (long long)r * ld1 + c0;
+      const T* p2 = x2 + (long long)r * ld2 + c0;
+      if (full[i]) {
+        load8(p1, g[i]);
+        load8(p2, u[i]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (c0 + j < n) po[j] = from_f32<T>(y[j]);
+        for (int j = 0; j < 8; ++j)
+          if (c0 + j < n) { g[i][j] = to_f32<T>(p1[j]); u[i][j] = to_f32<T>(p2[j]); }
       }
     }
   }
-  if (q) mxfp4_encode_group(y, active, r, kb, sub, n, nblocks, k_atoms, q, scale_rm, scale_packed);
+#pragma unroll
+  for (int i = 0; i < U; ++i) {
+    const int kb = g0 * U + i;
+    const int c0 = kb * 32 + sub * 8;
+    float y[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = __fdividef(g[i][j], 1.0f + __expf(-g[i][j])) * u[i][j];  // ~1e-6 relative
+    if (out && active[i]) {
+      T* po = out + (long long)r * ldo + c0;
+      if (full[i]) {
+        store8(po, y);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (c0 + j < n) po[j] = from_f32<T>(y[j]);
+      }
+    }
+    if (q) mxfp4_encode_group<8>(y, active[i], r, kb, sub, n, nblocks, k_atoms, q, scale_rm, scale_packed);
+  }
 }
 
 // out[t, c] = sum_j weight[t * top_k + j] * y[row_of[t * top_k + j], c], accumulated in f32 in slot

@@ -9,31 +9,36 @@
 //   amax == 0 -> byte 127; y = x * 2^-(byte - 127), clamped to [-6, 6], rounded to the nearest E2M1
 //   value, a value on a midpoint going to the neighbour with the even code; even k in the low nibble.
 //
-// HBM-bound: 8 lanes share one block (4 values each), so a warp reads 512 contiguous bytes (f32)
-// per load instruction and writes 64 contiguous bytes of codes.
+// HBM-bound: 4 lanes share one block (8 values each), so a warp reads 512 contiguous bytes of bf16
+// per load instruction and writes 128 contiguous bytes of codes; the E2M1 rounding is the hardware conversion.
 #pragma once
 #include "scales.cuh"
 #include <cuda_bf16.h>
 
 namespace wb {
 
-__device__ __forceinline__ uint32_t e2m1_code(float y) {
-  const float m = fabsf(y);
-  // midpoints between neighbouring magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6}: strict above an even
-  // code, inclusive above an odd one (ties to the even code)
-  uint32_t idx = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) + (m > 2.5f) + (m >= 3.5f) + (m > 5.0f);
-  return idx | ((__float_as_uint(y) >> 31) << 3);
+// Two f32 -> one byte of E2M1 codes (lo in the low nibble), by the hardware conversion: round to
+// nearest with ties to the even code (of the magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6}: 0.25 -> 0, 0.75 -> 1,
+// 1.25 -> 1, 1.75 -> 2, 2.5 -> 2, 3.5 -> 4, 5 -> 4), saturating at +-6, sign in bit 3.
+__device__ __forceinline__ uint32_t e2m1x2_code(float lo, float hi) {
+  uint16_t r;
+  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(hi), "f"(lo));
+  return uint32_t(r);
 }
 
-// Quantises the 32 values held by a group of 8 lanes (v: 4 consecutive values of lane `sub`) of row r,
-// K block kb, and stores codes and scale. All 8 lanes of a group must call it together (shuffles);
-// inactive groups pass active = false and store nothing.
-__device__ __forceinline__ void mxfp4_encode_group(const float (&v)[4], bool active, int r, int kb, int sub, int K,
+// Quantises the 32 values of row r, K block kb held by a group of 32 / VPL neighbouring lanes (v: the VPL
+// consecutive values of lane `sub` of the group; VPL = 4 or 8) and stores codes and scale. All lanes of a
+// warp must call it together (shuffles); inactive groups pass active = false and store nothing.
+template <int VPL>
+__device__ __forceinline__ void mxfp4_encode_group(const float (&v)[VPL], bool active, int r, int kb, int sub, int K,
                                                    int kblocks, int k_atoms, uint8_t* __restrict__ q,
                                                    uint8_t* __restrict__ scale_rm, uint8_t* __restrict__ scale_packed) {
-  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  static_assert(VPL == 4 || VPL == 8, "4 or 8 values per lane");
+  float amax = 0.f;
 #pragma unroll
-  for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  for (int j = 0; j < VPL; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+  for (int o = 1; o < 32 / VPL; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   // floor(log2(amax)) is the unbiased exponent field for normal numbers; subnormal maxima fall
   // below the clamp at 0 either way
   int sb = 127;
@@ -46,12 +51,11 @@ __device__ __forceinline__ void mxfp4_encode_group(const float (&v)[4], bool act
   const float inv = (ie == -127) ? __int_as_float(0x00400000) : __int_as_float((ie + 127) << 23);
   uint32_t packed = 0;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float y = fminf(fmaxf(v[j] * inv, -6.0f), 6.0f);
-    packed |= e2m1_code(y) << (4 * j);
-  }
+  for (int j = 0; j < VPL / 2; ++j) packed |= e2m1x2_code(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
   if (!active) return;
-  reinterpret_cast<uint16_t*>(q + (long long)r * (K / 2) + kb * 16)[sub] = uint16_t(packed);
+  uint8_t* dst = q + (long long)r * (K / 2) + kb * 16;
+  if constexpr (VPL == 4) reinterpret_cast<uint16_t*>(dst)[sub] = uint16_t(packed);
+  else reinterpret_cast<uint32_t*>(dst)[sub] = packed;
   if (sub == 0) {
     if (scale_rm) scale_rm[(long long)r * kblocks + kb] = uint8_t(sb);
     if (scale_packed) {
@@ -61,31 +65,33 @@ __device__ __forceinline__ void mxfp4_encode_group(const float (&v)[4], bool act
   }
 }
 
+// 8 consecutive values from 16-byte aligned memory.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 t = *reinterpret_cast<const uint4*>(p);
+  v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+  v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+  v[4] = __uint_as_float(t.z << 16); v[5] = __uint_as_float(t.z & 0xffff0000u);
+  v[6] = __uint_as_float(t.w << 16); v[7] = __uint_as_float(t.w & 0xffff0000u);
+}
+
+// Four lanes per 32-element block, 8 values (16 bytes of bf16, 32 of f32) each; grid (rows,
+// ceil(kblocks / 64)): a CTA covers 64 consecutive blocks of one row. x rows are 16-byte aligned.
 template <typename InT>
 __global__ void __launch_bounds__(256)
 quantize_mxfp4_kernel(const InT* __restrict__ x, long long ldx, int rows, int K, uint8_t* __restrict__ q,
                       uint8_t* __restrict__ scale_rm, uint8_t* __restrict__ scale_packed, int k_atoms) {
-  // one group of 8 lanes per 32-element block; blocks of a row are consecutive groups
-  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
-  const int sub = threadIdx.x & 7;
+  const int sub = threadIdx.x & 3;
   const int kblocks = K >> 5;
-  const long long total = (long long)rows * kblocks;
-  const bool active = group < total;
-  const int r = active ? int(group / kblocks) : 0;
-  const int kb = active ? int(group - (long long)r * kblocks) : 0;
-  float v[4] = {0.f, 0.f, 0.f, 0.f};
-  if (active) {
-    const InT* src = x + (long long)r * ldx + kb * 32 + sub * 4;
-    if constexpr (sizeof(InT) == 4) {
-      const float4 t = *reinterpret_cast<const float4*>(src);
-      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-    } else {
-      const uint2 t = *reinterpret_cast<const uint2*>(src);
-      v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
-      v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
-    }
-  }
-  mxfp4_encode_group(v, active, r, kb, sub, K, kblocks, k_atoms, q, scale_rm, scale_packed);
+  const int r = blockIdx.x;
+  const int kb = blockIdx.y * 64 + (threadIdx.x >> 2);
+  const bool active = r < rows && kb < kblocks;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (active) load8(x + (long long)r * ldx + kb * 32 + sub * 8, v);
+  mxfp4_encode_group<8>(v, active, r, kb, sub, K, kblocks, k_atoms, q, scale_rm, scale_packed);
 }
 
 // Fills the padding bytes of a packed scale array (rows past `rows` in the last 128-row block, K blocks

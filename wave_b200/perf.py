@@ -1,4 +1,5 @@
-"""Shape-sweep benchmark of the MXFP4 scaled GEMM: `python -m wave_b200.perf [--validate] [--csv out.csv]`.
+"""Shape-sweep benchmark of the MXFP4 scaled GEMM: `python -m wave_b200.perf [--validate] [--csv out.csv]`;
+`python -m wave_b200.perf --moe` times the steps of the MXFP4 expert MLP.
 
 Same bookkeeping as the reference's benchmark driver (wave_lang/kernel/wave/perf/benchmark_mxfp4.py):
 flops = 2 M N K (:78-79), bytes = M K/2 + M K/32 + N K/2 + N K/32 + M N sizeof(c) (:82-85), TFLOP/s from the
@@ -62,12 +63,89 @@ def time_shape(M, N, K, out_dtype=torch.bfloat16, iters: int = 20, validate: boo
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
+def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, device="cuda:0"):
+    """Device time of every step of the MXFP4 expert MLP at the grouped-GEMM benchmark's sizes
+    (8 experts x [14336, 4096] gate|up weights, 4096 tokens, top-2): microseconds per step and, for the
+    memory-bound steps, the bytes they must move / that time."""
+    from . import moe, ops
+    from .grouped import grouped_scaled_gemm
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(4)
+    rnd = lambda *shape: torch.randint(0, 256, shape, dtype=torch.uint8, device=dev, generator=g)  # noqa: E731
+    sc = lambda *shape: torch.randint(120, 126, shape, dtype=torch.uint8, device=dev, generator=g)  # noqa: E731
+    mlp = moe.MXFP4ExpertMLP([rnd(2 * inter, K // 2) for _ in range(experts)], [sc(2 * inter, K // 32) for _ in range(experts)],
+                             [rnd(K, inter // 2) for _ in range(experts)], [sc(K, inter // 32) for _ in range(experts)], top_k)
+    x = torch.randn(tokens, K, device=dev, generator=g).to(torch.bfloat16)
+    logits = torch.randn(tokens, experts, device=dev, generator=g)
+    n = tokens * top_k
+    B = mlp.BLOCK
+    weight, ids = mlp.route(logits)
+    cap = n + experts * (B - 1)
+    sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty((cap + B - 1) // B, dtype=torch.int32, device=dev)
+    post = torch.empty(1, dtype=torch.int32, device=dev)
+    inverse = torch.empty(n, dtype=torch.int32, device=dev)
+    moe.moe_align_block_size(ids, experts, B, sorted_ids, expert_ids, post, inverse)
+    counts = torch.bincount(ids.reshape(-1), minlength=experts).tolist()
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + (c + B - 1) // B * B)
+    R = offsets[-1]
+    xq, xs, _ = ops.quantize_mxfp4(x, want_packed=False)
+    a = torch.empty(R, K // 2, dtype=torch.uint8, device=dev)
+    a_s = torch.empty(R, K // 32, dtype=torch.uint8, device=dev)
+    h = torch.empty(R, 2 * inter, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(R, K, dtype=torch.bfloat16, device=dev)
+    out = torch.empty(tokens, K, dtype=torch.bfloat16, device=dev)
+    moe.gather_rows(xq, sorted_ids, n, top_k, a)
+    moe.gather_rows(xs, sorted_ids, n, top_k, a_s)
+    grouped_scaled_gemm(a, a_s, mlp.w1, offsets, h)
+    _, hq, hs = moe.silu_and_mul(h[:, :inter], h[:, inter:], quantize=True)
+    steps = [
+        ("moe_align_block_size", lambda: moe.moe_align_block_size(ids, experts, B, sorted_ids, expert_ids, post, inverse), None),
+        ("quantize tokens", lambda: ops.quantize_mxfp4(x, want_packed=False), tokens * K * 2 + tokens * K // 2 + tokens * K // 32),
+        ("gather codes + scales", lambda: (moe.gather_rows(xq, sorted_ids, n, top_k, a), moe.gather_rows(xs, sorted_ids, n, top_k, a_s)),
+         2 * R * (K // 2 + K // 32)),
+        ("grouped GEMM gate|up", lambda: grouped_scaled_gemm(a, a_s, mlp.w1, offsets, h), None),
+        ("silu_and_mul + quantise", lambda: moe.silu_and_mul(h[:, :inter], h[:, inter:], quantize=True),
+         R * 2 * inter * 2 + R * inter // 2 + R * inter // 32),
+        ("grouped GEMM down", lambda: grouped_scaled_gemm(hq, hs, mlp.w2, offsets, y), None),
+        ("combine", lambda: moe.combine(y, inverse, weight.reshape(-1), top_k, out), R * K * 2 + tokens * K * 2),
+        ("whole forward", lambda: mlp(x, logits), None),
+    ]
+    rows = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, fn, nbytes in steps:
+        for _ in range(2):
+            fn()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / iters
+        row = {"step": name, "us": round(us, 1)}
+        if nbytes:
+            row["gbytes_per_s"] = round(nbytes / us / 1e3, 1)
+        if "GEMM" in name:
+            NN, KK = (2 * inter, K) if "gate" in name else (K, inter)
+            row["tflops"] = round(2.0 * n * NN * KK / us / 1e6, 1)  # routed rows only; padding rows are not counted
+        rows.append(row)
+        print(row, flush=True)
+    ops.check_device_status()
+    return rows
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--validate", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--moe", action="store_true", help="time the steps of the MXFP4 expert MLP instead of the shape sweep")
     args = ap.parse_args(argv)
+    if args.moe:
+        time_moe(iters=args.iters)
+        return
     rows = []
     for M, N, K in default_shapes():
         us = time_shape(M, N, K, iters=args.iters, validate=args.validate)
