@@ -1,0 +1,43 @@
+"""CPU oracle for the MXFP8 scaled GEMM — TEST INFRASTRUCTURE, not a product path.
+
+Restates the reference's own CPU functions for this variant, which live in its test file:
+`generate_gemm_afp8wfp8_inputs` (tests/kernel/wave_gemm_mxfp_test.py:64-77) and
+`torchScaledGemmMXFP8` (tests/kernel/wave_gemm_mxfp_test.py:80-91). Only `tests/` may import this module.
+
+Parity is pinned: `tests/golden/make_golden.py` executes those two reference functions themselves
+(their source is read from the reference tree at generation time) and stores their outputs in
+`tests/golden/gemm_mxfp8_seed5_64x96x128.npz`; `tests/test_oracle.py` checks this file against them.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .mxfp4_oracle import SCALE_GROUP_SIZE, e8m0_to_f32
+
+
+def generate_gemm_afp8wfp8_inputs(shape, seed: int = 5, dtype=torch.float8_e5m2):
+    """tests/kernel/wave_gemm_mxfp_test.py:64-77 on the CPU: x [M, K] f8, w [K, N] f8 (a transposed view of
+    [N, K]), scales uniform in [124, 128) generated as [K/32, rows] and transposed (views, not contiguous)."""
+    M, N, K = shape
+    torch.manual_seed(seed)                                                         # :66
+    x = torch.randn((M, K), dtype=torch.float32).to(dtype)                          # :68
+    w = torch.randn((N, K), dtype=torch.float32).to(dtype)                          # :69
+    w = w.T                                                                         # :70
+    x_scales = torch.randint(124, 128, (K // SCALE_GROUP_SIZE, M), dtype=torch.uint8)   # :72
+    w_scales = torch.randint(124, 128, (K // SCALE_GROUP_SIZE, N), dtype=torch.uint8)   # :73
+    return x, w, x_scales.T, w_scales.T                                             # :74-77
+
+
+def dequant_mxfp8(x: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """[R, K] f8 and [R, K/32] E8M0 -> [R, K] f32 (:82-86: value * 2^(scale - 127), exact in f32)."""
+    s = scales.repeat_interleave(SCALE_GROUP_SIZE, dim=1).to(torch.float32)
+    return x.to(torch.float32) * e8m0_to_f32(s)
+
+
+def torch_scaled_gemm_mxfp8(x, w, x_scales, w_scales) -> torch.Tensor:
+    """tests/kernel/wave_gemm_mxfp_test.py:80-91: w is [K, N], w_scales [N, K/32]."""
+    x_f32 = dequant_mxfp8(x, x_scales)                                              # :82-87
+    w_f32 = w.to(torch.float32) * e8m0_to_f32(
+        w_scales.repeat_interleave(SCALE_GROUP_SIZE, dim=1).to(torch.float32)).T   # :88-90
+    return torch.mm(x_f32, w_f32)                                                   # :91

@@ -96,6 +96,26 @@ def main(ref_root: str) -> None:
         store[f"case{ci}_expert_ids"] = expert_ids.numpy()
         store[f"case{ci}_post_pad"] = post.numpy()
     np.savez_compressed(HERE / "moe_align.npz", **store)
+
+    # 7. MXFP8: the reference keeps its generator and its oracle for this variant inside a test file
+    #    (tests/kernel/wave_gemm_mxfp_test.py:64-91) whose other imports need the compiler stack, so the
+    #    two function definitions are taken out of that file's syntax tree and executed as they are, with
+    #    the CPU forms of the helpers they call.
+    import ast
+    test_src = (Path(ref_root) / "tests/kernel/wave_gemm_mxfp_test.py").read_text()
+    wanted = [n for n in ast.parse(test_src).body
+              if isinstance(n, ast.FunctionDef) and n.name in ("generate_gemm_afp8wfp8_inputs", "torchScaledGemmMXFP8")]
+    assert len(wanted) == 2
+    ns = {"torch": torch, "SCALE_GROUP_SIZE": ref.SCALE_GROUP_SIZE, "e8m0_to_f32": ref.e8m0_to_f32,
+          "device_randn": torch.randn, "device_randint": torch.randint}
+    exec(compile(ast.Module(body=wanted, type_ignores=[]), "wave_gemm_mxfp_test.py", "exec"), ns)
+    torch.set_num_threads(1)
+    x, w, xs, ws = ns["generate_gemm_afp8wfp8_inputs"]((64, 96, 128))
+    out = ns["torchScaledGemmMXFP8"](x, w, xs, ws)
+    np.savez_compressed(HERE / "gemm_mxfp8_seed5_64x96x128.npz", x=x.view(torch.uint8).numpy(),
+                        w=np.ascontiguousarray(w.T.contiguous().view(torch.uint8).numpy()),  # stored as [N, K] bytes
+                        x_scales=np.ascontiguousarray(xs.numpy()), w_scales=np.ascontiguousarray(ws.numpy()),
+                        out=out.numpy())
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 

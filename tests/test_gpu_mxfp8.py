@@ -1,0 +1,123 @@
+"""GPU parity of the MXFP8 scaled GEMM (8-bit E5M2 / E4M3 operands, E8M0 block scales) against the CPU oracle
+and the golden vector made from the reference's own functions. Mirrors testScaledGemmMXFP8
+(tests/kernel/wave_gemm_mxfp_test.py:416-501), whose tolerance is atol 2e-3, rtol 1e-3; the checks here also
+apply the tighter f32 / bf16 criteria used for MXFP4 (products of dequantised operands are exact in f32, only
+the summation order differs)."""
+
+import numpy as np
+import pytest
+import torch
+
+import wave_b200 as wb
+from conftest import GOLDEN
+from oracle import mxfp4_oracle as orc
+from oracle import mxfp8_oracle as orc8
+from wave_b200 import _lib, ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def check(c, a, a_s, b, b_s, ref=None):
+    """a [M, K], b [N, K] f8 tensors on the CPU; c on the GPU."""
+    ad, bd = orc8.dequant_mxfp8(a, a_s), orc8.dequant_mxfp8(b, b_s)
+    if ref is None:
+        ref = ad @ bd.T
+    if c.dtype == torch.float32:
+        tol = orc.f32_tolerance(ad, bd, ref, a.shape[1])
+        err = (c.cpu() - ref).abs()
+        assert bool((err <= tol).all()), f"{int((err > tol).sum())} outside tolerance, max err {float(err.max())}"
+    else:
+        # 1 bf16 ulp of the rounded reference; where a sum cancels to a value far below its terms, the f32
+        # summation-order tolerance plus half an ulp applies instead (few entries: under 0.1 %)
+        ulp = orc.bf16_ulp_distance(c, ref)
+        tol = orc.f32_tolerance(ad, bd, ref, a.shape[1])
+        bad = (ulp > 1) & ~((c.float().cpu() - ref).abs() <= tol + ref.abs() * 2.0 ** -8)
+        assert not bool(bad.any()), f"{int(bad.sum())} entries outside both bounds"
+        assert float((ulp > 1).float().mean()) < 1e-3, "too many entries beyond 1 bf16 ulp"
+    ops.check_device_status()
+
+
+def problem(M, N, K, seed, dtype=torch.float8_e5m2, lo=124, hi=131):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(M, K, generator=g).to(dtype)
+    b = torch.randn(N, K, generator=g).to(dtype)
+    a_s = torch.randint(lo, hi, (M, K // 32), dtype=torch.uint8, generator=g)
+    b_s = torch.randint(lo, hi, (N, K // 32), dtype=torch.uint8, generator=g)
+    return a, a_s, b, b_s
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_golden_small(out_dtype):
+    g = np.load(GOLDEN / "gemm_mxfp8_seed5_64x96x128.npz")
+    x = torch.from_numpy(g["x"]).view(torch.float8_e5m2)
+    w_t = torch.from_numpy(g["w"]).view(torch.float8_e5m2)  # [N, K]
+    xs, ws = torch.from_numpy(g["x_scales"]), torch.from_numpy(g["w_scales"])
+    kernel, hyper = wb.get_scaled_gemm_mxfp8_kernel((64, 96, 128), wb.ScaledMMAType.F32_16x16x128_F8F6F4, output_dtype=out_dtype)
+    gemm = wb.wave_compile(wb.WaveCompileOptions(subs=hyper, canonicalize=True, schedule=wb.SchedulingType.NONE), kernel)
+    out = torch.zeros(64, 96, dtype=out_dtype, device=DEV)
+    gemm(x.to(DEV).view(torch.int8), xs.to(DEV), w_t.to(DEV).view(torch.int8), ws.to(DEV), out)
+    ref = torch.from_numpy(g["out"])
+    torch.testing.assert_close(ref, out.cpu().float(), atol=2e-3 if out_dtype == torch.float32 else 0.5, rtol=1e-3 if out_dtype == torch.float32 else 1e-2)
+    check(out, x, xs, w_t, ws, ref=ref)
+
+
+def test_reference_test_shape_1024_as_the_reference_writes_it():
+    shape = (1024, 1024, 1024)
+    kernel, hyper = wb.get_scaled_gemm_mxfp8_kernel(shape, wb.ScaledMMAType.F32_16x16x128_F8F6F4)
+    options = wb.set_default_run_config(wb.WaveCompileOptions(subs=hyper, canonicalize=True, schedule=wb.SchedulingType.NONE))
+    gemm = wb.wave_compile(options, kernel)
+    x, w, x_scales, w_scales = orc8.generate_gemm_afp8wfp8_inputs(shape)
+    out = torch.zeros(x.shape[0], w.shape[1], dtype=torch.float32, device=DEV)
+    w_t = w.T.contiguous()
+    # x_scales / w_scales are transposed views, as in the reference test
+    gemm(x.to(DEV).view(torch.int8), x_scales.to(DEV), w_t.to(DEV).view(torch.int8), w_scales.to(DEV), out)
+    torch_out = orc8.torch_scaled_gemm_mxfp8(x, w, x_scales, w_scales)
+    torch.testing.assert_close(torch_out, out.cpu(), atol=2e-3, rtol=1e-3, check_dtype=False)
+    check(out, x, x_scales, w_t, w_scales, ref=torch_out)
+
+
+PATHS = [_lib.PATH_TILE_1CTA, _lib.PATH_TILE_1CTA | _lib.TILE_N128, _lib.PATH_TILE_2CTA, _lib.PATH_TILE_2CTA | _lib.TILE_N128]
+
+
+@pytest.mark.parametrize("flags", PATHS)
+@pytest.mark.parametrize("shape", [(128, 128, 128), (256, 512, 1024), (1000, 1100, 992), (130, 260, 32), (3, 5, 64),
+                                   (2048, 3072, 512)])
+@pytest.mark.parametrize("out_dtype,elem", [(torch.float32, torch.float8_e5m2), (torch.bfloat16, torch.float8_e4m3fn)])
+def test_paths_and_shapes(flags, shape, out_dtype, elem):
+    M, N, K = shape
+    a, a_s, b, b_s = problem(M, N, K, seed=M + N + K, dtype=elem)
+    c = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_mxfp8_packed(a.to(DEV), ops.repack_scales(a_s.to(DEV)), b.to(DEV), ops.repack_scales(b_s.to(DEV)), c,
+                                 flags=flags)
+    check(c, a, a_s, b, b_s)
+
+
+def test_accumulate_and_errors():
+    a, a_s, b, b_s = problem(256, 384, 512, seed=4)
+    ad, bd = a.to(DEV), b.to(DEV)
+    asp, bsp = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
+    base = torch.randn(256, 384)
+    c = base.to(DEV)
+    ops.scaled_gemm_mxfp8_packed(ad, asp, bd, bsp, c, flags=_lib.ACCUMULATE)
+    ref = orc8.dequant_mxfp8(a, a_s) @ orc8.dequant_mxfp8(b, b_s).T
+    torch.testing.assert_close(c.cpu(), ref + base, rtol=1e-5, atol=1e-3)
+    with pytest.raises(ValueError):
+        ops.scaled_gemm_mxfp8_packed(ad.view(torch.uint8), asp, bd.view(torch.uint8), bsp, c)  # format not given
+    with pytest.raises(RuntimeError):
+        ops.scaled_gemm_mxfp8_packed(ad, asp, bd, bsp, c, flags=_lib.PATH_SKINNY)
+
+
+def test_full_size_8192_sampled():
+    """The reference test's large shape (8192^3): seeded inputs made on the GPU, sampled rows checked against
+    the dequantised f32 product."""
+    M = N = K = 8192
+    g = torch.Generator(device=DEV).manual_seed(5)
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.float8_e5m2)
+    b = torch.randn(N, K, device=DEV, generator=g).to(torch.float8_e5m2)
+    a_s = torch.randint(124, 128, (M, K // 32), dtype=torch.uint8, device=DEV, generator=g)
+    b_s = torch.randint(124, 128, (N, K // 32), dtype=torch.uint8, device=DEV, generator=g)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.scaled_gemm_mxfp8_packed(a, ops.repack_scales(a_s), b, ops.repack_scales(b_s), c)
+    rows = torch.arange(0, M, 331, device=DEV)
+    check(c[rows], a[rows].cpu(), a_s[rows].cpu(), b.cpu(), b_s.cpu())

@@ -140,3 +140,16 @@ def test_moe_align_block_size_oracle_matches_reference_outputs():
         assert np.array_equal(sorted_ids, ref_sorted)
         assert np.array_equal(expert_ids, ref_experts)
         assert np.array_equal(sorted_ids[inverse], np.arange(tokens * topk))
+
+
+def test_mxfp8_oracle_matches_reference_outputs():
+    """oracle/mxfp8_oracle.py against the stored outputs of the reference's own MXFP8 generator and oracle."""
+    from oracle import mxfp8_oracle
+    g = np.load(GOLDEN / "gemm_mxfp8_seed5_64x96x128.npz")
+    x, w, xs, ws = mxfp8_oracle.generate_gemm_afp8wfp8_inputs((64, 96, 128))
+    assert np.array_equal(x.view(torch.uint8).numpy(), g["x"])
+    assert np.array_equal(w.T.contiguous().view(torch.uint8).numpy(), g["w"])
+    assert np.array_equal(xs.numpy(), g["x_scales"]) and np.array_equal(ws.numpy(), g["w_scales"])
+    torch.set_num_threads(1)
+    out = mxfp8_oracle.torch_scaled_gemm_mxfp8(x, w, xs, ws)
+    assert np.array_equal(out.numpy(), g["out"])

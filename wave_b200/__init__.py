@@ -19,7 +19,7 @@ from .schedules import (get_mxfp4_asymmetric_schedule, get_mxfp4_dbuf_mixed_ping
                         get_mxfp4_dbuf_mixed_pingpong_shuffle_schedule, get_mxfp4_dbuf_pingpong_schedule,
                         get_mxfp4_dbuf_pingpong_schedule_Bshuffled, get_mxfp4_dbuf_pingpong_schedule_Bshuffled_lds,
                         get_mxfp4_dbuf_schedule)
-from .templates import (get_broadcasted_scale_gemm_mxfp4, get_scaled_gemm_kernel, get_tagged_mxfp4_gemm, get_tagged_mxfp4_gemm_preshuffle_b,  # noqa: F401
+from .templates import (get_broadcasted_scale_gemm_mxfp4, get_scaled_gemm_kernel, get_scaled_gemm_mxfp8_kernel, get_tagged_mxfp4_gemm, get_tagged_mxfp4_gemm_preshuffle_b,  # noqa: F401
                         get_tagged_mxfp4_gemm_preshuffle_b_wide_store, get_tagged_mxfp4_gemm_preshuffle_scales,
                         get_tagged_mxfp4_gemm_preshuffle_scales_and_B, get_tagged_splitk_mxfp4_gemm,
                         get_tagged_splitk_mxfp4_gemm_preshuffle_b, get_tagged_splitk_mxfp4_gemm_preshuffle_scales)

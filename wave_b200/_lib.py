@@ -30,6 +30,8 @@ PATH_SKINNY = 3
 TILE_N128 = 0x10
 TILE_N192 = 0x40
 ACCUMULATE = 0x20
+E4M3 = 0
+E5M2 = 1
 
 # Every symbol include/wave_b200.h declares; tests check that the built library exports them all.
 EXPORTED_SYMBOLS = (
@@ -47,6 +49,7 @@ EXPORTED_SYMBOLS = (
     "wb200_workspace_init",
     "wb200_mxfp4_gemm",
     "wb200_mxfp4_gemm_repack_a",
+    "wb200_mxfp8_gemm",
     "wb200_mxfp4_gemm_skinny_noalloc",
     "wb200_mxfp4_grouped_gemm",
     "wb200_moe_align_block_size",
@@ -115,6 +118,9 @@ def load() -> ctypes.CDLL:
     lib.wb200_mxfp4_gemm_repack_a.restype = c_int
     lib.wb200_mxfp4_gemm_repack_a.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_int, c_ll, c_void_p, c_size_t, c_uint, c_void_p]
+    lib.wb200_mxfp8_gemm.restype = c_int
+    lib.wb200_mxfp8_gemm.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_ll,
+                                     c_int, c_uint, c_void_p]
     lib.wb200_mxfp4_gemm_skinny_noalloc.restype = c_int
     lib.wb200_mxfp4_gemm_skinny_noalloc.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                     c_int, c_ll, c_uint, c_void_p]

@@ -149,8 +149,28 @@ class ScaledGemmKernel:
         if rc:
             _lib.check(rc)
 
+    def _invoke_mxfp8(self, a, a_scale, b, b_scale, c) -> None:
+        t = self.template
+        for name, x in (("a", a), ("b", b)):
+            if x.element_size() != 1 or x.dim() != 2 or not x.is_cuda:
+                raise ValueError(f"{name} must be a 2-D CUDA tensor of 8-bit elements, got {x.dtype} {tuple(x.shape)}")
+        if c.dtype != t.output_dtype.torch_dtype:
+            raise ValueError(f"this kernel writes {t.output_dtype}; got an output tensor of {c.dtype}")
+        a, b = a.contiguous(), b.contiguous()  # non-contiguous inputs are copied, as the reference does (run_utils.py:106-109)
+        M, K = a.shape
+        N = b.shape[0]
+        if self._static is not None and self._static != (M, N, K):
+            raise ValueError(f"kernel was built for (M, N, K) = {self._static}, called with {(M, N, K)}")
+        a_sf = a_scale if isinstance(a_scale, ops.PackedScales) else self._pack_activation_scales(a_scale, M, K)
+        b_sf = b_scale if isinstance(b_scale, ops.PackedScales) else self._weight_scales.get(self._check_scale(b_scale, N, K, "b_scale"))
+        fmt = _lib.E5M2 if t.element_format == "f8e5m2" else _lib.E4M3
+        flags = self.options.kernel_path | (_lib.ACCUMULATE if t.accumulate else 0)
+        ops.scaled_gemm_mxfp8_packed(a, a_sf, b, b_sf, c, fmt, flags)
+
     def _invoke_checked(self, a, a_scale, b, b_scale, c) -> None:
         t = self.template
+        if t.element_bits == 8:
+            return self._invoke_mxfp8(a, a_scale, b, b_scale, c)
         if a.dim() == 3:  # batched activations, shared weights (tests/kernel/wave_gemm_mxfp_test.py:205-288)
             if c.dim() != 3 or not c.is_contiguous():
                 raise ValueError("batched call needs a contiguous 3-D output")

@@ -135,10 +135,10 @@ int make_operand_map(CUtensorMap* map, const void* base, long long rows, long lo
 }
 
 // Packed scale array ([row_blocks][k_atoms][512 bytes]) as a 2-D tensor of 32-bit words, one
-// row per 128-row block; a box is 1024 bytes (the two atoms of one pipeline stage) x box_rows.
-int make_scale_map(CUtensorMap* map, const void* base, int row_blocks, int k_atoms, int box_rows) {
+// row per 128-row block; a box is box_atoms atoms of 512 bytes (those of one pipeline stage) x box_rows.
+int make_scale_map(CUtensorMap* map, const void* base, int row_blocks, int k_atoms, int box_rows, int box_atoms = 2) {
   const MapKey k{base, (unsigned long long)k_atoms * 128, (unsigned long long)row_blocks, (unsigned long long)k_atoms * 512,
-                 256u, unsigned(box_rows), int(CU_TENSOR_MAP_DATA_TYPE_UINT32), int(CU_TENSOR_MAP_SWIZZLE_NONE),
+                 unsigned(box_atoms) * 128u, unsigned(box_rows), int(CU_TENSOR_MAP_DATA_TYPE_UINT32), int(CU_TENSOR_MAP_SWIZZLE_NONE),
                  int(CU_TENSOR_MAP_L2_PROMOTION_L2_256B)};
   CUresult r = encode_2d(map, k);
   if (r != CUDA_SUCCESS)
@@ -194,21 +194,23 @@ int make_output_map(CUtensorMap* map, void* c, int M, int N, long long ldc, int 
   return WB200_OK;
 }
 
-template <int CG, int BN, typename OutT>
+// EB: bits per operand element (4: MXFP4, 8: MXFP8 with elem_format 0 = E4M3 / 1 = E5M2).
+template <int CG, int BN, typename OutT, int EB = 4>
 int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                 const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, int accumulate,
-                cudaStream_t stream) {
-  using Cfg = wb::GemmCfg<CG, BN, int(sizeof(OutT))>;
+                cudaStream_t stream, int elem_format = 0) {
+  using Cfg = wb::GemmCfg<CG, BN, int(sizeof(OutT)), EB>;
   wb::PlainMaps maps;
   CUtensorMap& tmA = maps.m[0];
   CUtensorMap& tmC = maps.m[4];
-  int rc = make_operand_map(&maps.m[0], a, M, K / 2, Cfg::BM);
+  const long long row_bytes = (long long)K * EB / 8;
+  int rc = make_operand_map(&maps.m[0], a, M, row_bytes, Cfg::BM);
   if (rc) return rc;
-  rc = make_operand_map(&maps.m[1], b, N, K / 2, Cfg::B_ROWS);
+  rc = make_operand_map(&maps.m[1], b, N, row_bytes, Cfg::B_ROWS);
   if (rc) return rc;
-  rc = make_scale_map(&maps.m[2], as, sfa_row_blocks, wb::sf_k_atoms(K), 1);
+  rc = make_scale_map(&maps.m[2], as, sfa_row_blocks, wb::sf_k_atoms(K), 1, Cfg::SF_ATOMS);
   if (rc) return rc;
-  rc = make_scale_map(&maps.m[3], bs, sfb_row_blocks, wb::sf_k_atoms(K), Cfg::SFB_BLOCKS);
+  rc = make_scale_map(&maps.m[3], bs, sfb_row_blocks, wb::sf_k_atoms(K), Cfg::SFB_BLOCKS, Cfg::SF_ATOMS);
   if (rc) return rc;
   wb::GemmParams p;
   p.c = c;
@@ -220,6 +222,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   const int esz = int(sizeof(OutT));
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0) ? 1 : 0;
   p.accumulate = accumulate;
+  p.elem_format = elem_format;
   p.tma_store = (p.vec_ok && !accumulate) ? 1 : 0;
   if (p.tma_store) {
     rc = make_output_map(&tmC, c, M, N, ldc, esz);
@@ -228,7 +231,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
     tmC = tmA;  // never dereferenced by the kernel on the direct-store path
   }
   p.status = dev.status_ptr;
-  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT, wb::PlainMaps>;
+  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT, wb::PlainMaps, EB>;
   static bool smem_set[kMaxDevices] = {};
   rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
   if (rc) return rc;
@@ -779,6 +782,46 @@ int wb200_mxfp4_gemm_repack_a(int M, int N, int K, const void* a, const void* a_
   if (rc) return rc;
   return wb200_mxfp4_gemm(M, N, K, a, a_scale_scratch, b, b_scale_packed, c, c_dtype, ldc, workspace, workspace_bytes, flags,
                           stream);
+}
+
+extern "C++" {
+template <int CG, int BN>
+static int launch_mxfp8(int c_dtype, const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
+                        const void* bs, void* c, long long ldc, int accumulate, cudaStream_t s, int elem_format) {
+  if (c_dtype == WB200_F32)
+    return launch_tile<CG, BN, float, 8>(dev, M, N, K, a, as, b, bs, c, ldc, wb::sf_row_blocks(M), wb::sf_row_blocks(N),
+                                         accumulate, s, elem_format);
+  return launch_tile<CG, BN, __nv_bfloat16, 8>(dev, M, N, K, a, as, b, bs, c, ldc, wb::sf_row_blocks(M), wb::sf_row_blocks(N),
+                                               accumulate, s, elem_format);
+}
+}  // extern "C++"
+
+int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,
+                     const void* b_scale_packed, void* c, int c_dtype, long long ldc, int elem_format, unsigned flags,
+                     void* stream) {
+  int rc = check_common(M, N, K, a, a_scale_packed, b, b_scale_packed, c, c_dtype, ldc);
+  if (rc) return rc;
+  if (elem_format != WB200_E4M3 && elem_format != WB200_E5M2)
+    return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown element format %d", elem_format);
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE)) != 0)
+    return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown flag bits %#x", flags);
+  unsigned path = flags & WB200_PATH_MASK;
+  if (path == WB200_PATH_SKINNY || path > WB200_PATH_SKINNY)
+    return fail(WB200_ERR_UNSUPPORTED, "mxfp8_gemm runs on the tile paths only (path flag %u)", path);
+  DeviceInfo* dev;
+  rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int accumulate = (flags & WB200_ACCUMULATE) ? 1 : 0;
+  if (path == WB200_PATH_AUTO) path = (M > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
+  bool n128 = (flags & WB200_TILE_N128) != 0;
+  if (!n128 && (flags & WB200_PATH_MASK) == WB200_PATH_AUTO)
+    n128 = (long long)((M + 127) / 128) * ((N + 255) / 256) < dev->sm_count;
+  if (path == WB200_PATH_TILE_2CTA)
+    return n128 ? launch_mxfp8<2, 128>(c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, accumulate, s, elem_format)
+                : launch_mxfp8<2, 256>(c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, accumulate, s, elem_format);
+  return n128 ? launch_mxfp8<1, 128>(c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, accumulate, s, elem_format)
+              : launch_mxfp8<1, 256>(c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, accumulate, s, elem_format);
 }
 
 int wb200_mxfp4_gemm_skinny_noalloc(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,

@@ -28,22 +28,29 @@
 
 namespace wb {
 
-template <int CG, int BN_, int OUT_BYTES>
+// EB: bits per operand element, 4 (MXFP4, kind::mxf4) or 8 (MXFP8, kind::mxf8f6f4). Either way a pipeline
+// stage is one 128-byte swizzle row of every operand row and four MMAs of 32 bytes of K each; what
+// differs is the K extent of a stage (256 or 128 elements) and hence its scale factors (8 or 4 K-blocks
+// per row = 2 or 1 atoms per 128 rows).
+template <int CG, int BN_, int OUT_BYTES, int EB = 4>
 struct GemmCfg {
+  static_assert(EB == 4 || EB == 8, "operand elements are 4 or 8 bits");
   static constexpr int BM = 128;  // accumulator rows per CTA (tensor-memory lanes)
   static constexpr int BN = BN_;
-  static constexpr int BK = 256;  // K elements per pipeline stage = one 128-byte swizzle row
+  static constexpr int BK = 1024 / EB;  // K elements per pipeline stage = one 128-byte swizzle row
+  static constexpr int SF_ATOMS = BK / 128;  // scale-factor atoms (4 K-blocks each) per 128 rows and stage
   static constexpr int B_ROWS = BN / CG;  // B rows this CTA loads
   static constexpr int A_BYTES = BM * 128;
   static constexpr int B_BYTES = B_ROWS * 128;
-  static constexpr int SFA_BYTES = 2 * 512;               // 128 rows x 8 K-blocks
+  static constexpr int SFA_BYTES = SF_ATOMS * 512;        // 128 rows x BK / 32 K-blocks
   // Packed scales come in blocks of 128 rows = 4 tensor-memory columns of 32 rows each. A 192-row
   // tile starts at column 0 or 2 of a block and ends inside the next one: the kernel loads both
   // blocks and points the MMA at the column the tile starts with. (The MMA takes even column
   // offsets only: an odd one, as a 224-row tile would need, raises a misaligned-address fault.)
   static constexpr int SFB_BLOCKS = (BN % 128 == 0) ? BN / 128 : (BN + 64 + 127) / 128;
-  static constexpr int SFB_BYTES = SFB_BLOCKS * 2 * 512;  // blocks x 8 K-blocks
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int SFB_BYTES = SFB_BLOCKS * SF_ATOMS * 512;
+  static constexpr int LOAD_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;  // what the loads of a stage deliver
+  static constexpr int STAGE_BYTES = (LOAD_BYTES + 1023) / 1024 * 1024;
   // Epilogue staging: each of the 4 epilogue warps owns two buffers of 32 rows x 32 columns of C,
   // written with the TMA store swizzle (64-byte rows for bf16, 128-byte rows for f32).
   // A buffer is 32 rows of 128 bytes: one 32-column chunk of f32, or two neighbouring chunks of bf16
@@ -62,6 +69,7 @@ struct GemmCfg {
   static constexpr int ACC_COL0 = 0;
   // Scale factors live in a small ring of column sets so that the tcgen05.cp of one K block does
   // not have to wait for the MMAs of the previous block to finish reading theirs.
+  // (sized for two atoms per 128 rows also when a stage has one, so that the accumulators sit at the same columns)
   static constexpr int SF_SET_COLS = 8 + SFB_BLOCKS * 8;  // A: 2 atoms x 4 columns, B: blocks x 2 atoms x 4
   static constexpr int SF_SETS = OVERLAP ? 2 : 4;
   static constexpr int SF_COL = OVERLAP ? 512 - SF_SETS * SF_SET_COLS : 2 * BN;
@@ -85,6 +93,7 @@ struct GemmParams {
   int vec_ok;         // C base and row pitch allow 16-byte stores
   int tma_store;      // write C with TMA stores from swizzled shared memory (needs vec_ok, no accumulate)
   int accumulate;     // add to the values already in C instead of overwriting them
+  int elem_format;    // 8-bit operands only: 0 = E4M3, 1 = E5M2
   int* status;
 };
 
@@ -224,10 +233,10 @@ __device__ __forceinline__ void stage_chunk32(uint32_t buf, int lane, int half, 
   }
 }
 
-template <int CG, int BN, typename OutT, typename Maps>
+template <int CG, int BN, typename OutT, typename Maps, int EB = 4>
 __global__ void __launch_bounds__(192, 1)
 mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
-  using Cfg = GemmCfg<CG, BN, int(sizeof(OutT))>;
+  using Cfg = GemmCfg<CG, BN, int(sizeof(OutT)), EB>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle; identical offset in both CTAs of a pair.
@@ -307,12 +316,12 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
         // therefore expects the bytes of two stages; the second CTA only issues its copies.
         const uint32_t fb = (CG == 2) ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
         if (elect_one()) {
-          if (leader) mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES * CG);
+          if (leader) mbar_expect_tx(full_bar(stage), Cfg::LOAD_BYTES * CG);
           tma_load_2d<CG>(sA, tm + 0, kb * 128, a_row, fb);
           tma_load_2d<CG>(sB, tm + 1, kb * 128, b_row, fb);
-          // scale factors: 1024 bytes (two atoms) per 128-row block and stage
-          tma_load_2d<CG>(sSFA, tm + 2, kb * 256, sfa_rb, fb);
-          tma_load_2d<CG>(sSFB, tm + 3, kb * 256, sfb_rb, fb);
+          // scale factors: SF_ATOMS atoms of 512 bytes (128 32-bit words) per 128-row block and stage
+          tma_load_2d<CG>(sSFA, tm + 2, kb * (Cfg::SF_ATOMS * 128), sfa_rb, fb);
+          tma_load_2d<CG>(sSFB, tm + 3, kb * (Cfg::SF_ATOMS * 128), sfb_rb, fb);
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -321,7 +330,8 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader) {
-      constexpr uint32_t idesc = make_idesc_mxf4(Cfg::BM * CG, BN);
+      const uint32_t idesc = (EB == 4) ? make_idesc_mxf4(Cfg::BM * CG, BN)
+                                       : make_idesc_mxf8(Cfg::BM * CG, BN, uint32_t(p.elem_format));
       const uint32_t peer_empty0 = (CG == 2) ? mapa_shared(empty_bar(0), 1) : 0u;
       const uint32_t peer_acc_full0 = (CG == 2) ? mapa_shared(acc_full_bar(0), 1) : 0u;
       uint32_t stage = 0, phase = 0, sf_set = 0;
@@ -368,20 +378,26 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
             // descriptor's address field = +512 bytes = the next atom
             {
 #pragma unroll
-              for (int a = 0; a < 2; ++a) utccp_sf_atom<CG>(t_sfa + a * 4, sfa_desc + uint64_t(a * 32));
+              for (int a = 0; a < Cfg::SF_ATOMS; ++a) utccp_sf_atom<CG>(t_sfa + a * 4, sfa_desc + uint64_t(a * 32));
 #pragma unroll
               for (int j = 0; j < Cfg::SFB_BLOCKS; ++j)
 #pragma unroll
-                for (int a = 0; a < 2; ++a)
-                  utccp_sf_atom<CG>(t_sfb + a * (Cfg::SFB_BLOCKS * 4) + j * 4, sfb_desc + uint64_t(j * 64 + a * 32));
+                for (int a = 0; a < Cfg::SF_ATOMS; ++a)
+                  utccp_sf_atom<CG>(t_sfb + a * (Cfg::SFB_BLOCKS * 4) + j * 4,
+                                    sfb_desc + uint64_t((j * Cfg::SF_ATOMS + a) * 32));
             }
             {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                // K = 64 per instruction = 32 bytes inside the 128-byte swizzle row
-                mma_mxf4<CG>(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2),
-                             idesc_with_sf_id(idesc, (k & 1) * 2), t_sfa + (k >> 1) * 4,
-                             t_sfb + (k >> 1) * (Cfg::SFB_BLOCKS * 4) + sfb_group, (kb > 0 || k > 0) ? 1u : 0u);
+                // one instruction = 32 bytes of K inside the 128-byte swizzle row: 64 E2M1 values with two
+                // scales each (bytes 0,1 or 2,3 of the atom's column), or 32 8-bit values with one scale (byte k)
+                if constexpr (EB == 4)
+                  mma_mxf4<CG>(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2),
+                               idesc_with_sf_id(idesc, (k & 1) * 2), t_sfa + (k >> 1) * 4,
+                               t_sfb + (k >> 1) * (Cfg::SFB_BLOCKS * 4) + sfb_group, (kb > 0 || k > 0) ? 1u : 0u);
+                else
+                  mma_mxf8<CG>(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2), idesc_with_sf_id(idesc, k),
+                               t_sfa, t_sfb + sfb_group, (kb > 0 || k > 0) ? 1u : 0u);
               }
             }
             // free the stage in both CTAs once these MMAs have read it

@@ -304,6 +304,13 @@ __device__ __forceinline__ uint32_t idesc_with_sf_id(uint32_t idesc, uint32_t sf
   return idesc | (sf_id << 4) | (sf_id << 29);
 }
 
+// Instruction descriptor of kind::mxf8f6f4 block-scaled with 8-bit operands: fmt 0 = E4M3, 1 = E5M2 (both
+// operands the same), K-major, UE8M0 scales, K = 32 per instruction; the scale-factor id (0..3) picks
+// the byte of the 32-bit scale column that this K = 32 step reads.
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n, uint32_t fmt) {
+  return (fmt << 7) | (fmt << 10) | (uint32_t(n >> 3) << 17) | (1u << 23) | (uint32_t(m >> 4) << 24);
+}
+
 template <int CTA_GROUP>
 __device__ __forceinline__ void utccp_sf_atom(uint32_t taddr, uint64_t sdesc) {
   if constexpr (CTA_GROUP == 1)
@@ -332,6 +339,29 @@ __device__ __forceinline__ void mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint6
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X "
+        "[%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
+// The same with 8-bit operands (MXFP8): one E8M0 scale per 32 elements = per instruction.
+template <int CTA_GROUP>
+__device__ __forceinline__ void mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                         uint32_t accumulate) {
+  if constexpr (CTA_GROUP == 1)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X "
+        "[%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X "
         "[%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
         : "memory");

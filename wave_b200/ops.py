@@ -155,6 +155,33 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
         _lib.check(rc)
 
 
+_FP8_FORMATS = {torch.float8_e5m2: _lib.E5M2, torch.float8_e4m3fn: _lib.E4M3}
+
+
+def scaled_gemm_mxfp8_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_sf: PackedScales, c: torch.Tensor,
+                             elem_format: int | None = None, flags: int = 0) -> None:
+    """c [M, N] = dequant(a) @ dequant(b)^T for 8-bit operands a [M, K], b [N, K] (torch float8 tensors, or
+    int8 / uint8 bytes with `elem_format` given) and packed E8M0 scales, on the current stream."""
+    lib = _lib.load()
+    if elem_format is None:
+        if a.dtype not in _FP8_FORMATS:
+            raise ValueError(f"give elem_format for operands of type {a.dtype}")
+        elem_format = _FP8_FORMATS[a.dtype]
+    for name, t in (("a", a), ("b", b)):
+        if t.element_size() != 1 or t.dim() != 2 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous 2-D CUDA tensor of 8-bit elements")
+    M, K = a.shape
+    N = b.shape[0]
+    if b.shape[1] != K or (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
+        raise ValueError("operand and scale shapes do not agree")
+    if c.dtype not in _DTYPE_CODE or tuple(c.shape) != (M, N) or c.stride(1) != 1:
+        raise ValueError(f"c must be f32 or bf16 [{M}, {N}] with unit column stride")
+    with torch.cuda.device(a.device):
+        _lib.check(lib.wb200_mxfp8_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
+                                        c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0) if M > 1 else N, elem_format, flags,
+                                        _stream()))
+
+
 class WeightScaleCache:
     """Packed copies of weight scales, keyed by the identity and version of the row-major tensor,
     so that a weight's scales are repacked once and reused by later calls."""

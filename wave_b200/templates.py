@@ -32,6 +32,8 @@ class ScaledGemmTemplate:
     preshuffled_scales: bool = False       # scale arguments are PackedScales from e8m0_shuffle
     preshuffled_b: bool = False            # b went through b_preshuffle (identity on B200)
     broadcast_a_scale: bool = False        # a_scale is [M]: one scale per row for all of K
+    element_bits: int = 4                  # 4: packed E2M1 (MXFP4); 8: one byte per element (MXFP8)
+    element_format: str = "f4e2m1fn"       # MXFP8: "f8e5m2" or "f8e4m3fn"
     hints: dict = field(default_factory=dict)
 
 
@@ -68,6 +70,20 @@ def get_broadcasted_scale_gemm_mxfp4(shape, mfma_variant: ScaledMMAType):
         raise TypeError("mfma_variant must be a ScaledMMAType")
     tpl = ScaledGemmTemplate("broadcasted_scale_scaled_mma", tuple(shape), f32, broadcast_a_scale=True,
                              hints={"mfma_variant": mfma_variant, "block_shape": (32, 32, 256)})
+    return tpl, _hyperparams(shape, (32, 32, 256), {"ADDRESS_SPACE": SHARED_ADDRESS_SPACE})
+
+
+def get_scaled_gemm_mxfp8_kernel(shape, mfma_variant: ScaledMMAType, element_format: str = "f8e5m2", output_dtype=f32):
+    """(kernel, hyperparams) for the MXFP8 scaled GEMM: a [M, K], b [N, K] bytes of f8e5m2 (or f8e4m3fn),
+    E8M0 scales [rows, K/32], c [M, N]. The reference has this kernel only inside its test
+    (tests/kernel/wave_gemm_mxfp_test.py:416-501: same signature as the MXFP4 kernel with K instead of K/2
+    columns and a bitcast to f8e5m2); this function gives it the template form of get_scaled_gemm_kernel."""
+    if not isinstance(mfma_variant, ScaledMMAType):
+        raise TypeError("mfma_variant must be a ScaledMMAType")
+    if element_format not in ("f8e5m2", "f8e4m3fn"):
+        raise ValueError(f"unknown 8-bit element format {element_format}")
+    tpl = ScaledGemmTemplate("scaled_gemm_mxfp8", tuple(shape), as_output_dtype(output_dtype), element_bits=8,
+                             element_format=element_format, hints={"mfma_variant": mfma_variant, "block_shape": (32, 32, 256)})
     return tpl, _hyperparams(shape, (32, 32, 256), {"ADDRESS_SPACE": SHARED_ADDRESS_SPACE})
 
 
