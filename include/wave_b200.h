@@ -213,6 +213,34 @@ int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* 
                              const void* const* b_ptrs, const void* const* b_scale_ptrs, void* c,
                              int c_dtype, long long ldc, void* stream);
 
+/* ---- K-sharded multi-GPU GEMM: compute step with its output scattered by rows ------------------- */
+
+/* c_p = a[row_offsets[p] : row_offsets[p+1], :] * b^T for every part p, part p written to the matrix at
+ * c_ptrs[p] ([rows of p, N], pitch ldc, 16-byte aligned), in ONE persistent launch whose tiles are stored
+ * as they finish. The output matrices may be another GPU's memory mapped into this process (CUDA IPC /
+ * peer access): a rank of a K-sharded GEMM deposits its partial products for rows owned by rank p directly
+ * in p's receive buffer over NVLink while the remaining tiles are still being computed. Parts start at
+ * multiples of 128 rows (HOST arrays; up to 32 parts). The reference distributes GEMMs by M / N tiles only
+ * (wave_lang/kernel/wave/templates/dist_gemm.py:49-50); it has no K-sharded form. */
+#define WB200_SCATTER_TMA_STORE 1u /* write the outputs with TMA stores instead of ordinary 16-byte stores */
+int wb200_mxfp4_gemm_scatter_rows(int num_parts, const int* row_offsets, int N, int K, const void* a,
+                                  const void* a_scale_packed, const void* b, const void* b_scale_packed, void* const* c_ptrs,
+                                  int c_dtype, long long ldc, unsigned flags, void* stream);
+
+/* Receive buffers of the K-sharded GEMM, shared between the processes of one node with CUDA IPC.
+ * create: cudaMalloc + zero fill on the current device, returns the pointer and a 64-byte handle to send to
+ * the other processes; open: maps another process's buffer for the CURRENT device (the device whose kernels
+ * will write to it; peer access to the owner is enabled as needed); close / destroy undo open / create. */
+int wb200_peer_buffer_create(size_t bytes, void** ptr, void* handle64);
+int wb200_peer_buffer_open(const void* handle64, void** ptr);
+int wb200_peer_buffer_close(void* ptr);
+int wb200_peer_buffer_destroy(void* ptr);
+
+/* out[i] = slots[0][i] + slots[1][i] + ... (f32, slot order, i < count; slot s starts at slots + s * slot_stride),
+ * rounded once to out_dtype: the reduction over the ranks' partial products. */
+int wb200_sum_slots(const float* slots, int num_slots, long long slot_stride, long long count, void* out, int out_dtype,
+                    void* stream);
+
 #ifdef __cplusplus
 }
 #endif

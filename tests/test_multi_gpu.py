@@ -138,3 +138,160 @@ def test_gpu_ranks_shard_and_gather():
     for p in procs:
         p.join(timeout=60)
     assert all(ok for _, ok in results)
+
+
+# ---------------------------------------------------------------------------------------------
+# K-sharded variant: partial products scattered by rows, summed in rank order
+# ---------------------------------------------------------------------------------------------
+def _k_operands(M, N, K, seed):
+    g = torch.Generator().manual_seed(seed)  # same operands on every rank
+    a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, generator=g)
+    b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+    a_s = torch.randint(124, 131, (M, K // 32), dtype=torch.uint8, generator=g)
+    b_s = torch.randint(124, 131, (N, K // 32), dtype=torch.uint8, generator=g)
+    return a, a_s, b, b_s
+
+
+def _cpu_rank_ksharded(rank, world, port, M, K, out_queue):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, str(ROOT))
+    from oracle import mxfp4_oracle as orc
+    import wave_b200 as wb
+    from wave_b200.multi_gpu import KShardedScaledGemm
+
+    class CpuStandIn(KShardedScaledGemm):
+        """Same partitioning, slot order and double buffering; the GEMM is the oracle, the scatter is send/recv."""
+
+        def _pack_scales(self, scale):
+            return scale
+
+        def _exchange_buffers(self, device):
+            self._recv = torch.zeros(2, self.world_size, self.rows_max, self.N, dtype=torch.float32)
+            return None
+
+        def _scatter_gemm(self, a, a_scale, parity):
+            part = orc.scaled_gemm(a, a_scale, self._b, self._b_sf)
+            reqs, keep = [], []
+            for d, (m0, m1) in enumerate(self.row_bounds):
+                if d == self.rank:
+                    self._recv[parity, self.rank, : m1 - m0] = part[m0:m1]
+                elif m1 > m0:
+                    keep.append(part[m0:m1].contiguous())
+                    reqs.append(dist.isend(keep[-1], d))
+            rows = self.m1 - self.m0
+            bufs = {}
+            for s in range(self.world_size):
+                if s != self.rank and rows:
+                    bufs[s] = torch.empty(rows, self.N)
+                    reqs.append(dist.irecv(bufs[s], s))
+            for r in reqs:
+                r.wait()
+            for s, t in bufs.items():
+                self._recv[parity, s, :rows] = t
+
+        def _barrier(self):
+            dist.barrier()
+
+        def _reduce(self, parity, out):
+            rows = self.m1 - self.m0
+            acc = self._recv[parity, 0, :rows].clone()
+            for s in range(1, self.world_size):
+                acc += self._recv[parity, s, :rows]
+            out.copy_(acc)
+
+    N = 96
+    a, a_s, b, b_s = _k_operands(M, N, K, seed=13)
+    op = CpuStandIn(M, N, K, wb.f32)
+    k0, k1 = op.k0, op.k1
+    with pytest.raises(ValueError):
+        op.load_weight_shard(b[:, : k1 // 2 - k0 // 2 + 1], b_s[:, k0 // 32:k1 // 32])
+    op.load_weight_shard(b[:, k0 // 2:k1 // 2], b_s[:, k0 // 32:k1 // 32])
+    ref = orc.scaled_gemm(a, a_s, b, b_s)
+    tol = orc.f32_tolerance(orc.dequant_mxfp4(a, a_s), orc.dequant_mxfp4(b, b_s), ref, K)
+    ok = True
+    for _ in range(3):  # alternating receive buffers
+        rows = op(a[:, k0 // 2:k1 // 2], a_s[:, k0 // 32:k1 // 32])
+        ok = ok and bool(((rows - ref[op.m0:op.m1]).abs() <= tol[op.m0:op.m1]).all())
+    full = op(a[:, k0 // 2:k1 // 2], a_s[:, k0 // 32:k1 // 32], gather=True)
+    ok = ok and bool(((full - ref).abs() <= tol).all())
+    out_queue.put((rank, ok, (op.k0, op.k1), (op.m0, op.m1)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("M,K", [(256, 512), (300, 1024), (100, 768)])  # equal parts, ragged rows, one rank without rows / uneven K
+def test_two_cpu_ranks_k_sharded(M, K):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_cpu_rank_ksharded, args=(r, 2, port, M, K, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _, _ in results)
+    assert results[0][2][0] == 0 and results[0][2][1] == results[1][2][0] and results[1][2][1] == K
+    assert results[0][3][0] == 0 and results[0][3][1] == results[1][3][0] and results[1][3][1] == M
+    assert results[0][2][1] % 256 == 0 and (results[0][3][1] % 128 == 0 or results[0][3][1] == M)
+
+
+def _gpu_rank_ksharded(rank, world, port, out_queue):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    sys.path.insert(0, str(ROOT))
+    from oracle import mxfp4_oracle as orc
+    import wave_b200 as wb
+    from wave_b200.multi_gpu import KShardedScaledGemm
+    dev = torch.device("cuda", rank)
+    ok = True
+    for (M, N, K) in [(512, 768, 1024 * world), (300, 1000, 512 * world + 256)]:
+        a, a_s, b, b_s = _k_operands(M, N, K, seed=17)
+        op = KShardedScaledGemm(M, N, K, wb.bf16)
+        k0, k1 = op.k0, op.k1
+        op.load_weight_shard(b[:, k0 // 2:k1 // 2].to(dev), b_s[:, k0 // 32:k1 // 32].to(dev))
+        ref = orc.scaled_gemm(a, a_s, b, b_s)
+        tol = orc.f32_tolerance(orc.dequant_mxfp4(a, a_s), orc.dequant_mxfp4(b, b_s), ref, K)
+        ad, asd = a[:, k0 // 2:k1 // 2].to(dev), a_s[:, k0 // 32:k1 // 32].to(dev)
+        first = None
+        for _ in range(3):
+            rows = op(ad, asd)
+            torch.cuda.synchronize()
+            r = ref[op.m0:op.m1]
+            ulp = orc.bf16_ulp_distance(rows, r)
+            bad = (ulp > 1) & ~((rows.float().cpu() - r).abs() <= tol[op.m0:op.m1] + r.abs() * 2.0 ** -8)
+            ok = ok and not bool(bad.any())
+            if first is None:
+                first = rows.clone()
+            ok = ok and torch.equal(first, rows)  # fixed slot order: the same bits every call
+        full = op(ad, asd, gather=True)
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(full[op.m0:op.m1], first)
+        ulp = orc.bf16_ulp_distance(full, ref)
+        ok = ok and not bool(((ulp > 1) & ~((full.float().cpu() - ref).abs() <= tol + ref.abs() * 2.0 ** -8)).any())
+        wb.ops.check_device_status()
+        dist.barrier()
+        op.close()
+    out_queue.put((rank, bool(ok)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_gpu_ranks_k_sharded_scatter_and_sum():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_rank_ksharded, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok in results)

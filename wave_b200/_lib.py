@@ -56,6 +56,12 @@ EXPORTED_SYMBOLS = (
     "wb200_moe_gather_rows",
     "wb200_silu_and_mul",
     "wb200_moe_combine",
+    "wb200_mxfp4_gemm_scatter_rows",
+    "wb200_peer_buffer_create",
+    "wb200_peer_buffer_open",
+    "wb200_peer_buffer_close",
+    "wb200_peer_buffer_destroy",
+    "wb200_sum_slots",
 )
 
 
@@ -139,6 +145,19 @@ def load() -> ctypes.CDLL:
     lib.wb200_moe_combine.restype = c_int
     lib.wb200_moe_combine.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_ll,
                                       c_void_p]
+    lib.wb200_mxfp4_gemm_scatter_rows.restype = c_int
+    lib.wb200_mxfp4_gemm_scatter_rows.argtypes = [c_int, ctypes.POINTER(c_int), c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                  c_void_p, ctypes.POINTER(c_void_p), c_int, c_ll, c_uint, c_void_p]
+    lib.wb200_peer_buffer_create.restype = c_int
+    lib.wb200_peer_buffer_create.argtypes = [c_size_t, ctypes.POINTER(c_void_p), c_void_p]
+    lib.wb200_peer_buffer_open.restype = c_int
+    lib.wb200_peer_buffer_open.argtypes = [c_void_p, ctypes.POINTER(c_void_p)]
+    lib.wb200_peer_buffer_close.restype = c_int
+    lib.wb200_peer_buffer_close.argtypes = [c_void_p]
+    lib.wb200_peer_buffer_destroy.restype = c_int
+    lib.wb200_peer_buffer_destroy.argtypes = [c_void_p]
+    lib.wb200_sum_slots.restype = c_int
+    lib.wb200_sum_slots.argtypes = [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p]
     _lib = lib
     return lib
 

@@ -280,7 +280,9 @@ int dispatch_tile(unsigned path, int bn, int c_dtype, const DeviceInfo& dev, int
 template <typename OutT>
 int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets, const int* row_block_offsets, int N, int K,
                    const void* a, const void* a_sf, const void* const* b_ptrs, const void* const* b_sf_ptrs, void* c,
-                   long long ldc, cudaStream_t stream) {
+                   long long ldc, cudaStream_t stream, void* const* c_ptrs = nullptr, int store_mode = 1) {
+  // c_ptrs (optional): group g writes its rows to the matrix that starts at c_ptrs[g] instead of to rows
+  // row_offsets[g].. of c; the matrices may live in another GPU's memory mapped into this process.
   constexpr int CG = 2, BN = 256;
   using Cfg = wb::GemmCfg<CG, BN, int(sizeof(OutT))>;
   static wb::GroupedMaps maps;  // ~21 KB: too large for comfort on the stack; guarded by the mutex below
@@ -291,35 +293,40 @@ int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets
   const size_t atom_row_bytes = size_t(k_atoms) * 512;
   const int tiles_n = (N + BN - 1) / BN;
   maps.num_groups = num_groups;
+  maps.interleave = (c_ptrs != nullptr) ? 1 : 0;
+  maps.tiles_max = 0;
   maps.tile_start[0] = 0;
   for (int g = 0; g < num_groups; ++g) {
     const int r0 = row_offsets[g], Mg = row_offsets[g + 1] - r0;
     maps.rows[g] = Mg;
     maps.tile_start[g + 1] = maps.tile_start[g] + ((Mg + Cfg::BM * CG - 1) / (Cfg::BM * CG)) * tiles_n;
+    if (maps.tile_start[g + 1] - maps.tile_start[g] > maps.tiles_max) maps.tiles_max = maps.tile_start[g + 1] - maps.tile_start[g];
     if (Mg == 0) continue;
     const uint8_t* ag = static_cast<const uint8_t*>(a) + size_t(r0) * (K / 2);
     const uint8_t* asg = static_cast<const uint8_t*>(a_sf) + size_t(row_block_offsets[g]) * atom_row_bytes;
-    uint8_t* cg = static_cast<uint8_t*>(c) + size_t(r0) * ldc * esz;
+    uint8_t* cg = c_ptrs ? static_cast<uint8_t*>(c_ptrs[g]) : static_cast<uint8_t*>(c) + size_t(r0) * ldc * esz;
     int rc = check_common(Mg, N, K, ag, asg, b_ptrs[g], b_sf_ptrs[g], cg, esz == 4 ? WB200_F32 : WB200_BF16, ldc);
     if (rc) return rc;
+    if (reinterpret_cast<uintptr_t>(cg) & 15) return fail(WB200_ERR_ALIGNMENT, "group %d: output must be 16-byte aligned", g);
     CUtensorMap* m = &maps.m[g * 5];
     if ((rc = make_operand_map(m + 0, ag, Mg, K / 2, Cfg::BM))) return rc;
     if ((rc = make_operand_map(m + 1, b_ptrs[g], N, K / 2, Cfg::B_ROWS))) return rc;
     if ((rc = make_scale_map(m + 2, asg, wb::sf_row_blocks(Mg), k_atoms, 1))) return rc;
     if ((rc = make_scale_map(m + 3, b_sf_ptrs[g], wb::sf_row_blocks(N), k_atoms, BN / 128))) return rc;
     if ((rc = make_output_map(m + 4, cg, Mg, N, ldc, esz))) return rc;
+    maps.c_base[g] = cg;
   }
   const int tiles = maps.tile_start[num_groups];
   if (tiles == 0) return WB200_OK;
   wb::GemmParams p = {};
-  p.c = c;
+  p.c = c;  // not dereferenced: the grouped kernel writes through each group's output map
   p.M = row_offsets[num_groups]; p.N = N; p.K = K;
   p.ldc = int(ldc);
   p.tiles_m = 0;
   p.tiles_n = tiles_n;
   p.group_n = 16;
   p.vec_ok = 1;
-  p.tma_store = 1;
+  p.tma_store = store_mode;
   p.accumulate = 0;
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT, wb::GroupedMaps>;
@@ -853,6 +860,92 @@ int wb200_mxfp4_gemm_skinny_noalloc(int M, int N, int K, const void* a, const vo
   if (c_dtype == WB200_F32)
     return dispatch_skinny<float>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, scratch, accumulate, s);
   return dispatch_skinny<__nv_bfloat16>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, scratch, accumulate, s);
+}
+
+int wb200_mxfp4_gemm_scatter_rows(int num_parts, const int* row_offsets, int N, int K, const void* a,
+                                  const void* a_scale_packed, const void* b, const void* b_scale_packed, void* const* c_ptrs,
+                                  int c_dtype, long long ldc, unsigned flags, void* stream) {
+  if (flags & ~WB200_SCATTER_TMA_STORE) return fail(WB200_ERR_INVALID_ARG, "gemm_scatter_rows: unknown flag bits %#x", flags);
+  const int store_mode = (flags & WB200_SCATTER_TMA_STORE) ? 1 : 2;
+  if (num_parts <= 0 || num_parts > wb::kMaxGroups || !row_offsets || !c_ptrs)
+    return fail(WB200_ERR_INVALID_ARG, "gemm_scatter_rows: 1..%d parts with row offsets and output pointers (got %d)",
+                wb::kMaxGroups, num_parts);
+  if (K <= 0 || K % 32 != 0) return fail(WB200_ERR_INVALID_ARG, "K = %d is not a positive multiple of 32", K);
+  if (c_dtype != WB200_F32 && c_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "unknown output dtype %d", c_dtype);
+  const int esz = (c_dtype == WB200_F32) ? 4 : 2;
+  if (ldc < N || (ldc * esz) % 16 != 0) return fail(WB200_ERR_ALIGNMENT, "gemm_scatter_rows: ldc = %lld must be >= N and a multiple of 16 bytes", ldc);
+  int block_offsets[wb::kMaxGroups + 1];
+  const void* b_ptrs[wb::kMaxGroups];
+  const void* b_sf_ptrs[wb::kMaxGroups];
+  for (int g = 0; g <= num_parts; ++g) {
+    if (g < num_parts && (row_offsets[g + 1] < row_offsets[g] || (row_offsets[g + 1] > row_offsets[g] && row_offsets[g] % 128 != 0)))
+      return fail(WB200_ERR_INVALID_ARG, "gemm_scatter_rows: part %d must start at a multiple of 128 rows and not end before it starts", g);
+    block_offsets[g] = (row_offsets[g] + 127) / 128;
+    if (g < num_parts) { b_ptrs[g] = b; b_sf_ptrs[g] = b_scale_packed; }
+  }
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  if (c_dtype == WB200_F32)
+    return launch_grouped<float>(*dev, num_parts, row_offsets, block_offsets, N, K, a, a_scale_packed, b_ptrs, b_sf_ptrs, nullptr,
+                                 ldc, static_cast<cudaStream_t>(stream), c_ptrs, store_mode);
+  return launch_grouped<__nv_bfloat16>(*dev, num_parts, row_offsets, block_offsets, N, K, a, a_scale_packed, b_ptrs, b_sf_ptrs,
+                                       nullptr, ldc, static_cast<cudaStream_t>(stream), c_ptrs, store_mode);
+}
+
+int wb200_peer_buffer_create(size_t bytes, void** ptr, void* handle64) {
+  if (!ptr || !handle64 || bytes == 0) return fail(WB200_ERR_INVALID_ARG, "peer_buffer_create: null pointer or empty buffer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is exchanged as 64 bytes");
+  void* p = nullptr;
+  WB_CUDA(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    WB_CUDA(e);
+  }
+  *ptr = p;
+  return WB200_OK;
+}
+
+int wb200_peer_buffer_open(const void* handle64, void** ptr) {
+  if (!ptr || !handle64) return fail(WB200_ERR_INVALID_ARG, "peer_buffer_open: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  WB_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return WB200_OK;
+}
+
+int wb200_peer_buffer_close(void* ptr) {
+  if (ptr) WB_CUDA(cudaIpcCloseMemHandle(ptr));
+  return WB200_OK;
+}
+
+int wb200_peer_buffer_destroy(void* ptr) {
+  if (ptr) WB_CUDA(cudaFree(ptr));
+  return WB200_OK;
+}
+
+int wb200_sum_slots(const float* slots, int num_slots, long long slot_stride, long long count, void* out, int out_dtype,
+                    void* stream) {
+  if (!slots || !out || num_slots <= 0 || count <= 0 || slot_stride < count)
+    return fail(WB200_ERR_INVALID_ARG, "sum_slots: num_slots = %d, count = %lld, slot_stride = %lld", num_slots, count, slot_stride);
+  if (out_dtype != WB200_F32 && out_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "sum_slots: unknown output dtype %d", out_dtype);
+  if ((reinterpret_cast<uintptr_t>(slots) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || slot_stride % 4 != 0)
+    return fail(WB200_ERR_ALIGNMENT, "sum_slots: buffers must be 16-byte aligned and the slot stride a multiple of 4 elements");
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  const long long vecs = (count + 3) / 4;
+  const unsigned blocks = unsigned((vecs + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == WB200_F32)
+    wb::sum_slots_kernel<float><<<blocks, 256, 0, s>>>(slots, num_slots, slot_stride, count, static_cast<float*>(out));
+  else
+    wb::sum_slots_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(slots, num_slots, slot_stride, count,
+                                                               static_cast<__nv_bfloat16*>(out));
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
 }
 
 int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* row_block_offsets, int N, int K,

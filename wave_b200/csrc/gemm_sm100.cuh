@@ -91,7 +91,8 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int group_n;        // N tiles per raster group
   int vec_ok;         // C base and row pitch allow 16-byte stores
-  int tma_store;      // write C with TMA stores from swizzled shared memory (needs vec_ok, no accumulate)
+  int tma_store;      // 1: write C with TMA stores from swizzled shared memory (needs vec_ok, no accumulate);
+                      // 2: same staging, then plain 16-byte stores covering whole 128-byte lines (needs vec_ok)
   int accumulate;     // add to the values already in C instead of overwriting them
   int elem_format;    // 8-bit operands only: 0 = E4M3, 1 = E5M2
   int* status;
@@ -110,9 +111,15 @@ constexpr int kMaxGroups = 32;
 struct GroupedMaps {
   static constexpr bool kGrouped = true;
   CUtensorMap m[kMaxGroups * 5];
+  void* c_base[kMaxGroups];  // first output row of each group, for the stores that do not go through its tensor map
   int tile_start[kMaxGroups + 1];
   int rows[kMaxGroups];
   int num_groups;
+  // interleave != 0: walk the groups round-robin (tile t = tile t / G of group t % G) over tiles_max tiles
+  // per group, skipping the ids a shorter group does not have, instead of group after group. Used when the
+  // groups differ in WHERE their output goes (another GPU): the remote stores then spread over the whole launch.
+  int interleave;
+  int tiles_max;
 };
 
 // Tile order: groups of `group_n` N tiles, each group swept down M with N fastest.
@@ -127,20 +134,29 @@ __device__ __forceinline__ void raster_tile(int t, int tiles_m, int tiles_n, int
   nt = n0 + (r - mt * gw);
 }
 
-// Tile id -> (group, M tile, N tile, rows of the group) and the group's first tensor map.
+// Tile id -> (group, M tile, N tile, rows of the group) and the group's first tensor map; nullptr for an
+// id that names no tile (interleaved walk over groups of unequal size).
 template <typename Maps>
 __device__ __forceinline__ const CUtensorMap* decode_tile(const Maps& maps, const GemmParams& p, int t, int& mt, int& nt,
-                                                          int& rows) {
+                                                          int& rows, void** c_base = nullptr) {
   if constexpr (!Maps::kGrouped) {
     raster_tile(t, p.tiles_m, p.tiles_n, p.group_n, mt, nt);
     rows = p.M;
+    if (c_base) *c_base = p.c;
     return &maps.m[0];
   } else {
-    int g = 0;
-    while (g + 1 < maps.num_groups && t >= maps.tile_start[g + 1]) ++g;
-    const int first = maps.tile_start[g];
-    raster_tile(t - first, (maps.tile_start[g + 1] - first) / p.tiles_n, p.tiles_n, p.group_n, mt, nt);
+    int g = 0, local;
+    if (maps.interleave) {
+      g = t % maps.num_groups;
+      local = t / maps.num_groups;
+      if (local >= maps.tile_start[g + 1] - maps.tile_start[g]) return nullptr;
+    } else {
+      while (g + 1 < maps.num_groups && t >= maps.tile_start[g + 1]) ++g;
+      local = t - maps.tile_start[g];
+    }
+    raster_tile(local, (maps.tile_start[g + 1] - maps.tile_start[g]) / p.tiles_n, p.tiles_n, p.group_n, mt, nt);
     rows = maps.rows[g];
+    if (c_base) *c_base = maps.c_base[g];
     return &maps.m[g * 5];
   }
 }
@@ -204,6 +220,13 @@ __device__ __forceinline__ void store_chunk32(OutT* __restrict__ p, const uint32
         if (j < ncols) p[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
     }
   }
+}
+
+// One 16-byte load from shared memory.
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
 }
 
 // One 16-byte store to shared memory.
@@ -290,7 +313,8 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
   const uint32_t tmem_base = *tmem_slot;
 
   int num_tiles = p.tiles_m * p.tiles_n;
-  if constexpr (Maps::kGrouped) num_tiles = maps.tile_start[maps.num_groups];
+  if constexpr (Maps::kGrouped)
+    num_tiles = maps.interleave ? maps.num_groups * maps.tiles_max : maps.tile_start[maps.num_groups];
   const int first_tile = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_step = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
   const int num_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
@@ -302,6 +326,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     for (int t = first_tile; t < num_tiles; t += tile_step) {
       int mt, nt, rows;
       const CUtensorMap* tm = decode_tile(maps, p, t, mt, nt, rows);
+      if (Maps::kGrouped && tm == nullptr) continue;
       const int a_row = (mt * CG + int(rank)) * Cfg::BM;
       const int b_row = nt * BN + int(rank) * Cfg::B_ROWS;
       const int sfa_rb = mt * CG + int(rank);
@@ -336,15 +361,15 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
       const uint32_t peer_acc_full0 = (CG == 2) ? mapa_shared(acc_full_bar(0), 1) : 0u;
       uint32_t stage = 0, phase = 0, sf_set = 0;
       int it = 0;
-      for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
-        const int as = it & 1;
+      for (int t = first_tile; t < num_tiles; t += tile_step) {
         // first 32-row group of this tile inside its first 128-row scale block = first scale column (0 or 2)
         uint32_t sfb_group = 0;
-        if constexpr (BN % 128 != 0) {
+        if constexpr (BN % 128 != 0 || Maps::kGrouped) {
           int mt, nt, rows;
-          decode_tile(maps, p, t, mt, nt, rows);
+          if (decode_tile(maps, p, t, mt, nt, rows) == nullptr) continue;
           sfb_group = uint32_t((nt * BN) % 128) / 32u;
         }
+        const int as = it & 1;
         // accumulator availability
         if constexpr (Cfg::OVERLAP) {
           // Needs the previous tile's epilogue to have drained the 48 shared columns
@@ -411,12 +436,12 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
           __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
+        ++it;
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps 2..5
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
-    OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
     const uint32_t acc_empty_leader0 = (CG == 2) ? mapa_shared(acc_empty_bar(0), 0) : 0u;
     const uint32_t acc_empty_leader1 = (CG == 2) ? mapa_shared(acc_empty_bar(1), 0) : 0u;
     const uint32_t stg = staging_base + uint32_t(warp - 2) * 2 * Cfg::STORE_BUF_BYTES;
@@ -424,9 +449,11 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     const uint64_t store_policy = l2_policy_evict_first();
     int it = 0;
     uint32_t store_count = 0;
-    for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
+    for (int t = first_tile; t < num_tiles; t += tile_step) {
       int mt, nt, rows;
-      const CUtensorMap* tm = decode_tile(maps, p, t, mt, nt, rows);
+      void* c_group = nullptr;
+      const CUtensorMap* tm = decode_tile(maps, p, t, mt, nt, rows, &c_group);
+      if (Maps::kGrouped && tm == nullptr) continue;
       const int as = it & 1;
       mbar_wait(acc_full_bar(as), uint32_t(it >> 1) & 1u, ctx, WB_DEV_TIMEOUT_EPILOGUE);
       tc_fence_after_sync();
@@ -468,11 +495,36 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
           const int half = ci % PER_STORE;
           const uint32_t buf = stg + (store_count & 1u) * Cfg::STORE_BUF_BYTES;
           if (half == 0) {
-            if (lane == 0) bulk_wait_group_read<1>();
+            if (p.tma_store == 1 && lane == 0) bulk_wait_group_read<1>();
             __syncwarp();
           }
           stage_chunk32<OutT>(buf, lane, half, r);
-          if (half == PER_STORE - 1) {
+          if (Maps::kGrouped && half == PER_STORE - 1 && p.tma_store == 2) {  // compiled for the grouped kernels only
+            // Plain stores from the staged rows: each instruction writes four whole 128-byte lines (8 lanes
+            // per line). Used where C is another GPU's memory, which is written with ordinary stores.
+            __syncwarp();
+            constexpr int EPV = 16 / int(sizeof(OutT));  // elements per 16-byte piece
+            const int scol = col - (PER_STORE - 1) * 32;
+            OutT* cb = reinterpret_cast<OutT*>(c_group);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3), j = lane & 7;
+              const int grow = row0 + rr, gcol = scol + j * EPV;
+              if (grow < rows && gcol < p.N) {
+                const uint4 v = ld_shared_v4(buf + rr * 128 + ((j ^ (rr & 7)) << 4));
+                OutT* dst = cb + size_t(grow) * p.ldc + gcol;
+                if (gcol + EPV <= p.N) {
+                  *reinterpret_cast<uint4*>(dst) = v;
+                } else {
+                  const OutT* e = reinterpret_cast<const OutT*>(&v);
+                  for (int k = 0; k < EPV; ++k)
+                    if (gcol + k < p.N) dst[k] = e[k];
+                }
+              }
+            }
+            __syncwarp();  // the rows are read before the buffer is staged again
+            ++store_count;
+          } else if (half == PER_STORE - 1) {
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -486,13 +538,14 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
             ++store_count;  // the buffers alternate store by store, across tiles too
           }
         } else if (row < rows && col < p.N) {
-          OutT* dst = C + size_t(row) * p.ldc + col;
+          OutT* dst = reinterpret_cast<OutT*>(c_group) + size_t(row) * p.ldc + col;
           const int ncols = min(32, p.N - col);
           if (p.accumulate) add_old_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);
           store_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);
         }
       }
       if constexpr (!Cfg::OVERLAP) release();
+      ++it;
     }
     if (lane == 0) bulk_wait_group<0>();  // all of this warp's stores have left shared memory and landed
   }

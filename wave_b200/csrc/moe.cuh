@@ -219,4 +219,31 @@ moe_combine_kernel(const T* __restrict__ y, long long ldy, const int* __restrict
     if (c0 + i < cols) out[(long long)t * ldo + c0 + i] = from_f32<T>(acc[i]);
 }
 
+// out[i] = slots[0][i] + slots[1][i] + ... in slot order (f32), rounded once to the output type: the
+// reduction step of the K-sharded GEMM, whose ranks deposit f32 partial tiles in one slot each.
+template <typename T>
+__global__ void __launch_bounds__(256)
+sum_slots_kernel(const float* __restrict__ slots, int num_slots, long long slot_stride, long long count, T* __restrict__ out) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= count) return;
+  if (i + 4 <= count) {
+    float4 acc = *reinterpret_cast<const float4*>(slots + i);
+    for (int s = 1; s < num_slots; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(slots + s * slot_stride + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if constexpr (sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(out + i) = acc;
+    } else {
+      *reinterpret_cast<uint2*>(out + i) = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    }
+  } else {
+    for (long long j = i; j < count; ++j) {
+      float acc = slots[j];
+      for (int s = 1; s < num_slots; ++s) acc += slots[s * slot_stride + j];
+      out[j] = from_f32<T>(acc);
+    }
+  }
+}
+
 }  // namespace wb

@@ -1,4 +1,4 @@
-"""N-sharded scaled GEMM over the GPUs of one node, one process per GPU.
+"""N-sharded (and K-sharded) scaled GEMM over the GPUs of one node, one process per GPU.
 
 The reference distributes a GEMM by tiling M and/or N over IREE devices inside one process: its
 `DeviceConstraint` (wave_lang/kernel/wave/constraints.py:1105-1180) makes the host wrapper slice
@@ -112,4 +112,163 @@ class ShardedScaledGemm:
             for r, (n0, n1) in enumerate(self.bounds):
                 if n1 > n0:
                     full[:, n0:n1].copy_(stacked[r][:, : n1 - n0])
+        return full
+
+
+class KShardedScaledGemm:
+    """K-sharded MXFP4 GEMM: rank r holds the K columns [k0_r, k1_r) of a and b (multiples of 256 elements),
+    C = sum over ranks of a_r · b_r^T, and rank r ends up with the rows [m0_r, m1_r) of C (multiples of 128).
+
+    The reference distributes a GEMM by M / N tiles only (wave_lang/kernel/wave/templates/dist_gemm.py:49-50);
+    this is the second sharding axis, the one a row-parallel linear layer needs. Compute and exchange are one
+    step: every rank runs ONE persistent GEMM launch (`wb200_mxfp4_gemm_scatter_rows`) whose tiles are stored,
+    as they finish, straight into the receive buffer of the rank that owns those rows — the peers' buffers are
+    mapped for this rank's device with CUDA IPC, so the f32 partial products cross NVLink while the remaining tiles
+    are still being computed. A stream-ordered barrier follows, then each rank adds the `world` slots of its
+    receive buffer in rank order (`wb200_sum_slots`, deterministic) and rounds once to the output type.
+    Two receive buffers alternate between calls, so a rank may start scattering call i+1 while a peer still
+    sums call i.
+
+        op = KShardedScaledGemm(M, N, K, wave_b200.bf16)
+        op.load_weight_shard(b[:, k0/2:k1/2], b_scale[:, k0/32:k1/32])     # this rank's K columns of b
+        c_rows = op(a[:, k0/2:k1/2], a_scale[:, k0/32:k1/32])              # [m1 - m0, N]
+        c_full = op(..., gather=True)                                      # [M, N] on every rank (one all-gather)
+    """
+
+    def __init__(self, M: int, N: int, K: int, output_dtype, group: Optional[dist.ProcessGroup] = None):
+        self.M, self.N, self.K = M, N, K
+        self.group = group
+        self.world_size = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.out = as_output_dtype(output_dtype)
+        self.k0, self.k1 = shard_bounds(K, self.world_size, self.rank, granule=256)
+        self.row_bounds = [shard_bounds(M, self.world_size, r, granule=128) for r in range(self.world_size)]
+        self.m0, self.m1 = self.row_bounds[self.rank]
+        self.rows_max = max(m1 - m0 for m0, m1 in self.row_bounds)
+        self._b = self._b_sf = None
+        self._calls = 0
+        self._peers = None
+        self.scatter_flags = 0  # 1: TMA stores instead of ordinary stores to the peers' buffers
+
+    @property
+    def local_k(self) -> int:
+        return self.k1 - self.k0
+
+    def load_weight_shard(self, b_cols: torch.Tensor, b_scale_cols: torch.Tensor) -> None:
+        """Keep this rank's K columns of b ([N, local_k/2]) and of its scales ([N, local_k/32], packed once)."""
+        if tuple(b_cols.shape) != (self.N, self.local_k // 2) or \
+                tuple(b_scale_cols.shape) != (self.N, self.local_k // ops.SCALE_GROUP_SIZE):
+            raise ValueError(f"rank {self.rank} owns K columns [{self.k0}, {self.k1}): expected b {(self.N, self.local_k // 2)} "
+                             f"and scales {(self.N, self.local_k // ops.SCALE_GROUP_SIZE)}, got {tuple(b_cols.shape)} and "
+                             f"{tuple(b_scale_cols.shape)}")
+        self._b = b_cols.contiguous()
+        self._b_sf = self._pack_scales(b_scale_cols.contiguous()) if self.local_k else None
+        if self._peers is None:
+            self._peers = self._exchange_buffers(self._b.device)
+
+    # ---- the hooks below are the only places that touch CUDA; CPU ranks replace them in tests ----------
+    def _pack_scales(self, scale: torch.Tensor):
+        return ops.repack_scales(scale)
+
+    def _exchange_buffers(self, device):
+        """Allocate this rank's receive buffers [2, world, rows_max, N] f32 and map every peer's for THIS device.
+        Returns the base address of every rank's buffer as seen from this process."""
+        import ctypes
+        from . import _lib
+        lib = _lib.load()
+        self._slot_elems = self.rows_max * self.N
+        nbytes = 2 * self.world_size * self._slot_elems * 4
+        handle = ctypes.create_string_buffer(64)
+        base = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(lib.wb200_peer_buffer_create(nbytes, ctypes.byref(base), handle))
+        self._recv_ptr = base.value
+        self._opened = []
+        if self.world_size == 1:
+            return [self._recv_ptr]
+        gathered = [None] * self.world_size
+        dist.all_gather_object(gathered, handle.raw, group=self.group)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        peers = []
+        with torch.cuda.device(device):
+            for r in range(self.world_size):
+                if r == self.rank:
+                    peers.append(self._recv_ptr)
+                    continue
+                p = ctypes.c_void_p()
+                _lib.check(lib.wb200_peer_buffer_open(ctypes.create_string_buffer(gathered[r], 64), ctypes.byref(p)))
+                self._opened.append(p.value)
+                peers.append(p.value)
+        return peers
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's. Call on every rank, after a barrier."""
+        from . import _lib
+        lib = _lib.load()
+        for p in getattr(self, "_opened", []):
+            lib.wb200_peer_buffer_close(p)
+        self._opened = []
+        if getattr(self, "_recv_ptr", None):
+            lib.wb200_peer_buffer_destroy(self._recv_ptr)
+            self._recv_ptr = None
+
+    def _slot_ptr(self, owner: int, parity: int, source: int) -> int:
+        return self._peers[owner] + ((parity * self.world_size + source) * self._slot_elems) * 4
+
+    def _scatter_gemm(self, a: torch.Tensor, a_scale: torch.Tensor, parity: int) -> None:
+        """Partial products of this rank's K columns, rows of rank d written to slot [parity, self.rank] of d's buffer."""
+        import ctypes
+        from . import _lib
+        lib = _lib.load()
+        a_sf = ops.repack_scales(a_scale)
+        W = self.world_size
+        offsets = (ctypes.c_int * (W + 1))(*([m0 for m0, _ in self.row_bounds] + [self.row_bounds[-1][1]]))
+        ptrs = (ctypes.c_void_p * W)(*[self._slot_ptr(d, parity, self.rank) for d in range(W)])
+        with torch.cuda.device(a.device):
+            _lib.check(lib.wb200_mxfp4_gemm_scatter_rows(W, offsets, self.N, self.local_k, a.data_ptr(), a_sf.data.data_ptr(),
+                                                         self._b.data_ptr(), self._b_sf.data.data_ptr(), ptrs, ops._DTYPE_CODE[torch.float32],
+                                                         self.N, self.scatter_flags, torch.cuda.current_stream().cuda_stream))
+        self._keep = (a, a_sf)  # alive until the next call: the launch is asynchronous
+
+    def _barrier(self) -> None:
+        """Stream-ordered: returns (on the stream) once every rank's scatter has finished."""
+        if self.world_size > 1:
+            dist.all_reduce(self._flag, group=self.group)
+
+    def _reduce(self, parity: int, out: torch.Tensor) -> None:
+        from . import _lib
+        lib = _lib.load()
+        rows = self.m1 - self.m0
+        if rows == 0:
+            return
+        with torch.cuda.device(out.device):
+            _lib.check(lib.wb200_sum_slots(self._slot_ptr(self.rank, parity, 0), self.world_size, self._slot_elems, rows * self.N,
+                                           out.data_ptr(), ops._DTYPE_CODE[out.dtype], torch.cuda.current_stream().cuda_stream))
+
+    # -----------------------------------------------------------------------------------------------------
+    def __call__(self, a_cols: torch.Tensor, a_scale_cols: torch.Tensor, gather: bool = False) -> torch.Tensor:
+        if self._b is None:
+            raise RuntimeError("load_weight_shard() must be called before the first GEMM")
+        if tuple(a_cols.shape) != (self.M, self.local_k // 2) or \
+                tuple(a_scale_cols.shape) != (self.M, self.local_k // ops.SCALE_GROUP_SIZE):
+            raise ValueError(f"rank {self.rank} takes a {(self.M, self.local_k // 2)} and scales "
+                             f"{(self.M, self.local_k // ops.SCALE_GROUP_SIZE)}, got {tuple(a_cols.shape)} and {tuple(a_scale_cols.shape)}")
+        parity = self._calls & 1
+        self._calls += 1
+        if self.local_k:
+            self._scatter_gemm(a_cols.contiguous(), a_scale_cols.contiguous(), parity)
+        self._barrier()
+        rows = self.m1 - self.m0
+        if not gather:
+            c = torch.empty(rows, self.N, dtype=self.out.torch_dtype, device=a_cols.device)
+            self._reduce(parity, c)
+            return c
+        stacked = torch.zeros(self.world_size, self.rows_max, self.N, dtype=self.out.torch_dtype, device=a_cols.device)
+        self._reduce(parity, stacked[self.rank][:rows])
+        if self.world_size > 1:
+            dist.all_gather_into_tensor(stacked.view(-1), stacked[self.rank].reshape(-1).clone(), group=self.group)
+        full = torch.empty(self.M, self.N, dtype=self.out.torch_dtype, device=a_cols.device)
+        for r, (m0, m1) in enumerate(self.row_bounds):
+            if m1 > m0:
+                full[m0:m1].copy_(stacked[r][: m1 - m0])
         return full

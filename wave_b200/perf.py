@@ -136,15 +136,86 @@ def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, devi
     return rows
 
 
+def time_k_sharded(M=8192, N=8192, k_per_rank=8192, iters=20):
+    """Under torchrun (one rank per GPU): the K-sharded GEMM whose tiles are scattered to the owning ranks'
+    buffers by the GEMM kernel itself, against the unfused sequence on the same operands (GEMM into a local
+    f32 matrix, NCCL reduce-scatter, cast). Prints device microseconds per call, max over ranks."""
+    import os
+    import torch.distributed as dist
+    from . import ops
+    from .multi_gpu import KShardedScaledGemm
+    from .lang import bf16
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    K = k_per_rank * world
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    a = torch.randint(0, 256, (M, k_per_rank // 2), dtype=torch.uint8, device=dev, generator=g)
+    b = torch.randint(0, 256, (N, k_per_rank // 2), dtype=torch.uint8, device=dev, generator=g)
+    a_s = torch.randint(124, 128, (M, k_per_rank // 32), dtype=torch.uint8, device=dev, generator=g)
+    b_s = torch.randint(124, 128, (N, k_per_rank // 32), dtype=torch.uint8, device=dev, generator=g)
+    op = KShardedScaledGemm(M, N, K, bf16)
+    op.load_weight_shard(b, b_s)
+    a_sf, b_sf = ops.repack_scales(a_s), ops.repack_scales(b_s)
+    partial = torch.empty(M, N, dtype=torch.float32, device=dev)
+    rows = torch.empty(M // world, N, dtype=torch.float32, device=dev)
+
+    def unfused():
+        ops.scaled_gemm_packed(a, a_sf, b, b_sf, partial)
+        dist.reduce_scatter_tensor(rows, partial)
+        return rows.to(torch.bfloat16)
+
+    def fused():
+        return op(a, a_s)
+
+    ref, got = unfused().float(), fused().float()
+    torch.cuda.synchronize()
+    err = float((ref - got).abs().max() / ref.abs().max())
+    out = {}
+    def fused_tma():
+        op.scatter_flags = 1
+        r = op(a, a_s)
+        op.scatter_flags = 0
+        return r
+
+    for name, fn in (("fused scatter + sum", fused), ("fused, TMA stores", fused_tma), ("gemm + nccl reduce_scatter + cast", unfused), ("gemm alone", lambda: ops.scaled_gemm_packed(a, a_sf, b, b_sf, partial))):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name] = round(float(t[0]), 1)
+    if rank == 0:
+        flops = 2.0 * M * N * K
+        print({"world": world, "M": M, "N": N, "K": K, "us": out, "tflops_fused": round(flops / out["fused scatter + sum"] / 1e6, 1),
+               "nvlink_bytes_per_rank": (world - 1) * (M // world) * N * 4, "max_rel_diff_fused_vs_unfused": err}, flush=True)
+    ops.check_device_status()
+    dist.barrier()
+    op.close()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--validate", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--k-sharded", action="store_true", help="under torchrun: time the K-sharded GEMM against GEMM + NCCL reduce-scatter")
     ap.add_argument("--moe", action="store_true", help="time the steps of the MXFP4 expert MLP instead of the shape sweep")
     args = ap.parse_args(argv)
     if args.moe:
         time_moe(iters=args.iters)
+        return
+    if args.k_sharded:
+        time_k_sharded(iters=args.iters)
         return
     rows = []
     for M, N, K in default_shapes():
