@@ -106,6 +106,17 @@ int wb200_repack_scales_grouped(const void* src, long long src_row_stride, int n
 int wb200_quantize_mxfp4(const void* x, int x_dtype, long long ldx, int rows, int K, void* q, void* scale_rowmajor,
                          void* scale_packed, void* stream);
 
+/* Grouped GEMM driven by DEVICE routing arrays, for rows laid out by wb200_moe_align_block_size with
+ * block_size = 256: a [max_rows, K/2] holds the routed rows of all experts, every expert padded to whole
+ * 256-row blocks; expert_ids[i] (device) is the expert of block i; *num_rows (device) the padded total, row
+ * blocks at or past it are skipped. a_scale_packed: the scales of all max_rows rows packed by wb200_repack_scales
+ * (every expert starts on a block boundary, so one packing serves). c [max_rows, N]. Nothing about the routing
+ * is read on the host: no synchronisation, and the call can be captured in a CUDA graph. max_rows: a multiple of
+ * 256 (the buffers' capacity). Up to 32 experts. */
+int wb200_mxfp4_moe_gemm(int num_experts, int max_rows, const int* expert_ids, const int* num_rows, int N, int K, const void* a,
+                         const void* a_scale_packed, const void* const* b_ptrs, const void* const* b_scale_ptrs, void* c,
+                         int c_dtype, long long ldc, void* stream);
+
 /* ---- mixture-of-experts steps either side of wb200_mxfp4_grouped_gemm ------------------------- */
 
 /* Sort routed (token, slot) pairs by expert and pad every expert to whole blocks: the outputs of the

@@ -167,3 +167,73 @@ def test_expert_mlp_against_oracle(T, E, K, inter):
     rel = (out.cpu().float() - ref).abs().mean() / ref.pow(2).mean().sqrt()
     assert float(rel) < 2e-2
     ops.check_device_status()
+
+
+def test_device_driven_grouped_gemm_matches_host_offsets_form():
+    """wb200_mxfp4_moe_gemm (routing read from the alignment kernel's device outputs) against
+    wb200_mxfp4_grouped_gemm (row offsets given by the host) on the same routed rows: identical bits."""
+    from wave_b200.grouped import ExpertWeights, grouped_scaled_gemm, moe_scaled_gemm
+    T, E, K, N, k = 700, 5, 512, 384, 2
+    g = torch.Generator().manual_seed(21)
+    _, ids = torch.topk(torch.rand(T, E, generator=g), k=k, dim=1)
+    ids[:, :] = torch.where(ids == 3, torch.zeros_like(ids), ids)  # expert 3 gets no rows
+    n = T * k
+    cap = (n + E * 255 + 255) // 256 * 256
+    sorted_ids, expert_ids, post, _ = run_align(ids, E, 256)
+    sorted_ids = np.concatenate([sorted_ids, np.full(cap - sorted_ids.size, n, dtype=np.int32)])
+    xq = torch.randint(0, 256, (T, K // 2), dtype=torch.uint8, generator=g)
+    xs = torch.randint(122, 129, (T, K // 32), dtype=torch.uint8, generator=g)
+    w = [torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g) for _ in range(E)]
+    ws = [torch.randint(122, 129, (N, K // 32), dtype=torch.uint8, generator=g) for _ in range(E)]
+    experts = ExpertWeights([t.to(DEV) for t in w], [t.to(DEV) for t in ws])
+    a = torch.empty(cap, K // 2, dtype=torch.uint8, device=DEV)
+    a_s = torch.empty(cap, K // 32, dtype=torch.uint8, device=DEV)
+    sid = torch.from_numpy(sorted_ids).to(DEV)
+    moe.gather_rows(xq.to(DEV), sid, n, k, a)
+    moe.gather_rows(xs.to(DEV), sid, n, k, a_s)
+    c_dev = torch.full((cap, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    eid = torch.full((cap // 256,), -1, dtype=torch.int32, device=DEV)
+    eid[: expert_ids.size] = torch.from_numpy(expert_ids).to(DEV)[: cap // 256]
+    moe_scaled_gemm(a, a_s, experts, eid, torch.tensor([post], dtype=torch.int32, device=DEV), c_dev)
+    counts = torch.bincount(ids.reshape(-1), minlength=E).tolist()
+    offsets = [0]
+    for cnt in counts:
+        offsets.append(offsets[-1] + (cnt + 255) // 256 * 256)
+    assert offsets[-1] == post
+    c_host = torch.empty(post, N, dtype=torch.bfloat16, device=DEV)
+    grouped_scaled_gemm(a[:post], a_s[:post], experts, offsets, c_host)
+    assert torch.equal(c_dev[:post].view(torch.int16), c_host.view(torch.int16))
+    assert bool(c_dev[post:].isnan().all())  # row blocks past the padded total are not touched
+    # and against the oracle for one expert's rows
+    e = 1
+    rows = slice(offsets[e], offsets[e] + counts[e])
+    ref = orc.scaled_gemm(a[rows].cpu(), a_s[rows].cpu(), w[e], ws[e])
+    assert int(orc.bf16_ulp_distance(c_dev[rows], ref).max()) <= 1
+    ops.check_device_status()
+
+
+def test_expert_mlp_forward_can_be_captured_in_a_cuda_graph():
+    """No step of the forward pass reads the routing back to the host."""
+    T, E, K, inter = 64, 4, 512, 256
+    g = torch.Generator().manual_seed(2)
+    w1, w1s, w2, w2s = [], [], [], []
+    for e in range(E):
+        q, s = orc.quantize_mxfp4(torch.randn(2 * inter, K, generator=g) * 0.05)
+        w1.append(q.to(DEV)); w1s.append(s.to(DEV))
+        q, s = orc.quantize_mxfp4(torch.randn(K, inter, generator=g) * 0.05)
+        w2.append(q.to(DEV)); w2s.append(s.to(DEV))
+    mlp = wb.MXFP4ExpertMLP(w1, w1s, w2, w2s, top_k=2)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    logits = torch.randn(T, E, generator=g).to(DEV)
+    eager = mlp(x, logits)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = mlp(x, logits)
+    x.copy_(torch.randn(T, K, generator=g).to(torch.bfloat16))  # new tokens, same buffers
+    graph.replay()
+    torch.cuda.synchronize()
+    again = mlp(x, logits)
+    torch.cuda.synchronize()
+    assert torch.equal(captured, again) and not torch.equal(captured, eager)
+    ops.check_device_status()

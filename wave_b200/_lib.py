@@ -52,6 +52,7 @@ EXPORTED_SYMBOLS = (
     "wb200_mxfp8_gemm",
     "wb200_mxfp4_gemm_skinny_noalloc",
     "wb200_mxfp4_grouped_gemm",
+    "wb200_mxfp4_moe_gemm",
     "wb200_moe_align_block_size",
     "wb200_moe_gather_rows",
     "wb200_silu_and_mul",
@@ -134,6 +135,9 @@ def load() -> ctypes.CDLL:
     lib.wb200_mxfp4_grouped_gemm.argtypes = [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, c_int,
                                              c_void_p, c_void_p, ctypes.POINTER(c_void_p),
                                              ctypes.POINTER(c_void_p), c_void_p, c_int, c_ll, c_void_p]
+    lib.wb200_mxfp4_moe_gemm.restype = c_int
+    lib.wb200_mxfp4_moe_gemm.argtypes = [c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                         ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_int, c_ll, c_void_p]
     lib.wb200_moe_align_block_size.restype = c_int
     lib.wb200_moe_align_block_size.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
                                                c_void_p, c_void_p, c_void_p]

@@ -195,6 +195,11 @@ int make_output_map(CUtensorMap* map, void* c, int M, int N, long long ldc, int 
 }
 
 // EB: bits per operand element (4: MXFP4, 8: MXFP8 with elem_format 0 = E4M3 / 1 = E5M2).
+// Set by wb200_mxfp4_gemm_repack_a around its GEMM launch: the GEMM is then launched as a programmatic
+// dependent of the repack kernel before it (its set-up and weight loads overlap that kernel; it waits for
+// the kernel's completion before reading the packed scales).
+static thread_local bool tl_dependent_launch = false;
+
 template <int CG, int BN, typename OutT, int EB = 4>
 int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                 const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, int accumulate,
@@ -243,13 +248,15 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = tl_dependent_launch ? 2 : 1;
   WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps, p));
   return WB200_OK;
 }
@@ -294,6 +301,7 @@ int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets
   const int tiles_n = (N + BN - 1) / BN;
   maps.num_groups = num_groups;
   maps.interleave = (c_ptrs != nullptr) ? 1 : 0;
+  maps.aligned = 0;
   maps.tiles_max = 0;
   maps.tile_start[0] = 0;
   for (int g = 0; g < num_groups; ++g) {
@@ -350,6 +358,71 @@ int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets
   return WB200_OK;
 }
 
+// Grouped GEMM over a block-aligned row layout described by DEVICE arrays (see GroupedMaps::aligned).
+template <typename OutT>
+int launch_aligned(const DeviceInfo& dev, int num_groups, int max_rows, const int* expert_ids, const int* num_rows, int N, int K,
+                   const void* a, const void* a_sf, const void* const* b_ptrs, const void* const* b_sf_ptrs, void* c,
+                   long long ldc, cudaStream_t stream) {
+  constexpr int CG = 2, BN = 256;
+  using Cfg = wb::GemmCfg<CG, BN, int(sizeof(OutT))>;
+  static wb::GroupedMaps maps;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  const int esz = int(sizeof(OutT));
+  const int k_atoms = wb::sf_k_atoms(K);
+  maps.num_groups = num_groups;
+  maps.interleave = 0;
+  maps.aligned = 1;
+  maps.tile_rows = Cfg::BM * CG;
+  maps.tiles_m_cap = max_rows / (Cfg::BM * CG);
+  maps.tiles_max = 0;
+  maps.expert_ids = expert_ids;
+  maps.num_rows = num_rows;
+  maps.c_base[0] = c;
+  for (int g = 0; g < num_groups; ++g) {
+    int rc = check_common(max_rows, N, K, a, a_sf, b_ptrs[g], b_sf_ptrs[g], c, esz == 4 ? WB200_F32 : WB200_BF16, ldc);
+    if (rc) return rc;
+    CUtensorMap* m = &maps.m[g * 5];
+    if ((rc = make_operand_map(m + 0, a, max_rows, K / 2, Cfg::BM))) return rc;
+    if ((rc = make_operand_map(m + 1, b_ptrs[g], N, K / 2, Cfg::B_ROWS))) return rc;
+    if ((rc = make_scale_map(m + 2, a_sf, wb::sf_row_blocks(max_rows), k_atoms, 1))) return rc;
+    if ((rc = make_scale_map(m + 3, b_sf_ptrs[g], wb::sf_row_blocks(N), k_atoms, BN / 128))) return rc;
+    if ((rc = make_output_map(m + 4, c, max_rows, N, ldc, esz))) return rc;
+  }
+  wb::GemmParams p = {};
+  p.c = c;
+  p.M = max_rows; p.N = N; p.K = K;
+  p.ldc = int(ldc);
+  p.tiles_m = maps.tiles_m_cap;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.group_n = 16;
+  p.vec_ok = 1;
+  p.tma_store = 1;
+  p.accumulate = 0;
+  p.status = dev.status_ptr;
+  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, OutT, wb::GroupedMaps>;
+  static bool smem_set[kMaxDevices] = {};
+  int rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
+  if (rc) return rc;
+  const long long tiles = (long long)maps.tiles_m_cap * p.tiles_n;
+  if (tiles == 0) return WB200_OK;
+  const int units = dev.sm_count / CG;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(int(tiles < units ? tiles : units) * CG, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps, p));
+  return WB200_OK;
+}
+
 // ------------------------------------------------------------------------------------------
 // skinny path
 // ------------------------------------------------------------------------------------------
@@ -388,7 +461,17 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   if (rc) return rc;
   const long long units = (long long)p.tiles_n * p.num_kb;
   const int grid = int(units < dev.sm_count ? units : dev.sm_count);
-  kernel<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, tmSFW, tmSFX, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tl_dependent_launch ? 1 : 0;
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmW, tmX, tmSFW, tmSFX, p));
   WB_CUDA(cudaGetLastError());
   return WB200_OK;
 }
@@ -787,8 +870,10 @@ int wb200_mxfp4_gemm_repack_a(int M, int N, int K, const void* a, const void* a_
   if (!a_scale_scratch) return fail(WB200_ERR_INVALID_ARG, "gemm_repack_a: null scratch for the packed activation scales");
   int rc = wb200_repack_scales(a_scale, a_scale_stride, M, K, a_scale_scratch, stream);
   if (rc) return rc;
-  return wb200_mxfp4_gemm(M, N, K, a, a_scale_scratch, b, b_scale_packed, c, c_dtype, ldc, workspace, workspace_bytes, flags,
-                          stream);
+  tl_dependent_launch = true;  // the GEMM is the repack kernel's programmatic dependent
+  rc = wb200_mxfp4_gemm(M, N, K, a, a_scale_scratch, b, b_scale_packed, c, c_dtype, ldc, workspace, workspace_bytes, flags, stream);
+  tl_dependent_launch = false;
+  return rc;
 }
 
 extern "C++" {
@@ -860,6 +945,28 @@ int wb200_mxfp4_gemm_skinny_noalloc(int M, int N, int K, const void* a, const vo
   if (c_dtype == WB200_F32)
     return dispatch_skinny<float>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, scratch, accumulate, s);
   return dispatch_skinny<__nv_bfloat16>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, scratch, accumulate, s);
+}
+
+int wb200_mxfp4_moe_gemm(int num_experts, int max_rows, const int* expert_ids, const int* num_rows, int N, int K, const void* a,
+                         const void* a_scale_packed, const void* const* b_ptrs, const void* const* b_scale_ptrs, void* c,
+                         int c_dtype, long long ldc, void* stream) {
+  if (num_experts <= 0 || num_experts > wb::kMaxGroups || !expert_ids || !num_rows || !b_ptrs || !b_scale_ptrs)
+    return fail(WB200_ERR_INVALID_ARG, "moe_gemm: 1..%d experts with device routing arrays and weight pointers (got %d)",
+                wb::kMaxGroups, num_experts);
+  if (max_rows <= 0 || max_rows % 256 != 0)
+    return fail(WB200_ERR_INVALID_ARG, "moe_gemm: max_rows = %d must be a positive multiple of 256 (the row-block size)", max_rows);
+  if (c_dtype != WB200_F32 && c_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "unknown output dtype %d", c_dtype);
+  const int esz = (c_dtype == WB200_F32) ? 4 : 2;
+  if (!c || (reinterpret_cast<uintptr_t>(c) & 15) || (ldc * esz) % 16 != 0 || ldc < N)
+    return fail(WB200_ERR_ALIGNMENT, "moe_gemm: c must be 16-byte aligned with a row pitch >= N that is a multiple of 16 bytes");
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  if (c_dtype == WB200_F32)
+    return launch_aligned<float>(*dev, num_experts, max_rows, expert_ids, num_rows, N, K, a, a_scale_packed, b_ptrs, b_scale_ptrs,
+                                 c, ldc, static_cast<cudaStream_t>(stream));
+  return launch_aligned<__nv_bfloat16>(*dev, num_experts, max_rows, expert_ids, num_rows, N, K, a, a_scale_packed, b_ptrs,
+                                       b_scale_ptrs, c, ldc, static_cast<cudaStream_t>(stream));
 }
 
 int wb200_mxfp4_gemm_scatter_rows(int num_parts, const int* row_offsets, int N, int K, const void* a,

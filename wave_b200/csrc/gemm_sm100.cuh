@@ -120,6 +120,16 @@ struct GroupedMaps {
   // groups differ in WHERE their output goes (another GPU): the remote stores then spread over the whole launch.
   int interleave;
   int tiles_max;
+  // aligned != 0: the rows of all groups sit in ONE matrix, every group padded to whole tile_rows-row tiles, and
+  // which group a row tile belongs to is read from device memory (expert_ids[M tile], as written by
+  // moe_align_block_size with block_size = tile_rows); row tiles at or past *num_rows are skipped. Slots 0, 2, 4
+  // of every group's maps describe that one matrix; slots 1, 3 are the group's own weights. The host needs
+  // no knowledge of the routing: no read-back, and the launch can be captured in a CUDA graph.
+  int aligned;
+  int tile_rows;
+  int tiles_m_cap;
+  const int* expert_ids;
+  const int* num_rows;
 };
 
 // Tile order: groups of `group_n` N tiles, each group swept down M with N fastest.
@@ -145,6 +155,16 @@ __device__ __forceinline__ const CUtensorMap* decode_tile(const Maps& maps, cons
     if (c_base) *c_base = p.c;
     return &maps.m[0];
   } else {
+    if (maps.aligned) {
+      raster_tile(t, maps.tiles_m_cap, p.tiles_n, p.group_n, mt, nt);
+      const int total = __ldg(maps.num_rows);
+      if (mt * maps.tile_rows >= total) return nullptr;
+      int e = __ldg(maps.expert_ids + mt);
+      if (e < 0 || e >= maps.num_groups) return nullptr;  // never written by a correct router; do not index out of the table
+      rows = total;
+      if (c_base) *c_base = maps.c_base[0];
+      return &maps.m[e * 5];
+    }
     int g = 0, local;
     if (maps.interleave) {
       g = t % maps.num_groups;
@@ -314,7 +334,8 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
 
   int num_tiles = p.tiles_m * p.tiles_n;
   if constexpr (Maps::kGrouped)
-    num_tiles = maps.interleave ? maps.num_groups * maps.tiles_max : maps.tile_start[maps.num_groups];
+    num_tiles = maps.aligned ? maps.tiles_m_cap * p.tiles_n
+                             : (maps.interleave ? maps.num_groups * maps.tiles_max : maps.tile_start[maps.num_groups]);
   const int first_tile = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_step = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
   const int num_kb = (p.K + Cfg::BK - 1) / Cfg::BK;
@@ -323,6 +344,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the loop; one elected lane issues the copies.
     uint32_t stage = 0, phase = 0;
+    pdl_wait();  // the packed activation scales may be written by the kernel launched just before this one
     for (int t = first_tile; t < num_tiles; t += tile_step) {
       int mt, nt, rows;
       const CUtensorMap* tm = decode_tile(maps, p, t, mt, nt, rows);
@@ -444,6 +466,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
     const uint32_t acc_empty_leader0 = (CG == 2) ? mapa_shared(acc_empty_bar(0), 0) : 0u;
     const uint32_t acc_empty_leader1 = (CG == 2) ? mapa_shared(acc_empty_bar(1), 0) : 0u;
+    pdl_wait();  // C may still be read by the kernels before this one
     const uint32_t stg = staging_base + uint32_t(warp - 2) * 2 * Cfg::STORE_BUF_BYTES;
     // C is written once and not read again by this kernel: keep it from pushing A and B out of L2
     const uint64_t store_policy = l2_policy_evict_first();

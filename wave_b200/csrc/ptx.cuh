@@ -304,6 +304,12 @@ __device__ __forceinline__ uint32_t idesc_with_sf_id(uint32_t idesc, uint32_t sf
   return idesc | (sf_id << 4) | (sf_id << 29);
 }
 
+// Programmatic dependent launch. launch_dependents: kernels launched behind this one with the
+// programmatic-serialisation attribute may start now; wait: returns once every kernel this one depends on has
+// finished and its writes are visible (a no-op in a kernel launched without the attribute).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Instruction descriptor of kind::mxf8f6f4 block-scaled with 8-bit operands: fmt 0 = E4M3, 1 = E5M2 (both
 // operands the same), K-major, UE8M0 scales, K = 32 per instruction; the scale-factor id (0..3) picks
 // the byte of the 32-bit scale column that this K = 32 step reads.

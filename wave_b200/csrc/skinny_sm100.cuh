@@ -133,7 +133,9 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   int p_seg = 0, p_tile = 0, p_kb = 0, p_kbe = 0, p_issued = 0;
   if (nseg > 0) segment(0, p_tile, p_kb, p_kbe);
   uint64_t stream_policy = 0, keep_policy = 0;
-  auto produce = [&](int max_units, bool wait_for_slot) {
+  // part 0: all four loads of a stage; part 1: only the weights and their scales (no arrival on the barrier
+  // yet); part 2: the arrival with the stage's byte count plus the activations and their scales.
+  auto produce = [&](int max_units, bool wait_for_slot, int part) {
     while (p_seg < nseg && p_issued < max_units) {
       if (wait_for_slot) mbar_wait(empty_bar(p_stage), p_phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
       const uint32_t sW = smem_base + p_stage * Cfg::STAGE_BYTES;
@@ -142,11 +144,15 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
       const uint32_t fb = full_bar(p_stage);
       if (elect_one()) {
-        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-        tma_load_2d_hint(sW, &tmW, p_kb * 128, p_tile * 128, fb, stream_policy);
-        tma_load_2d_hint(sX, &tmX, p_kb * 128, 0, fb, keep_policy);
-        tma_load_2d(sSFW, &tmSFW, p_kb * 256, p_tile, fb);
-        tma_load_2d(sSFX, &tmSFX, p_kb * 256, 0, fb);
+        if (part != 1) mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+        if (part != 2) {
+          tma_load_2d_hint(sW, &tmW, p_kb * 128, p_tile * 128, fb, stream_policy);
+          tma_load_2d(sSFW, &tmSFW, p_kb * 256, p_tile, fb);
+        }
+        if (part != 1) {
+          tma_load_2d_hint(sX, &tmX, p_kb * 128, 0, fb, keep_policy);
+          tma_load_2d(sSFX, &tmSFX, p_kb * 256, 0, fb);
+        }
       }
       __syncwarp();
       ++p_issued;
@@ -160,7 +166,15 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     __syncwarp();  // lane 0 initialised the barriers above
     stream_policy = l2_policy_evict_first();  // weights are read once
     keep_policy = l2_policy_evict_last();     // activations are re-read by every CTA
-    produce(STAGES, false);                   // the first pass over the ring needs no free-slot wait
+    // The first pass over the ring needs no free-slot wait. It runs in two parts: the weight loads go out
+    // at once; the activation loads follow the dependency wait, because the activations' packed scales may
+    // be written by the kernel launched just before this one (programmatic dependent launch).
+    const uint32_t s_stage = p_stage, s_phase = p_phase;
+    const int s_seg = p_seg, s_tile = p_tile, s_kb = p_kb, s_kbe = p_kbe;
+    produce(STAGES, false, 1);
+    p_stage = s_stage; p_phase = s_phase; p_seg = s_seg; p_tile = s_tile; p_kb = s_kb; p_kbe = s_kbe; p_issued = 0;
+    pdl_wait();
+    produce(STAGES, false, 2);
   }
   if (warp == 1) {
     tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -174,7 +188,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the loop; one elected lane issues the copies.
-    produce(0x7fffffff, true);
+    produce(0x7fffffff, true, 0);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = make_idesc_mxf4(128, NP);
@@ -224,6 +238,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     // ------------------------------------------------------------------ epilogue warps 2..5
     const int quad = warp & 3;
     const int nl = quad * 32 + lane;  // weight row inside the tile
+    pdl_wait();  // C, the partial tiles and the counters may still be in use by the kernels before this one
     OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
     auto store_out = [&](int m, int n, float v) {
       OutT* dst = C + size_t(m) * p.ldc + n;

@@ -103,3 +103,27 @@ def grouped_scaled_gemm(a: torch.Tensor, a_scale: torch.Tensor, experts: ExpertW
         _lib.check(lib.wb200_mxfp4_grouped_gemm(E, offs, boffs, N, K, a.data_ptr(), a_sf.data_ptr(), experts._b_ptrs,
                                                 experts._sf_ptrs, c.data_ptr(), ops._DTYPE_CODE[c.dtype], c.stride(0),
                                                 torch.cuda.current_stream().cuda_stream))
+
+
+def moe_scaled_gemm(a: torch.Tensor, a_scale: torch.Tensor, experts: ExpertWeights, expert_ids: torch.Tensor,
+                    num_rows: torch.Tensor, c: torch.Tensor) -> None:
+    """Grouped GEMM over the row layout of `moe_align_block_size(..., block_size=256, ...)`, driven by its device
+    outputs: a [R, K/2] / a_scale [R, K/32] hold the routed rows of all experts (R a multiple of 256, every expert
+    padded to whole 256-row blocks), expert_ids [>= R/256] int32 the expert of each block, num_rows [1] int32 the
+    padded total. c [R, N]; row blocks at or past num_rows are left untouched. No host synchronisation."""
+    lib = _lib.load()
+    ops._as_u8(a, "a")
+    R = a.shape[0]
+    K, N = experts.K, experts.N
+    if R % 256 or a.shape[1] * 2 != K or tuple(a_scale.shape) != (R, K // ops.SCALE_GROUP_SIZE) or not a.is_contiguous():
+        raise ValueError("a must be contiguous [R, K/2] with R a multiple of 256, a_scale [R, K/32]")
+    if tuple(c.shape) != (R, N) or c.stride(1) != 1:
+        raise ValueError(f"c must be [{R}, {N}] with unit column stride")
+    if expert_ids.dtype != torch.int32 or num_rows.dtype != torch.int32 or expert_ids.numel() < R // 256:
+        raise ValueError("expert_ids (one int32 per 256-row block) and num_rows (int32) must be device tensors")
+    as_output_dtype(c.dtype)
+    a_sf = ops.repack_scales(a_scale)
+    with torch.cuda.device(a.device):
+        _lib.check(lib.wb200_mxfp4_moe_gemm(len(experts), R, expert_ids.data_ptr(), num_rows.data_ptr(), N, K, a.data_ptr(),
+                                            a_sf.data.data_ptr(), experts._b_ptrs, experts._sf_ptrs, c.data_ptr(),
+                                            ops._DTYPE_CODE[c.dtype], c.stride(0), torch.cuda.current_stream().cuda_stream))

@@ -6,8 +6,11 @@ wave_lang/kernel/wave/templates/moe.py). Its block-alignment step exists as a to
 (tests/kernel/moe/torch_kernels.py:10-97). Here every step is a CUDA kernel behind the C ABI and the
 two projections are grouped MXFP4 GEMMs over all experts at once:
 
-    route -> moe_align_block_size(128) -> quantise tokens -> gather rows -> grouped GEMM (gate|up)
+    route -> moe_align_block_size(256) -> quantise tokens -> gather rows -> grouped GEMM (gate|up)
           -> silu_and_mul fused with MXFP4 quantisation -> grouped GEMM (down) -> weighted combine
+
+The grouped GEMMs read the routing (expert of every 256-row block, padded row count) from the device arrays
+the alignment kernel wrote, so a forward pass has no host synchronisation.
 """
 
 from __future__ import annotations
@@ -17,7 +20,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib, ops
-from .grouped import ExpertWeights, grouped_scaled_gemm
+from .grouped import ExpertWeights, moe_scaled_gemm
 from .lang import DataType, TORCH_DTYPE_TO_WAVE, bf16, f32
 
 
@@ -136,7 +139,7 @@ class MXFP4ExpertMLP:
     Routing weights are softmax(logits) in f32, top-k (tests/kernel/moe_test.py:111-112).
     """
 
-    BLOCK = 128  # rows per scale-factor block: every expert's rows start on such a boundary
+    BLOCK = 256  # rows per routing block = rows of one CTA-pair tile: every tile belongs to one expert
 
     def __init__(self, w1, w1_scale, w2, w2_scale, top_k: int = 2):
         self.w1 = ExpertWeights(w1, w1_scale)
@@ -152,31 +155,30 @@ class MXFP4ExpertMLP:
         return weight.contiguous(), ids.contiguous()
 
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        """Everything is sized by the worst case of the routing (tokens * top_k + E * 255 rows) and driven by the
+        device outputs of the block alignment, so the call never waits for the GPU."""
         T, dev = x.shape[0], x.device
         n = T * self.top_k
+        B = self.BLOCK
         weight, ids = self.route(router_logits)
-        cap = n + self.E * (self.BLOCK - 1)
+        cap = (n + self.E * (B - 1) + B - 1) // B * B
         sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
-        expert_ids = torch.empty((cap + self.BLOCK - 1) // self.BLOCK, dtype=torch.int32, device=dev)
+        expert_ids = torch.empty(cap // B, dtype=torch.int32, device=dev)
         post_pad = torch.empty(1, dtype=torch.int32, device=dev)
         inverse = torch.empty(n, dtype=torch.int32, device=dev)
-        moe_align_block_size(ids, self.E, self.BLOCK, sorted_ids, expert_ids, post_pad, inverse)
+        moe_align_block_size(ids, self.E, B, sorted_ids, expert_ids, post_pad, inverse)
         xq, xs, _ = ops.quantize_mxfp4(x, want_packed=False)
-        # the grouped GEMM takes per-expert row offsets from the host: one small read-back per call
-        counts = torch.bincount(ids.reshape(-1), minlength=self.E).tolist()
-        offsets = [0]
-        for c in counts:
-            offsets.append(offsets[-1] + (c + self.BLOCK - 1) // self.BLOCK * self.BLOCK)
-        R = offsets[-1]
-        a = torch.empty(R, self.K // 2, dtype=torch.uint8, device=dev)
-        a_s = torch.empty(R, self.K // 32, dtype=torch.uint8, device=dev)
-        gather_rows(xq, sorted_ids, n, self.top_k, a)
+        a = torch.empty(cap, self.K // 2, dtype=torch.uint8, device=dev)
+        a_s = torch.empty(cap, self.K // 32, dtype=torch.uint8, device=dev)
+        gather_rows(xq, sorted_ids, n, self.top_k, a)      # padding rows (id == n) become zero rows
         gather_rows(xs, sorted_ids, n, self.top_k, a_s)
-        h = torch.empty(R, 2 * self.I, dtype=torch.bfloat16, device=dev)
-        grouped_scaled_gemm(a, a_s, self.w1, offsets, h)
+        h = torch.empty(cap, 2 * self.I, dtype=torch.bfloat16, device=dev)
+        moe_scaled_gemm(a, a_s, self.w1, expert_ids, post_pad, h)
+        # row blocks past the padded total are never written by the GEMM: whatever they hold goes through
+        # silu_and_mul and the second GEMM skips them again, and `combine` only reads routed rows
         _, hq, hs = silu_and_mul(h[:, :self.I], h[:, self.I:], quantize=True)
-        y = torch.empty(R, self.w2.N, dtype=torch.bfloat16, device=dev)
-        grouped_scaled_gemm(hq, hs, self.w2, offsets, y)
+        y = torch.empty(cap, self.w2.N, dtype=torch.bfloat16, device=dev)
+        moe_scaled_gemm(hq, hs, self.w2, expert_ids, post_pad, y)
         out = torch.empty(T, self.w2.N, dtype=torch.bfloat16, device=dev)
         combine(y, inverse, weight.reshape(-1), self.top_k, out)
         return out

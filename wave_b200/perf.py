@@ -68,7 +68,7 @@ def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, devi
     (8 experts x [14336, 4096] gate|up weights, 4096 tokens, top-2): microseconds per step and, for the
     memory-bound steps, the bytes they must move / that time."""
     from . import moe, ops
-    from .grouped import grouped_scaled_gemm
+    from .grouped import moe_scaled_gemm
     dev = torch.device(device)
     g = torch.Generator(device=dev).manual_seed(4)
     rnd = lambda *shape: torch.randint(0, 256, shape, dtype=torch.uint8, device=dev, generator=g)  # noqa: E731
@@ -80,17 +80,13 @@ def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, devi
     n = tokens * top_k
     B = mlp.BLOCK
     weight, ids = mlp.route(logits)
-    cap = n + experts * (B - 1)
+    cap = (n + experts * (B - 1) + B - 1) // B * B
     sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
-    expert_ids = torch.empty((cap + B - 1) // B, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(cap // B, dtype=torch.int32, device=dev)
     post = torch.empty(1, dtype=torch.int32, device=dev)
     inverse = torch.empty(n, dtype=torch.int32, device=dev)
     moe.moe_align_block_size(ids, experts, B, sorted_ids, expert_ids, post, inverse)
-    counts = torch.bincount(ids.reshape(-1), minlength=experts).tolist()
-    offsets = [0]
-    for c in counts:
-        offsets.append(offsets[-1] + (c + B - 1) // B * B)
-    R = offsets[-1]
+    R = cap  # every buffer has the worst-case row count; the GEMMs skip the row blocks past the padded total
     xq, xs, _ = ops.quantize_mxfp4(x, want_packed=False)
     a = torch.empty(R, K // 2, dtype=torch.uint8, device=dev)
     a_s = torch.empty(R, K // 32, dtype=torch.uint8, device=dev)
@@ -99,17 +95,17 @@ def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, devi
     out = torch.empty(tokens, K, dtype=torch.bfloat16, device=dev)
     moe.gather_rows(xq, sorted_ids, n, top_k, a)
     moe.gather_rows(xs, sorted_ids, n, top_k, a_s)
-    grouped_scaled_gemm(a, a_s, mlp.w1, offsets, h)
+    moe_scaled_gemm(a, a_s, mlp.w1, expert_ids, post, h)
     _, hq, hs = moe.silu_and_mul(h[:, :inter], h[:, inter:], quantize=True)
     steps = [
         ("moe_align_block_size", lambda: moe.moe_align_block_size(ids, experts, B, sorted_ids, expert_ids, post, inverse), None),
         ("quantize tokens", lambda: ops.quantize_mxfp4(x, want_packed=False), tokens * K * 2 + tokens * K // 2 + tokens * K // 32),
         ("gather codes + scales", lambda: (moe.gather_rows(xq, sorted_ids, n, top_k, a), moe.gather_rows(xs, sorted_ids, n, top_k, a_s)),
          2 * R * (K // 2 + K // 32)),
-        ("grouped GEMM gate|up", lambda: grouped_scaled_gemm(a, a_s, mlp.w1, offsets, h), None),
+        ("grouped GEMM gate|up", lambda: moe_scaled_gemm(a, a_s, mlp.w1, expert_ids, post, h), None),
         ("silu_and_mul + quantise", lambda: moe.silu_and_mul(h[:, :inter], h[:, inter:], quantize=True),
          R * 2 * inter * 2 + R * inter // 2 + R * inter // 32),
-        ("grouped GEMM down", lambda: grouped_scaled_gemm(hq, hs, mlp.w2, offsets, y), None),
+        ("grouped GEMM down", lambda: moe_scaled_gemm(hq, hs, mlp.w2, expert_ids, post, y), None),
         ("combine", lambda: moe.combine(y, inverse, weight.reshape(-1), top_k, out), R * K * 2 + tokens * K * 2),
         ("whole forward", lambda: mlp(x, logits), None),
     ]
