@@ -132,6 +132,53 @@ def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, devi
     return rows
 
 
+def compare_cublaslt(shapes=((8192, 8192, 8192), (4096, 4096, 4096), (2048, 8192, 8192), (16384, 16384, 16384)), iters=20,
+                     device="cuda:0"):
+    """Context only, never a product path: the vendor library's block-scaled FP4 GEMM (cuBLASLt through
+    torch.nn.functional.scaled_mm, 1x32 blocks, E8M0 scales in the 32x4x4 swizzle, which is the packed layout of
+    this library when K is a multiple of 256) on the same operands, timed the same way. Prints both times and the
+    largest difference of the results."""
+    import torch.nn.functional as F
+    from torch.nn.functional import ScalingType, SwizzleType
+    from . import ops
+    rows = []
+    for M, N, K in shapes:
+        g = torch.Generator(device=device).manual_seed(1)
+        a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=device, generator=g)
+        b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=g)
+        a_sf = ops.repack_scales(torch.randint(124, 128, (M, K // 32), dtype=torch.uint8, device=device, generator=g))
+        b_sf = ops.repack_scales(torch.randint(124, 128, (N, K // 32), dtype=torch.uint8, device=device, generator=g))
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+        a4, b4 = a.view(torch.float4_e2m1fn_x2), b.view(torch.float4_e2m1fn_x2)
+        sa, sb = a_sf.data.view(torch.float8_e8m0fnu), b_sf.data.view(torch.float8_e8m0fnu)
+
+        def ours():
+            ops.scaled_gemm_packed(a, a_sf, b, b_sf, c)
+            return c
+
+        def vendor():
+            return F.scaled_mm(a4, b4.t(), sa, ScalingType.BlockWise1x32, sb, ScalingType.BlockWise1x32,
+                               swizzle_a=SwizzleType.SWIZZLE_32_4_4, swizzle_b=SwizzleType.SWIZZLE_32_4_4,
+                               output_dtype=torch.bfloat16)
+
+        diff = float((vendor().float() - ours().float()).abs().max())
+        row = {"M": M, "N": N, "K": K, "max_abs_diff": diff}
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for name, fn in (("wave_b200", ours), ("cublaslt", vendor), ("wave_b200 again", ours)):
+            for _ in range(3):
+                fn()
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / iters
+            row[name] = f"{us:.1f} us / {runtime_us_to_tflops(M, N, K, us):.0f} TFLOP/s"
+        rows.append(row)
+        print(row, flush=True)
+    return rows
+
+
 def time_k_sharded(M=8192, N=8192, k_per_rank=8192, iters=20):
     """Under torchrun (one rank per GPU): the K-sharded GEMM whose tiles are scattered to the owning ranks'
     buffers by the GEMM kernel itself, against the unfused sequence on the same operands (GEMM into a local
@@ -204,11 +251,15 @@ def main(argv=None):
     ap.add_argument("--validate", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--compare-cublaslt", action="store_true", help="context: time cuBLASLt's block-scaled FP4 GEMM on the same operands")
     ap.add_argument("--k-sharded", action="store_true", help="under torchrun: time the K-sharded GEMM against GEMM + NCCL reduce-scatter")
     ap.add_argument("--moe", action="store_true", help="time the steps of the MXFP4 expert MLP instead of the shape sweep")
     args = ap.parse_args(argv)
     if args.moe:
         time_moe(iters=args.iters)
+        return
+    if args.compare_cublaslt:
+        compare_cublaslt(iters=args.iters)
         return
     if args.k_sharded:
         time_k_sharded(iters=args.iters)
