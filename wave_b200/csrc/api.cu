@@ -454,6 +454,7 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   p.tiles_n = (N + 127) / 128;
   p.num_kb = (K + 255) / 256;
   p.accumulate = accumulate;
+  p.dependent = tl_dependent_launch ? 1 : 0;
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_skinny_kernel<NP, STAGES, OutT>;
   static bool smem_set[kMaxDevices] = {};

@@ -52,6 +52,7 @@ struct SkinnyParams {
   int tiles_n;   // ceil(N / 128)
   int num_kb;    // ceil(K / 256)
   int accumulate;  // add to the values already in C instead of overwriting them
+  int dependent;   // launched as the programmatic dependent of the kernel that writes the activations' packed scales
   int* status;
 };
 
@@ -166,15 +167,20 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     __syncwarp();  // lane 0 initialised the barriers above
     stream_policy = l2_policy_evict_first();  // weights are read once
     keep_policy = l2_policy_evict_last();     // activations are re-read by every CTA
-    // The first pass over the ring needs no free-slot wait. It runs in two parts: the weight loads go out
-    // at once; the activation loads follow the dependency wait, because the activations' packed scales may
-    // be written by the kernel launched just before this one (programmatic dependent launch).
-    const uint32_t s_stage = p_stage, s_phase = p_phase;
-    const int s_seg = p_seg, s_tile = p_tile, s_kb = p_kb, s_kbe = p_kbe;
-    produce(STAGES, false, 1);
-    p_stage = s_stage; p_phase = s_phase; p_seg = s_seg; p_tile = s_tile; p_kb = s_kb; p_kbe = s_kbe; p_issued = 0;
-    pdl_wait();
-    produce(STAGES, false, 2);
+    // The first pass over the ring needs no free-slot wait. When this kernel was launched as the programmatic
+    // dependent of the kernel that packs the activations' scales, the pass runs in two parts: the weight loads
+    // go out at once, the activation loads follow the dependency wait. Otherwise the four loads of a stage go
+    // out together (the copy engine takes them in order: a stage completes sooner that way).
+    if (p.dependent) {
+      const uint32_t s_stage = p_stage, s_phase = p_phase;
+      const int s_seg = p_seg, s_tile = p_tile, s_kb = p_kb, s_kbe = p_kbe;
+      produce(STAGES, false, 1);
+      p_stage = s_stage; p_phase = s_phase; p_seg = s_seg; p_tile = s_tile; p_kb = s_kb; p_kbe = s_kbe; p_issued = 0;
+      pdl_wait();
+      produce(STAGES, false, 2);
+    } else {
+      produce(STAGES, false, 0);
+    }
   }
   if (warp == 1) {
     tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -238,7 +244,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     // ------------------------------------------------------------------ epilogue warps 2..5
     const int quad = warp & 3;
     const int nl = quad * 32 + lane;  // weight row inside the tile
-    pdl_wait();  // C, the partial tiles and the counters may still be in use by the kernels before this one
+    if (p.dependent) pdl_wait();  // C, the partial tiles and the counters may still be in use by the kernels before this one
     OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
     auto store_out = [&](int m, int n, float v) {
       OutT* dst = C + size_t(m) * p.ldc + n;
