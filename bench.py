@@ -127,13 +127,16 @@ def cpu_reference_run(w, steps, warmup):
     threads = torch.get_num_threads()
     for _ in range(warmup):
         orc.scaled_gemm(a, a_s, b, b_s)
+    # exactly `steps` steps unless they would take more than two minutes of CPU time: then as many as fit
+    done = 0
     t0 = time.perf_counter()
-    for _ in range(steps):
+    while done < max(steps, 1) and (done == 0 or time.perf_counter() - t0 < 120.0):
         orc.scaled_gemm(a, a_s, b, b_s)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
+        done += 1
+    dt = (time.perf_counter() - t0) / done
     flops = 2.0 * rows * w["N"] * w["K"]
     sample = f"rows 0..{rows - 1} of a against all of b (N={w['N']}, K={w['K']}): dequantise both, f32 torch.mm; {rows}/{w['M']} of the workload's flops"
-    return flops / dt / 1e12, dt, sample, threads
+    return flops / dt / 1e12, dt, sample, threads, done
 
 
 def main():
@@ -158,8 +161,8 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        steps, warm = min(args.steps, 3), min(args.warmup, 1)
-        tf, dt, sample, threads = cpu_reference_run(w, steps, warm)
+        warm = min(args.warmup, 3)
+        tf, dt, sample, threads, steps = cpu_reference_run(w, args.steps, warm)
         print(json.dumps({
             "impl": "reference", "metric": metric, "value": tf, "unit": unit, "n_gpus": args.gpus, "steps": steps,
             "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -321,7 +324,7 @@ def main():
         "gpu_launches": 2 * args.steps + ksteps + 3, "roofline": roofline,
     }
     if world == 1 and not args.no_cpu_baseline:
-        tf, dt, sample, threads = cpu_reference_run(w, 1, 1)
+        tf, dt, sample, threads, _ = cpu_reference_run(w, 1, 1)
         line["cpu_baseline"] = {"value": tf, "unit": unit, "cores": threads, "kind": "port", "sample": sample,
                                 "seconds_per_sample": dt}
     print(json.dumps(line))
