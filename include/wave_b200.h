@@ -48,6 +48,8 @@ extern "C" {
 #define WB200_PATH_TILE_1CTA 1u   /* 128 x BN tiles, one CTA each */
 #define WB200_PATH_TILE_2CTA 2u   /* 256 x BN tiles on CTA pairs (cta_group::2) */
 #define WB200_PATH_SKINNY 3u      /* M <= 128: swapped operands, stream-K, needs a workspace */
+#define WB200_PATH_TILE_SPLITK 4u /* M > 128 with few output tiles and a long K: K slices x tiles in one launch, f32
+                                     partial products in the workspace, added in slice order; needs a workspace */
 #define WB200_PATH_MASK 0xFu
 #define WB200_TILE_N128 0x10u     /* force BN = 128 (default 256 for the tile paths) */
 #define WB200_TILE_N192 0x40u     /* force BN = 192: both accumulators fit tensor memory without sharing columns */
@@ -154,10 +156,12 @@ int wb200_moe_combine(const void* y, long long ldy, int dtype, const int* row_of
  * mxfp4_to_f32 / e8m0_to_f32 (wave_lang/kernel/wave/utils/mxfp_utils.py:60-95). */
 int wb200_mxfp4_dequant(const void* q, const void* scale, int rows, int K, float* out, void* stream);
 
-/* Workspace the GEMM may need for this shape (0 when none). Only the skinny path uses one:
- * f32 partial tiles plus per-tile counters. The first wb200_workspace_init'ed bytes hold the
- * counters; a workspace must be initialised once before its first use and is left clean by
- * every successful call. */
+/* Workspace the GEMM may use for this shape (0 when none). The skinny path (M <= 128) needs one:
+ * f32 partial tiles plus per-tile counters. The split-K tile path (M > 128, so few 256 x 256 output
+ * tiles that they fill less than half of the CTA pairs, K >= 2048) is taken by WB200_PATH_AUTO only
+ * when a workspace of this size is passed: one f32 [M, N] slot per K slice. The first
+ * wb200_workspace_init'ed bytes hold the counters; a workspace must be initialised once before its
+ * first use and is left clean by every successful call. */
 size_t wb200_mxfp4_gemm_workspace_bytes(int M, int N, int K);
 int wb200_workspace_init(void* workspace, size_t bytes, void* stream);
 

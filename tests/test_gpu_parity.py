@@ -689,3 +689,36 @@ def test_config5_one_shard_of_the_sharded_gemm_bf16_sampled(ways):
     gemm(a, a_s + 1, b, b_s, c2)
     assert torch.equal((c.float() * 2).to(torch.bfloat16), c2)
     ops.check_device_status()
+
+
+@pytest.mark.parametrize("shape", [(512, 512, 16000), (256, 512, 4096), (1000, 300, 8192), (300, 260, 2560), (2048, 512, 16000)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_split_k_tile_path(shape, out_dtype):
+    """Few output tiles and a long K (the small-N end of the reference's benchmark shapes,
+    perf/mxfp4_shapes_macrotiles.csv): K slices x tiles in one launch, partial products added in slice order."""
+    M, N, K = shape
+    a, a_s, b, b_s = random_problem(M, N, K, seed=M + N + K, lo=125, hi=129)
+    ad, bd = a.to(DEV), b.to(DEV)
+    asp, bsp = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
+    ref = orc.scaled_gemm(a, a_s, b, b_s)
+    c = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_packed(ad, asp, bd, bsp, c, _lib.PATH_TILE_SPLITK)
+    check(c, a, a_s, b, b_s, ref=ref)
+    auto = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_packed(ad, asp, bd, bsp, auto)  # the automatic choice (split-K from three slices up)
+    check(auto, a, a_s, b, b_s, ref=ref)
+    if out_dtype == torch.float32:  # the split-K templates' contract: add into a caller-initialised c
+        base = torch.randn(M, N)
+        acc = base.to(DEV)
+        ops.scaled_gemm_packed(ad, asp, bd, bsp, acc, _lib.PATH_TILE_SPLITK | _lib.ACCUMULATE)
+        tol = orc.f32_tolerance(orc.dequant_mxfp4(a, a_s), orc.dequant_mxfp4(b, b_s), ref, K)
+        assert bool(((acc.cpu() - (ref + base)).abs() <= tol + 1e-6 * base.abs()).all())
+    ops.check_device_status()
+
+
+def test_split_k_tile_path_refuses_what_it_cannot_do():
+    a, a_s, b, b_s = random_problem(4096, 4096, 1024, seed=1)
+    c = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError):  # plenty of tiles: not a split-K shape
+        ops.scaled_gemm_packed(a.to(DEV), ops.repack_scales(a_s.to(DEV)), b.to(DEV), ops.repack_scales(b_s.to(DEV)), c,
+                               _lib.PATH_TILE_SPLITK)

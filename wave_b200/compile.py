@@ -90,7 +90,7 @@ def validate_options(options: WaveCompileOptions) -> None:
     wave_lang/kernel/wave/compile.py:1489-1500, raises ValueError in the same way)."""
     if options.num_devices != 1:
         raise ValueError("num_devices > 1 is served by wave_b200.multi_gpu.ShardedScaledGemm, not by wave_compile")
-    if options.kernel_path not in (_lib.PATH_AUTO, _lib.PATH_TILE_1CTA, _lib.PATH_TILE_2CTA, _lib.PATH_SKINNY):
+    if options.kernel_path not in (_lib.PATH_AUTO, _lib.PATH_TILE_1CTA, _lib.PATH_TILE_2CTA, _lib.PATH_SKINNY, _lib.PATH_TILE_SPLITK):
         raise ValueError(f"unknown kernel_path {options.kernel_path}")
 
 
@@ -213,8 +213,8 @@ class ScaledGemmKernel:
             # remember this signature: later calls go straight to the combined repack + GEMM entry point
             ws_bytes = ws_ptr = 0
             ws = None  # the plan keeps the workspace tensor alive: it holds its address
-            if M <= 128:
-                ws_bytes = int(self._lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
+            ws_bytes = int(self._lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
+            if ws_bytes:
                 ws = ops._workspace(a.device, ws_bytes)
                 ws_ptr = ws.data_ptr()
             idx = a.device.index if a.device.index is not None else torch.cuda.current_device()

@@ -122,9 +122,11 @@ CUresult encode_2d(CUtensorMap* map, const MapKey& k) {
   return r;
 }
 
-// [rows, row_bytes] uint8 matrix, box = 128 bytes x box_rows, 128-byte swizzle, zero fill.
-int make_operand_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_rows) {
-  const MapKey k{base, (unsigned long long)row_bytes, (unsigned long long)rows, (unsigned long long)row_bytes, 128u,
+// [rows, row_bytes] uint8 matrix (rows pitch_bytes apart; 0 = dense), box = 128 bytes x box_rows, 128-byte swizzle, zero fill.
+int make_operand_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_rows,
+                     long long pitch_bytes = 0) {
+  const MapKey k{base, (unsigned long long)row_bytes, (unsigned long long)rows,
+                 (unsigned long long)(pitch_bytes ? pitch_bytes : row_bytes), 128u,
                  unsigned(box_rows), int(CU_TENSOR_MAP_DATA_TYPE_UINT8), int(CU_TENSOR_MAP_SWIZZLE_128B),
                  int(CU_TENSOR_MAP_L2_PROMOTION_L2_256B)};
   CUresult r = encode_2d(map, k);
@@ -136,8 +138,11 @@ int make_operand_map(CUtensorMap* map, const void* base, long long rows, long lo
 
 // Packed scale array ([row_blocks][k_atoms][512 bytes]) as a 2-D tensor of 32-bit words, one
 // row per 128-row block; a box is box_atoms atoms of 512 bytes (those of one pipeline stage) x box_rows.
-int make_scale_map(CUtensorMap* map, const void* base, int row_blocks, int k_atoms, int box_rows, int box_atoms = 2) {
-  const MapKey k{base, (unsigned long long)k_atoms * 128, (unsigned long long)row_blocks, (unsigned long long)k_atoms * 512,
+// pitch_atoms: atoms between consecutive row blocks when the map covers a K slice of a wider packed array (0 = k_atoms).
+int make_scale_map(CUtensorMap* map, const void* base, int row_blocks, int k_atoms, int box_rows, int box_atoms = 2,
+                   int pitch_atoms = 0) {
+  const MapKey k{base, (unsigned long long)k_atoms * 128, (unsigned long long)row_blocks,
+                 (unsigned long long)(pitch_atoms ? pitch_atoms : k_atoms) * 512,
                  unsigned(box_atoms) * 128u, unsigned(box_rows), int(CU_TENSOR_MAP_DATA_TYPE_UINT32), int(CU_TENSOR_MAP_SWIZZLE_NONE),
                  int(CU_TENSOR_MAP_L2_PROMOTION_L2_256B)};
   CUresult r = encode_2d(map, k);
@@ -424,10 +429,107 @@ int launch_aligned(const DeviceInfo& dev, int num_groups, int max_rows, const in
 }
 
 // ------------------------------------------------------------------------------------------
+// split-K on the tile path: few output tiles, long K
+// ------------------------------------------------------------------------------------------
+constexpr size_t kCounterBytes = 16384;  // head of every workspace: the skinny path's tile counters (room for 4096 N tiles)
+
+// How many K slices to cut a problem into so that its 256 x 256 tiles fill one wave of CTA pairs: 0 when the
+// tiles alone fill at least half of them, or K is too short for slices of at least 4 pipeline stages.
+int splitk_slices(int sm_count, int M, int N, int K) {
+  if (M <= 128) return 0;
+  const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+  const int units = sm_count / 2, kb = (K + 255) / 256;
+  if (tiles * 2 > units) return 0;
+  long long s = units / tiles;
+  if (s > kb / 4) s = kb / 4;
+  if (s > wb::kMaxGroups) s = wb::kMaxGroups;
+  return s >= 2 ? int(s) : 0;
+}
+size_t splitk_workspace_bytes(int slices, int M, int N) { return kCounterBytes + size_t(slices) * M * N * sizeof(float); }
+
+// One persistent launch over (K slice, tile) pairs, slices walked round-robin, every slice writing its f32
+// partial product to its own slot of the workspace; then one pass adds the slots in slice order.
+template <typename OutT>
+int launch_splitk(const DeviceInfo& dev, int slices, int M, int N, int K, const void* a, const void* as, const void* b,
+                  const void* bs, void* c, long long ldc, void* workspace, int accumulate, cudaStream_t stream) {
+  constexpr int CG = 2, BN = 256;
+  using Cfg = wb::GemmCfg<CG, BN, 4>;
+  static wb::GroupedMaps maps;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  const int kb_total = (K + 255) / 256, kb_per = (kb_total + slices - 1) / slices;
+  const int atoms_total = wb::sf_k_atoms(K);
+  const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + Cfg::BM * CG - 1) / (Cfg::BM * CG);
+  float* slots = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kCounterBytes);
+  maps.num_groups = slices;
+  maps.interleave = 1;
+  maps.aligned = 0;
+  maps.tiles_max = tiles_m * tiles_n;
+  maps.tile_start[0] = 0;
+  int used = 0;
+  for (int g = 0; g < slices; ++g) {
+    const int k0 = g * kb_per * 256;
+    const int kg = (k0 >= K) ? 0 : ((K - k0 < kb_per * 256) ? K - k0 : kb_per * 256);
+    maps.rows[g] = M;
+    maps.tile_start[g + 1] = maps.tile_start[g] + (kg > 0 ? tiles_m * tiles_n : 0);
+    if (kg == 0) continue;
+    used = g + 1;
+    const uint8_t* ag = static_cast<const uint8_t*>(a) + k0 / 2;
+    const uint8_t* bg = static_cast<const uint8_t*>(b) + k0 / 2;
+    const uint8_t* asg = static_cast<const uint8_t*>(as) + size_t(k0 / 128) * 512;
+    const uint8_t* bsg = static_cast<const uint8_t*>(bs) + size_t(k0 / 128) * 512;
+    float* cg = slots + size_t(g) * M * N;
+    CUtensorMap* m = &maps.m[g * 5];
+    int rc;
+    if ((rc = make_operand_map(m + 0, ag, M, kg / 2, Cfg::BM, K / 2))) return rc;
+    if ((rc = make_operand_map(m + 1, bg, N, kg / 2, Cfg::B_ROWS, K / 2))) return rc;
+    if ((rc = make_scale_map(m + 2, asg, wb::sf_row_blocks(M), wb::sf_k_atoms(kg), 1, 2, atoms_total))) return rc;
+    if ((rc = make_scale_map(m + 3, bsg, wb::sf_row_blocks(N), wb::sf_k_atoms(kg), BN / 128, 2, atoms_total))) return rc;
+    if ((rc = make_output_map(m + 4, cg, M, N, N, 4))) return rc;
+    maps.c_base[g] = cg;
+  }
+  wb::GemmParams p = {};
+  p.c = slots;
+  p.M = M; p.N = N; p.K = kb_per * 256;  // every slice runs kb_per stages; a shorter last slice reads zero fill
+  p.ldc = N;
+  p.tiles_m = tiles_m;
+  p.tiles_n = tiles_n;
+  p.group_n = 16;
+  p.vec_ok = 1;
+  p.tma_store = 1;
+  p.accumulate = 0;
+  p.status = dev.status_ptr;
+  auto kernel = wb::mxfp4_gemm_kernel<CG, BN, float, wb::GroupedMaps>;
+  static bool smem_set[kMaxDevices] = {};
+  int rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
+  if (rc) return rc;
+  const long long tiles = (long long)maps.num_groups * maps.tiles_max;
+  const int units = dev.sm_count / CG;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(int(tiles < units ? tiles : units) * CG, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tl_dependent_launch ? 2 : 1;
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps, p));
+  const long long vecs = (long long)M * ((N + 3) / 4);
+  wb::splitk_reduce_kernel<OutT><<<unsigned((vecs + 255) / 256), 256, 0, stream>>>(slots, used, (long long)M * N, M, N,
+                                                                                  static_cast<OutT*>(c), ldc, accumulate);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
 // skinny path
 // ------------------------------------------------------------------------------------------
-constexpr size_t kCounterBytes = 16384;  // room for 4096 N tiles (N up to 524288)
-
 size_t skinny_workspace_bytes(int sm_count, int M) {
   return kCounterBytes + size_t(2) * sm_count * M * 128 * sizeof(float);
 }
@@ -803,10 +905,11 @@ int wb200_mxfp4_dequant(const void* q, const void* scale, int rows, int K, float
 }
 
 size_t wb200_mxfp4_gemm_workspace_bytes(int M, int N, int K) {
-  (void)N; (void)K;
-  if (M <= 0 || M > 128) return 0;
-  // 148 SMs on B200; sized for up to 160 so the same buffer fits any sm_100 part.
-  return skinny_workspace_bytes(160, M);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  // 148 SMs on B200; the skinny path's buffer is sized for up to 160 so that it fits any sm_100 part.
+  if (M <= 128) return skinny_workspace_bytes(160, M);
+  const int slices = splitk_slices(148, M, N, K);
+  return slices ? splitk_workspace_bytes(slices, M, N) : 0;
 }
 
 int wb200_workspace_init(void* workspace, size_t bytes, void* stream) {
@@ -827,13 +930,28 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   unsigned path = flags & WB200_PATH_MASK;
   if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_TILE_N192 | WB200_ACCUMULATE)) != 0) return fail(WB200_ERR_INVALID_ARG, "unknown flag bits %#x", flags);
-  if (path > WB200_PATH_SKINNY) return fail(WB200_ERR_INVALID_ARG, "unknown path flag %u", path);
+  if (path > WB200_PATH_TILE_SPLITK) return fail(WB200_ERR_INVALID_ARG, "unknown path flag %u", path);
   if ((flags & WB200_TILE_N128) && (flags & WB200_TILE_N192)) return fail(WB200_ERR_INVALID_ARG, "two tile widths forced at once");
   const int accumulate = (flags & WB200_ACCUMULATE) ? 1 : 0;
+  const int slices = splitk_slices(dev->sm_count, M, N, K);
+  const bool splitk_ok = slices >= 2 && workspace && workspace_bytes >= splitk_workspace_bytes(slices, M, N) &&
+                         (reinterpret_cast<uintptr_t>(workspace) & 15) == 0 && N % 4 == 0;
   if (path == WB200_PATH_AUTO) {
     const bool ws_ok = workspace && workspace_bytes >= skinny_workspace_bytes(dev->sm_count, M);
     if (M <= 128 && ws_ok) path = WB200_PATH_SKINNY;
+    // split-K pays from three slices up; with two, 128-wide tiles do better (1024 x 2048 x 16000: 21.7 us
+    // with two slices, 18.6 us with 128-wide tiles, 24.3 us with neither)
+    else if (splitk_ok && slices >= 3 && !(flags & (WB200_TILE_N128 | WB200_TILE_N192))) path = WB200_PATH_TILE_SPLITK;
     else path = (M > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
+  }
+  if (path == WB200_PATH_TILE_SPLITK) {
+    if (!splitk_ok)
+      return fail(slices >= 2 ? WB200_ERR_WORKSPACE : WB200_ERR_UNSUPPORTED,
+                  "the split-K tile path needs M > 128, at most %d output tiles of 256 x 256, K >= 2048, N %% 4 == 0 and a 16-byte "
+                  "aligned workspace of wb200_mxfp4_gemm_workspace_bytes(M, N, K) bytes", dev->sm_count / 4);
+    if (c_dtype == WB200_F32)
+      return launch_splitk<float>(*dev, slices, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, accumulate, s);
+    return launch_splitk<__nv_bfloat16>(*dev, slices, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, accumulate, s);
   }
   if (path == WB200_PATH_SKINNY) {
     if (M > 128) return fail(WB200_ERR_UNSUPPORTED, "the skinny path handles M <= 128 (got %d)", M);
@@ -849,8 +967,13 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   // Narrow problems fill more SMs with 128-wide tiles.
   int bn = (flags & WB200_TILE_N128) ? 128 : (flags & WB200_TILE_N192) ? 192 : 256;
   if (!(flags & (WB200_TILE_N128 | WB200_TILE_N192)) && (flags & WB200_PATH_MASK) == WB200_PATH_AUTO) {
-    const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
-    if (tiles256 < dev->sm_count) {
+    // 128-wide tiles when the 256-wide ones would leave at least half of the CTAs (or CTA pairs) idle: halving
+    // the tile then doubles the parallelism; above that, two waves of half tiles lose to one wave of whole ones
+    // (2048 x 2048 x 16000: 31.5 us with 128, 25.8 us with 256).
+    const long long tile_rows = (path == WB200_PATH_TILE_2CTA) ? 256 : 128;
+    const long long tiles256 = ((M + tile_rows - 1) / tile_rows) * ((N + 255) / 256);
+    const long long units_now = (path == WB200_PATH_TILE_2CTA) ? dev->sm_count / 2 : dev->sm_count;
+    if (tiles256 * 2 <= units_now) {
       bn = 128;
     } else if (path == WB200_PATH_TILE_2CTA) {
       // 192-wide tiles cost ~4 % more per column (more operand traffic per flop, measured on

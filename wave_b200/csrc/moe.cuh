@@ -246,4 +246,32 @@ sum_slots_kernel(const float* __restrict__ slots, int num_slots, long long slot_
   }
 }
 
+// c[r, :] (+)= slots[0][r, :] + slots[1][r, :] + ... in slot order (f32), rounded once to the output type:
+// the reduction of the tile path's split-K. Slots are dense [M, N] f32 matrices; c has row pitch ldc.
+template <typename T>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ slots, int num_slots, long long slot_stride, int M, int N, T* __restrict__ c,
+                     long long ldc, int accumulate) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int nvec = (N + 3) >> 2;
+  if (idx >= (long long)M * nvec) return;
+  const int r = int(idx / nvec), c0 = int(idx - (long long)r * nvec) * 4;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const float* src = slots + (long long)r * N + c0;
+  if (c0 + 4 <= N && (N & 3) == 0) {
+    for (int s = 0; s < num_slots; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(src + s * slot_stride);
+      acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+    }
+  } else {
+    for (int s = 0; s < num_slots; ++s)
+      for (int j = 0; j < 4; ++j)
+        if (c0 + j < N) acc[j] += src[s * slot_stride + j];
+  }
+  T* dst = c + (long long)r * ldc + c0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (c0 + j < N) dst[j] = from_f32<T>(accumulate ? acc[j] + to_f32<T>(dst[j]) : acc[j]);
+}
+
 }  // namespace wb

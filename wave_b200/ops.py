@@ -139,9 +139,9 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
     if (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
         raise ValueError("packed scales do not match the operand shapes")
     ldc = c.stride(0) if M > 1 else N  # the stride of a size-1 dimension is arbitrary
-    ws_bytes = ws_ptr = 0
-    if M <= 128:
-        ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
+    ws_ptr = 0
+    ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))  # skinny shapes and split-K shapes use one
+    if ws_bytes:
         ws_ptr = _workspace(a.device, ws_bytes).data_ptr()
     dev_index = a.device.index
     if dev_index is None or dev_index == torch.cuda.current_device():

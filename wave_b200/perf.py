@@ -3,7 +3,8 @@
 
 Same bookkeeping as the reference's benchmark driver (wave_lang/kernel/wave/perf/benchmark_mxfp4.py):
 flops = 2 M N K (:78-79), bytes = M K/2 + M K/32 + N K/2 + N K/32 + M N sizeof(c) (:82-85), TFLOP/s from the
-mean device time of `iters` back-to-back launches between two CUDA events (:117-138), optional
+mean device time of `iters` back-to-back launches between two CUDA events (:117-138; here the launches are
+replayed from a CUDA graph so that the Python launch cost is not in the figure), optional
 validation of every shape against a reference GEMM before timing (:163-177). The reference sweeps a
 CSV of 167 shapes with K = 16000; here the grid is generated: M in {512 .. 8192}, N in {512 .. 32768},
 K = 16000 (not a multiple of the 256-element pipeline stage, so every shape exercises the K tail),
@@ -53,10 +54,17 @@ def time_shape(M, N, K, out_dtype=torch.bfloat16, iters: int = 20, validate: boo
         rows = torch.arange(0, M, max(1, M // 64), device=device)
         ref = ops.dequant_mxfp4(x[rows].contiguous(), xs[rows].contiguous()) @ ops.dequant_mxfp4(w_t, ws).T
         torch.testing.assert_close(c[rows].float(), ref, rtol=2e-2, atol=1e-2 * float(ref.abs().max()))
+    # `iters` launches captured in one CUDA graph and replayed: the Python launch cost (~15 us per call) would
+    # otherwise bound every shape that runs for less than that
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c)
+    graph.replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(iters):
-        ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c)
+    graph.replay()
     e1.record()
     torch.cuda.synchronize()
     ops.check_device_status()
