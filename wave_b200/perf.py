@@ -61,14 +61,22 @@ def time_shape(M, N, K, out_dtype=torch.bfloat16, iters: int = 20, validate: boo
     with torch.cuda.graph(graph):
         for _ in range(iters):
             ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c)
-    graph.replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     graph.replay()
     e1.record()
     torch.cuda.synchronize()
+    # warm up for ~30 ms of GPU time (clocks ramp up under load), then time as many replays as fill ~30 ms more
+    reps = max(2, int(30.0 / max(e0.elapsed_time(e1), 1e-3)))
+    for _ in range(reps):
+        graph.replay()
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
     ops.check_device_status()
-    return e0.elapsed_time(e1) * 1e3 / iters
+    return e0.elapsed_time(e1) * 1e3 / (iters * reps)
 
 
 def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, device="cuda:0"):
