@@ -716,6 +716,32 @@ def test_split_k_tile_path(shape, out_dtype):
     ops.check_device_status()
 
 
+def test_split_k_is_the_automatic_choice_under_graph_capture_only():
+    """Eager Python calls keep the plain tile path (the split-K launch costs more host time than it saves on
+    the GPU for a slow host); a call captured into a CUDA graph takes split-K. Both match the oracle; the
+    captured one equals the forced split-K result bit for bit."""
+    M, N, K = 512, 512, 8192
+    a, a_s, b, b_s = random_problem(M, N, K, seed=77, lo=125, hi=129)
+    ad, bd = a.to(DEV), b.to(DEV)
+    asp, bsp = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
+    forced = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    plain = torch.empty_like(forced)
+    eager = torch.empty_like(forced)
+    captured = torch.empty_like(forced)
+    ops.scaled_gemm_packed(ad, asp, bd, bsp, forced, _lib.PATH_TILE_SPLITK)
+    ops.scaled_gemm_packed(ad, asp, bd, bsp, plain, _lib.PATH_TILE_2CTA | _lib.TILE_N128)
+    ops.scaled_gemm_packed(ad, asp, bd, bsp, eager)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.scaled_gemm_packed(ad, asp, bd, bsp, captured)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(eager, plain) and torch.equal(captured, forced)
+    check(captured, a, a_s, b, b_s)
+    check(eager, a, a_s, b, b_s)
+
+
 def test_split_k_tile_path_refuses_what_it_cannot_do():
     a, a_s, b, b_s = random_problem(4096, 4096, 1024, seed=1)
     c = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV)

@@ -28,6 +28,7 @@ PATH_TILE_1CTA = 1
 PATH_TILE_2CTA = 2
 PATH_SKINNY = 3
 PATH_TILE_SPLITK = 4
+PATH_MASK = 0xF
 TILE_N128 = 0x10
 TILE_N192 = 0x40
 ACCUMULATE = 0x20

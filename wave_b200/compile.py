@@ -134,6 +134,8 @@ class ScaledGemmKernel:
 
     def _launch(self, plan, a, a_scale, b, b_scale, c) -> None:
         M, N, K, a_buf, ws_ptr, ws_bytes, flags, dtype_code, dev_index, _ws_keepalive = plan
+        if M > 128 and ws_bytes and not ops.split_k_pays() and (flags & _lib.PATH_MASK) != _lib.PATH_TILE_SPLITK:
+            ws_ptr = ws_bytes = 0  # eager call: stay on the plain tile path (see ops.split_k_pays)
         b_sf = self._weight_scales.get(b_scale)
         lib = self._lib
         if dev_index == torch.cuda.current_device():

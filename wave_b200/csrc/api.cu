@@ -461,12 +461,24 @@ int launch_splitk(const DeviceInfo& dev, int slices, int M, int N, int K, const 
   const int atoms_total = wb::sf_k_atoms(K);
   const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + Cfg::BM * CG - 1) / (Cfg::BM * CG);
   float* slots = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kCounterBytes);
+  // The descriptor table depends on the operand addresses and the shape only: a caller that repeats a call
+  // (the usual case) reuses the table built last time instead of looking up 5 maps per slice again.
+  struct Key { const void *a, *as, *b, *bs, *ws; int M, N, K, slices, dev, zero; };  // 64 bytes, no padding (compared with memcmp)
+  static Key last = {};
+  static bool last_valid = false;
+  static int last_used = 0;
+  int cur_dev = 0;
+  WB_CUDA(cudaGetDevice(&cur_dev));
+  const Key key{a, as, b, bs, workspace, M, N, K, slices, cur_dev, 0};
+  const bool reuse = last_valid && memcmp(&last, &key, sizeof(Key)) == 0;
+  int used = reuse ? last_used : 0;
+  if (!reuse) {
+  last_valid = false;
   maps.num_groups = slices;
   maps.interleave = 1;
   maps.aligned = 0;
   maps.tiles_max = tiles_m * tiles_n;
   maps.tile_start[0] = 0;
-  int used = 0;
   for (int g = 0; g < slices; ++g) {
     const int k0 = g * kb_per * 256;
     const int kg = (k0 >= K) ? 0 : ((K - k0 < kb_per * 256) ? K - k0 : kb_per * 256);
@@ -487,6 +499,10 @@ int launch_splitk(const DeviceInfo& dev, int slices, int M, int N, int K, const 
     if ((rc = make_scale_map(m + 3, bsg, wb::sf_row_blocks(N), wb::sf_k_atoms(kg), BN / 128, 2, atoms_total))) return rc;
     if ((rc = make_output_map(m + 4, cg, M, N, N, 4))) return rc;
     maps.c_base[g] = cg;
+  }
+  last = key;
+  last_used = used;
+  last_valid = true;
   }
   wb::GemmParams p = {};
   p.c = slots;

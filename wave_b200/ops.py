@@ -124,6 +124,14 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 _DTYPE_CODE = {torch.float32: _lib.WB200_F32, torch.bfloat16: _lib.WB200_BF16}
 
 
+def split_k_pays() -> bool:
+    """The split-K tile path halves the GPU time of small long-K shapes but its launch costs ~15 us more on the
+    host (a 20 KB kernel parameter block plus a second kernel). From Python that only pays where the host cost
+    is not in the loop: while the call is being captured into a CUDA graph. Eager calls pass no workspace for
+    M > 128 and so stay on the plain tile path; C callers decide for themselves by passing one or not."""
+    return torch.cuda.is_current_stream_capturing()
+
+
 def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_sf: PackedScales, c: torch.Tensor,
                        flags: int = _lib.PATH_AUTO) -> None:
     """c[M, N] = dequant(a) @ dequant(b).T with both scale sets already packed. c may be a column
@@ -139,10 +147,11 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
     if (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
         raise ValueError("packed scales do not match the operand shapes")
     ldc = c.stride(0) if M > 1 else N  # the stride of a size-1 dimension is arbitrary
-    ws_ptr = 0
-    ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))  # skinny shapes and split-K shapes use one
-    if ws_bytes:
-        ws_ptr = _workspace(a.device, ws_bytes).data_ptr()
+    ws_ptr = ws_bytes = 0
+    if M <= 128 or (flags & _lib.PATH_MASK) == _lib.PATH_TILE_SPLITK or split_k_pays():
+        ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))  # skinny shapes and split-K shapes use one
+        if ws_bytes:
+            ws_ptr = _workspace(a.device, ws_bytes).data_ptr()
     dev_index = a.device.index
     if dev_index is None or dev_index == torch.cuda.current_device():
         rc = lib.wb200_mxfp4_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
