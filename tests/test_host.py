@@ -136,3 +136,14 @@ def test_tile_order_is_a_permutation_grouped_by_n():
         # a run of `g` consecutive ids inside a full group shares one M tile
         if nt >= g:
             assert len({m for m, _ in seen[:g]}) == 1
+
+
+def test_perf_formulas_match_the_reference_benchmark_driver():
+    """flops and byte counts of wave_lang/kernel/wave/perf/benchmark_mxfp4.py:78-92."""
+    from wave_b200 import perf
+    M, N, K = 8192, 28672, 16000
+    assert perf.get_flops(M, N, K) == 2 * M * N * K
+    assert perf.get_byte_count_mxfp4(M, N, K) == M * K // 2 + M * K // 32 + N * K // 2 + N * K // 32 + M * N * 2
+    assert abs(perf.runtime_us_to_tflops(8192, 8192, 8192, 122.17) - 9000) < 1
+    shapes = perf.default_shapes()
+    assert (8192, 8192, 8192) in shapes and all(k % 32 == 0 for _, _, k in shapes)
