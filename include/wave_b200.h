@@ -142,9 +142,17 @@ int wb200_moe_gather_rows(const void* src, long long src_pitch, int row_bytes, c
 /* out = x1 / (1 + exp(-x1)) * x2 elementwise on [rows, n] matrices of f32 or bf16 (pitches in elements):
  * get_silu_and_mul_kernel (wave_lang/kernel/wave/templates/moe.py:89-145). out may be NULL when q is
  * given: q [rows, n/2] and the scale outputs (as wb200_quantize_mxfp4) receive the f32 result quantised
- * to MXFP4 in the same pass, ready for the down-projection GEMM. */
+ * to MXFP4 in the same pass, ready for the down-projection GEMM. num_rows (may be NULL): DEVICE value, rows at or
+ * past it are skipped (the padded row count of a routed batch whose buffers have the worst-case size). */
 int wb200_silu_and_mul(const void* x1, const void* x2, long long ld1, long long ld2, int dtype, int rows, int n, void* out,
-                       long long ldo, void* q, void* scale_rowmajor, void* scale_packed, void* stream);
+                       long long ldo, void* q, void* scale_rowmajor, void* scale_packed, const int* num_rows, void* stream);
+
+/* Quantise routed tokens straight to their expert-sorted rows: row t of x [tokens, K] (f32 or bf16) is quantised
+ * once (as wb200_quantize_mxfp4) and its codes and row-major scales are written to the rows dst_rows[t * top_k + j]
+ * of q / scale_rowmajor for j < top_k (DEVICE array, the `inverse` output of wb200_moe_align_block_size; negative
+ * entries are skipped). Rows of q that no token maps to are not written. Replaces quantise + wb200_moe_gather_rows. */
+int wb200_moe_quantize_scatter(const void* x, int x_dtype, long long ldx, int tokens, int K, int top_k, const int* dst_rows,
+                               void* q, void* scale_rowmajor, void* stream);
 
 /* out[t, :] = sum over j < top_k of weight[t * top_k + j] * y[row_of[t * top_k + j], :], f32 accumulation in
  * slot order, pairs with row_of < 0 skipped: the weighted sum that ends the reference's MoE

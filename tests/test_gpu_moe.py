@@ -237,3 +237,35 @@ def test_expert_mlp_forward_can_be_captured_in_a_cuda_graph():
     torch.cuda.synchronize()
     assert torch.equal(captured, again) and not torch.equal(captured, eager)
     ops.check_device_status()
+
+
+def test_quantize_scatter_equals_quantise_then_gather_on_routed_rows():
+    T, E, K, k = 300, 6, 1024, 2
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    _, ids = torch.topk(torch.rand(T, E, generator=g), k=k, dim=1)
+    sorted_ids, _, post, inverse = run_align(ids, E, 256)
+    cap = (T * k + E * 255 + 255) // 256 * 256
+    q = torch.full((cap, K // 2), 0xEE, dtype=torch.uint8, device=DEV)
+    s = torch.full((cap, K // 32), 0xEE, dtype=torch.uint8, device=DEV)
+    moe.quantize_scatter(x.to(DEV), torch.from_numpy(inverse).to(DEV), k, q, s)
+    q_ref, s_ref = orc.quantize_mxfp4(x.float())
+    routed = torch.from_numpy(sorted_ids[:post]).long()
+    real = routed < T * k
+    pos = torch.arange(post)[real]
+    assert torch.equal(q.cpu()[pos], q_ref[routed[real] // k]) and torch.equal(s.cpu()[pos], s_ref[routed[real] // k])
+    untouched = torch.ones(cap, dtype=torch.bool)
+    untouched[pos] = False
+    assert bool((q.cpu()[untouched] == 0xEE).all()) and bool((s.cpu()[untouched] == 0xEE).all())
+
+
+def test_silu_and_mul_row_limit_from_device():
+    rows, n = 512, 256
+    g = torch.Generator().manual_seed(8)
+    h = torch.randn(rows, 2 * n, generator=g).to(torch.bfloat16).to(DEV)
+    out = torch.full((rows, n), -3.0, dtype=torch.bfloat16, device=DEV)
+    limit = torch.tensor([384], dtype=torch.int32, device=DEV)
+    wb.silu_and_mul(h[:, :n], h[:, n:], out=out, num_rows=limit)
+    ref = moe_oracle.silu_and_mul(h[:384, :n].cpu(), h[:384, n:].cpu())
+    assert int(orc.bf16_ulp_distance(out[:384], ref).max()) <= 1
+    assert bool((out[384:] == -3.0).all())

@@ -58,6 +58,7 @@ EXPORTED_SYMBOLS = (
     "wb200_moe_align_block_size",
     "wb200_moe_gather_rows",
     "wb200_silu_and_mul",
+    "wb200_moe_quantize_scatter",
     "wb200_moe_combine",
     "wb200_mxfp4_gemm_scatter_rows",
     "wb200_peer_buffer_create",
@@ -147,7 +148,10 @@ def load() -> ctypes.CDLL:
     lib.wb200_moe_gather_rows.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_ll, c_void_p]
     lib.wb200_silu_and_mul.restype = c_int
     lib.wb200_silu_and_mul.argtypes = [c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p,
-                                       c_void_p, c_void_p, c_void_p]
+                                       c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.wb200_moe_quantize_scatter.restype = c_int
+    lib.wb200_moe_quantize_scatter.argtypes = [c_void_p, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                               c_void_p]
     lib.wb200_moe_combine.restype = c_int
     lib.wb200_moe_combine.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_ll,
                                       c_void_p]

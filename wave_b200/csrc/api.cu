@@ -835,7 +835,7 @@ int wb200_moe_gather_rows(const void* src, long long src_pitch, int row_bytes, c
 extern "C++" {
 template <typename T>
 static int launch_silu(const void* x1, const void* x2, long long ld1, long long ld2, int rows, int n, void* out, long long ldo,
-                       void* q, void* scale_rm, void* scale_packed, int k_atoms, cudaStream_t s) {
+                       void* q, void* scale_rm, void* scale_packed, int k_atoms, const int* row_limit, cudaStream_t s) {
   auto ok = [&](const void* p, long long ld) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * sizeof(T)) % 16 == 0; };
   const bool vec = ok(x1, ld1) && ok(x2, ld2) && (!out || ok(out, ldo));
   const dim3 blocks(rows, ((n + 31) / 32 + 64 * wb::kSiluUnroll - 1) / (64 * wb::kSiluUnroll));
@@ -843,19 +843,19 @@ static int launch_silu(const void* x1, const void* x2, long long ld1, long long 
     wb::silu_and_mul_kernel<T, true><<<blocks, 256, 0, s>>>(static_cast<const T*>(x1), static_cast<const T*>(x2), ld1, ld2, rows,
                                                             n, static_cast<T*>(out), ldo, static_cast<uint8_t*>(q),
                                                             static_cast<uint8_t*>(scale_rm),
-                                                            static_cast<uint8_t*>(scale_packed), k_atoms);
+                                                            static_cast<uint8_t*>(scale_packed), k_atoms, row_limit);
   else
     wb::silu_and_mul_kernel<T, false><<<blocks, 256, 0, s>>>(static_cast<const T*>(x1), static_cast<const T*>(x2), ld1, ld2,
                                                              rows, n, static_cast<T*>(out), ldo, static_cast<uint8_t*>(q),
                                                              static_cast<uint8_t*>(scale_rm),
-                                                             static_cast<uint8_t*>(scale_packed), k_atoms);
+                                                             static_cast<uint8_t*>(scale_packed), k_atoms, row_limit);
   WB_CUDA(cudaGetLastError());
   return WB200_OK;
 }
 }  // extern "C++"
 
 int wb200_silu_and_mul(const void* x1, const void* x2, long long ld1, long long ld2, int dtype, int rows, int n, void* out,
-                       long long ldo, void* q, void* scale_rowmajor, void* scale_packed, void* stream) {
+                       long long ldo, void* q, void* scale_rowmajor, void* scale_packed, const int* num_rows, void* stream) {
   if (rows <= 0 || n <= 0) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: rows = %d, n = %d", rows, n);
   if (!x1 || !x2 || (!out && !q)) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: null pointer");
   if (dtype != WB200_F32 && dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "silu_and_mul: unknown dtype %d", dtype);
@@ -877,8 +877,8 @@ int wb200_silu_and_mul(const void* x1, const void* x2, long long ld1, long long 
                                                                                   n / 32, k_atoms, rbs);
   }
   if (dtype == WB200_F32)
-    return launch_silu<float>(x1, x2, ld1, ld2, rows, n, out, ldo, q, scale_rowmajor, scale_packed, k_atoms, s);
-  return launch_silu<__nv_bfloat16>(x1, x2, ld1, ld2, rows, n, out, ldo, q, scale_rowmajor, scale_packed, k_atoms, s);
+    return launch_silu<float>(x1, x2, ld1, ld2, rows, n, out, ldo, q, scale_rowmajor, scale_packed, k_atoms, num_rows, s);
+  return launch_silu<__nv_bfloat16>(x1, x2, ld1, ld2, rows, n, out, ldo, q, scale_rowmajor, scale_packed, k_atoms, num_rows, s);
 }
 
 int wb200_moe_combine(const void* y, long long ldy, int dtype, const int* row_of, const float* weight, int tokens, int top_k,
@@ -900,6 +900,32 @@ int wb200_moe_combine(const void* y, long long ldy, int dtype, const int* row_of
   else
     wb::moe_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(y), ldy, row_of, weight,
                                                                  tokens, top_k, cols, static_cast<__nv_bfloat16*>(out), ldo);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
+int wb200_moe_quantize_scatter(const void* x, int x_dtype, long long ldx, int tokens, int K, int top_k, const int* dst_rows,
+                               void* q, void* scale_rowmajor, void* stream) {
+  if (tokens <= 0 || K <= 0 || K % 32 != 0 || top_k <= 0)
+    return fail(WB200_ERR_INVALID_ARG, "moe_quantize_scatter: tokens = %d, K = %d, top_k = %d", tokens, K, top_k);
+  if (!x || !dst_rows || !q || !scale_rowmajor) return fail(WB200_ERR_INVALID_ARG, "moe_quantize_scatter: null pointer");
+  if (x_dtype != WB200_F32 && x_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "moe_quantize_scatter: unknown input dtype %d", x_dtype);
+  if (ldx < K) return fail(WB200_ERR_INVALID_ARG, "moe_quantize_scatter: ldx = %lld is smaller than K = %d", ldx, K);
+  const int esz = (x_dtype == WB200_F32) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(q) & 3))
+    return fail(WB200_ERR_ALIGNMENT, "moe_quantize_scatter: x rows must be 16-byte aligned and q 4-byte aligned");
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 blocks(tokens, (K / 32 + 63) / 64);
+  if (x_dtype == WB200_F32)
+    wb::quantize_scatter_mxfp4_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), ldx, tokens, K, top_k, dst_rows,
+                                                                    static_cast<uint8_t*>(q), static_cast<uint8_t*>(scale_rowmajor));
+  else
+    wb::quantize_scatter_mxfp4_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx, tokens, K,
+                                                                            top_k, dst_rows, static_cast<uint8_t*>(q),
+                                                                            static_cast<uint8_t*>(scale_rowmajor));
   WB_CUDA(cudaGetLastError());
   return WB200_OK;
 }

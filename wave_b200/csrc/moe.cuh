@@ -143,8 +143,10 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 silu_and_mul_kernel(const T* __restrict__ x1, const T* __restrict__ x2, long long ld1, long long ld2, int rows, int n,
                     T* __restrict__ out, long long ldo, uint8_t* __restrict__ q, uint8_t* __restrict__ scale_rm,
-                    uint8_t* __restrict__ scale_packed, int k_atoms) {
+                    uint8_t* __restrict__ scale_packed, int k_atoms, const int* __restrict__ row_limit) {
   constexpr int U = kSiluUnroll;
+  // rows at or past *row_limit (a device value: the padded row count of a routed batch) are left alone
+  if (row_limit) rows = min(rows, __ldg(row_limit));
   const int g0 = blockIdx.y * 64 + (threadIdx.x >> 2);
   const int sub = threadIdx.x & 3;
   const int nblocks = (n + 31) >> 5;

@@ -26,13 +26,10 @@ __device__ __forceinline__ uint32_t e2m1x2_code(float lo, float hi) {
   return uint32_t(r);
 }
 
-// Quantises the 32 values of row r, K block kb held by a group of 32 / VPL neighbouring lanes (v: the VPL
-// consecutive values of lane `sub` of the group; VPL = 4 or 8) and stores codes and scale. All lanes of a
-// warp must call it together (shuffles); inactive groups pass active = false and store nothing.
+// Scale byte and codes of the 32 values held by a group of 32 / VPL neighbouring lanes (v: the VPL consecutive
+// values of this lane; VPL = 4 or 8). All lanes of a warp must call it together (shuffles).
 template <int VPL>
-__device__ __forceinline__ void mxfp4_encode_group(const float (&v)[VPL], bool active, int r, int kb, int sub, int K,
-                                                   int kblocks, int k_atoms, uint8_t* __restrict__ q,
-                                                   uint8_t* __restrict__ scale_rm, uint8_t* __restrict__ scale_packed) {
+__device__ __forceinline__ void mxfp4_encode_values(const float (&v)[VPL], uint32_t& packed, int& sb) {
   static_assert(VPL == 4 || VPL == 8, "4 or 8 values per lane");
   float amax = 0.f;
 #pragma unroll
@@ -41,7 +38,7 @@ __device__ __forceinline__ void mxfp4_encode_group(const float (&v)[VPL], bool a
   for (int o = 1; o < 32 / VPL; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   // floor(log2(amax)) is the unbiased exponent field for normal numbers; subnormal maxima fall
   // below the clamp at 0 either way
-  int sb = 127;
+  sb = 127;
   if (amax > 0.f) {
     sb = int((__float_as_uint(amax) >> 23) & 0xff) - 2;
     sb = max(0, min(254, sb));
@@ -49,10 +46,16 @@ __device__ __forceinline__ void mxfp4_encode_group(const float (&v)[VPL], bool a
   // y = x * 2^(127 - sb), exact; 2^127 and 2^-127 are both representable
   const int ie = 127 - sb;  // -127 .. 127
   const float inv = (ie == -127) ? __int_as_float(0x00400000) : __int_as_float((ie + 127) << 23);
-  uint32_t packed = 0;
+  packed = 0;
 #pragma unroll
   for (int j = 0; j < VPL / 2; ++j) packed |= e2m1x2_code(v[2 * j] * inv, v[2 * j + 1] * inv) << (8 * j);
-  if (!active) return;
+}
+
+// Stores what mxfp4_encode_values produced for row r, K block kb (lane `sub` of the group).
+template <int VPL>
+__device__ __forceinline__ void mxfp4_store_block(uint32_t packed, int sb, int r, int kb, int sub, int K, int kblocks,
+                                                  int k_atoms, uint8_t* __restrict__ q, uint8_t* __restrict__ scale_rm,
+                                                  uint8_t* __restrict__ scale_packed) {
   uint8_t* dst = q + (long long)r * (K / 2) + kb * 16;
   if constexpr (VPL == 4) reinterpret_cast<uint16_t*>(dst)[sub] = uint16_t(packed);
   else reinterpret_cast<uint32_t*>(dst)[sub] = packed;
@@ -63,6 +66,18 @@ __device__ __forceinline__ void mxfp4_encode_group(const float (&v)[VPL], bool a
       scale_packed[off] = uint8_t(sb);
     }
   }
+}
+
+// Quantises the 32 values of row r, K block kb held by a group of 32 / VPL neighbouring lanes and stores codes
+// and scale. All lanes of a warp must call it together; inactive groups pass active = false and store nothing.
+template <int VPL>
+__device__ __forceinline__ void mxfp4_encode_group(const float (&v)[VPL], bool active, int r, int kb, int sub, int K,
+                                                   int kblocks, int k_atoms, uint8_t* __restrict__ q,
+                                                   uint8_t* __restrict__ scale_rm, uint8_t* __restrict__ scale_packed) {
+  uint32_t packed;
+  int sb;
+  mxfp4_encode_values<VPL>(v, packed, sb);
+  if (active) mxfp4_store_block<VPL>(packed, sb, r, kb, sub, K, kblocks, k_atoms, q, scale_rm, scale_packed);
 }
 
 // 8 consecutive values from 16-byte aligned memory.
@@ -92,6 +107,30 @@ quantize_mxfp4_kernel(const InT* __restrict__ x, long long ldx, int rows, int K,
   float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (active) load8(x + (long long)r * ldx + kb * 32 + sub * 8, v);
   mxfp4_encode_group<8>(v, active, r, kb, sub, K, kblocks, k_atoms, q, scale_rm, scale_packed);
+}
+
+// Quantise-and-scatter for routed tokens: row t of x is quantised once and written to the `copies` output rows
+// dst_rows[t * copies + j] (negative entries are skipped): the tokens of a mixture-of-experts layer go straight
+// to their expert-sorted rows without a separate gather pass. Scales are written row-major.
+template <typename InT>
+__global__ void __launch_bounds__(256)
+quantize_scatter_mxfp4_kernel(const InT* __restrict__ x, long long ldx, int rows, int K, int copies,
+                              const int* __restrict__ dst_rows, uint8_t* __restrict__ q, uint8_t* __restrict__ scale_rm) {
+  const int sub = threadIdx.x & 3;
+  const int kblocks = K >> 5;
+  const int r = blockIdx.x;
+  const int kb = blockIdx.y * 64 + (threadIdx.x >> 2);
+  const bool active = r < rows && kb < kblocks;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (active) load8(x + (long long)r * ldx + kb * 32 + sub * 8, v);
+  uint32_t packed;
+  int sb;
+  mxfp4_encode_values<8>(v, packed, sb);
+  if (!active) return;
+  for (int j = 0; j < copies; ++j) {
+    const int dst = dst_rows[r * copies + j];
+    if (dst >= 0) mxfp4_store_block<8>(packed, sb, dst, kb, sub, K, kblocks, 0, q, scale_rm, nullptr);
+  }
 }
 
 // Fills the padding bytes of a packed scale array (rows past `rows` in the last 128-row block, K blocks

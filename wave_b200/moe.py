@@ -63,10 +63,33 @@ def gather_rows(src: torch.Tensor, sorted_ids: torch.Tensor, num_ids: int, top_k
                                              num_ids, top_k, out.data_ptr(), out.stride(0), _stream()))
 
 
-def silu_and_mul(x1: torch.Tensor, x2: torch.Tensor, out: torch.Tensor | None = None, quantize: bool = False):
+def quantize_scatter(x: torch.Tensor, dst_rows: torch.Tensor, top_k: int, q: torch.Tensor, scale: torch.Tensor) -> None:
+    """Quantise x [T, K] (f32 / bf16) to MXFP4 and write row t to rows dst_rows[t * top_k + j] of q [R, K/2] and
+    scale [R, K/32] (both contiguous uint8): tokens go straight to their expert-sorted rows."""
+    lib = _lib.load()
+    if x.dtype not in ops._DTYPE_CODE or x.dim() != 2 or not x.is_cuda:
+        raise ValueError("x must be a 2-D f32 or bf16 CUDA tensor")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    T, K = x.shape
+    if dst_rows.dtype != torch.int32 or dst_rows.numel() != T * top_k or not dst_rows.is_contiguous():
+        raise ValueError("dst_rows must be a contiguous int32 tensor with tokens * top_k entries")
+    ops._as_u8(q, "q")
+    ops._as_u8(scale, "scale")
+    if not (q.is_contiguous() and scale.is_contiguous()) or q.shape[1] != K // 2 or scale.shape[1] != K // 32 or \
+            q.shape[0] != scale.shape[0]:
+        raise ValueError("q must be contiguous [R, K/2] and scale contiguous [R, K/32]")
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wb200_moe_quantize_scatter(x.data_ptr(), ops._DTYPE_CODE[x.dtype], x.stride(0) if T > 1 else K, T, K,
+                                                  top_k, dst_rows.data_ptr(), q.data_ptr(), scale.data_ptr(), _stream()))
+
+
+def silu_and_mul(x1: torch.Tensor, x2: torch.Tensor, out: torch.Tensor | None = None, quantize: bool = False,
+                 num_rows: torch.Tensor | None = None):
     """out = silu(x1) * x2 ([rows, n], f32 or bf16, unit column stride; x1 and x2 may be column blocks of one
     matrix). With quantize=True also returns (codes [rows, n/2], scales [rows, n/32]) of the f32 result
-    quantised to MXFP4 in the same pass; `out` may then be omitted."""
+    quantised to MXFP4 in the same pass; `out` may then be omitted. num_rows: int32 device tensor, rows at or
+    past its value are skipped."""
     lib = _lib.load()
     if x1.dtype not in ops._DTYPE_CODE or x2.dtype != x1.dtype or x1.shape != x2.shape or x1.dim() != 2:
         raise ValueError("x1 and x2 must be 2-D f32 or bf16 tensors of the same shape and type")
@@ -86,7 +109,7 @@ def silu_and_mul(x1: torch.Tensor, x2: torch.Tensor, out: torch.Tensor | None = 
         _lib.check(lib.wb200_silu_and_mul(x1.data_ptr(), x2.data_ptr(), ld(x1), ld(x2), ops._DTYPE_CODE[x1.dtype], rows, n,
                                           out.data_ptr() if out is not None else None, ld(out) if out is not None else n,
                                           q.data_ptr() if quantize else None, s.data_ptr() if quantize else None, None,
-                                          _stream()))
+                                          num_rows.data_ptr() if num_rows is not None else None, _stream()))
     return (out, q, s) if quantize else out
 
 
@@ -167,16 +190,15 @@ class MXFP4ExpertMLP:
         post_pad = torch.empty(1, dtype=torch.int32, device=dev)
         inverse = torch.empty(n, dtype=torch.int32, device=dev)
         moe_align_block_size(ids, self.E, B, sorted_ids, expert_ids, post_pad, inverse)
-        xq, xs, _ = ops.quantize_mxfp4(x, want_packed=False)
+        # Tokens are quantised once and written straight to their sorted rows. Padding rows are never written:
+        # every output row of a GEMM depends on its own input row only, and `combine` reads routed rows only,
+        # so whatever the padding rows hold stays in the padding rows.
         a = torch.empty(cap, self.K // 2, dtype=torch.uint8, device=dev)
         a_s = torch.empty(cap, self.K // 32, dtype=torch.uint8, device=dev)
-        gather_rows(xq, sorted_ids, n, self.top_k, a)      # padding rows (id == n) become zero rows
-        gather_rows(xs, sorted_ids, n, self.top_k, a_s)
+        quantize_scatter(x, inverse, self.top_k, a, a_s)
         h = torch.empty(cap, 2 * self.I, dtype=torch.bfloat16, device=dev)
         moe_scaled_gemm(a, a_s, self.w1, expert_ids, post_pad, h)
-        # row blocks past the padded total are never written by the GEMM: whatever they hold goes through
-        # silu_and_mul and the second GEMM skips them again, and `combine` only reads routed rows
-        _, hq, hs = silu_and_mul(h[:, :self.I], h[:, self.I:], quantize=True)
+        _, hq, hs = silu_and_mul(h[:, :self.I], h[:, self.I:], quantize=True, num_rows=post_pad)
         y = torch.empty(cap, self.w2.N, dtype=torch.bfloat16, device=dev)
         moe_scaled_gemm(hq, hs, self.w2, expert_ids, post_pad, y)
         out = torch.empty(T, self.w2.N, dtype=torch.bfloat16, device=dev)

@@ -103,24 +103,21 @@ def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, devi
     inverse = torch.empty(n, dtype=torch.int32, device=dev)
     moe.moe_align_block_size(ids, experts, B, sorted_ids, expert_ids, post, inverse)
     R = cap  # every buffer has the worst-case row count; the GEMMs skip the row blocks past the padded total
-    xq, xs, _ = ops.quantize_mxfp4(x, want_packed=False)
     a = torch.empty(R, K // 2, dtype=torch.uint8, device=dev)
     a_s = torch.empty(R, K // 32, dtype=torch.uint8, device=dev)
     h = torch.empty(R, 2 * inter, dtype=torch.bfloat16, device=dev)
     y = torch.empty(R, K, dtype=torch.bfloat16, device=dev)
     out = torch.empty(tokens, K, dtype=torch.bfloat16, device=dev)
-    moe.gather_rows(xq, sorted_ids, n, top_k, a)
-    moe.gather_rows(xs, sorted_ids, n, top_k, a_s)
+    moe.quantize_scatter(x, inverse, top_k, a, a_s)
     moe_scaled_gemm(a, a_s, mlp.w1, expert_ids, post, h)
-    _, hq, hs = moe.silu_and_mul(h[:, :inter], h[:, inter:], quantize=True)
+    _, hq, hs = moe.silu_and_mul(h[:, :inter], h[:, inter:], quantize=True, num_rows=post)
     steps = [
         ("moe_align_block_size", lambda: moe.moe_align_block_size(ids, experts, B, sorted_ids, expert_ids, post, inverse), None),
-        ("quantize tokens", lambda: ops.quantize_mxfp4(x, want_packed=False), tokens * K * 2 + tokens * K // 2 + tokens * K // 32),
-        ("gather codes + scales", lambda: (moe.gather_rows(xq, sorted_ids, n, top_k, a), moe.gather_rows(xs, sorted_ids, n, top_k, a_s)),
-         2 * R * (K // 2 + K // 32)),
+        ("quantise tokens into their sorted rows", lambda: moe.quantize_scatter(x, inverse, top_k, a, a_s),
+         tokens * K * 2 + n * (K // 2 + K // 32)),
         ("grouped GEMM gate|up", lambda: moe_scaled_gemm(a, a_s, mlp.w1, expert_ids, post, h), None),
-        ("silu_and_mul + quantise", lambda: moe.silu_and_mul(h[:, :inter], h[:, inter:], quantize=True),
-         R * 2 * inter * 2 + R * inter // 2 + R * inter // 32),
+        ("silu_and_mul + quantise", lambda: moe.silu_and_mul(h[:, :inter], h[:, inter:], quantize=True, num_rows=post),
+         int(post.item()) * (2 * inter * 2 + inter // 2 + inter // 32)),
         ("grouped GEMM down", lambda: moe_scaled_gemm(hq, hs, mlp.w2, expert_ids, post, y), None),
         ("combine", lambda: moe.combine(y, inverse, weight.reshape(-1), top_k, out), R * K * 2 + tokens * K * 2),
         ("whole forward", lambda: mlp(x, logits), None),
