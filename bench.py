@@ -147,6 +147,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="launch every call after the previous one has completed (for comparison)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
@@ -188,6 +189,12 @@ def main():
     dsets = [[t.to(dev, non_blocking=True).clone() for t in host] for _ in range(SETS)]
     outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(SETS)]
     kernel, options = wb.get_tagged_mxfp4_gemm((M, N, K), output_dtype=wb.bf16)
+    # the weights (b, b_scale) are resident and never written inside the loop: consecutive calls may overlap
+    # their tails and heads (programmatic dependent launch, wave_b200's overlap_previous option)
+    # (measured on one box: the decode kernel gains 5 %, 23.7 against 25.0 us; the 8192-cubed kernel gains nothing)
+    options.overlap_previous = M <= 128 and not args.no_overlap
+    if options.overlap_previous:
+        config["overlap"] = "each launch is a programmatic dependent of the one before it (weights are not written in the loop)"
     gemm = wb.wave_compile(wb.set_default_run_config(options), kernel)
     b_packed = [ops.repack_scales(d[3]) for d in dsets]  # weights: packed once, outside the timed region
     torch.cuda.synchronize()
@@ -209,7 +216,11 @@ def main():
             graphed[i % SETS].replay()
 
     def gemm_only(i):
-        ops.scaled_gemm_packed(dsets[i % SETS][0], a_packed[i % SETS], dsets[i % SETS][2], b_packed[i % SETS], outs[i % SETS])
+        ops.scaled_gemm_packed(dsets[i % SETS][0], a_packed[i % SETS], dsets[i % SETS][2], b_packed[i % SETS], outs[i % SETS],
+                               _lib_flags)
+
+    from wave_b200 import _lib as _wb_lib
+    _lib_flags = _wb_lib.OVERLAP_PREVIOUS if options.overlap_previous else 0
 
     def barrier():
         if world > 1:

@@ -56,6 +56,13 @@ extern "C" {
 #define WB200_ACCUMULATE 0x20u    /* c += a * b^T: the split-K templates' contract, which adds into a
                                      caller-initialised c (tagged_mxfp4_gemm.py:780-781, 830-831) */
 
+#define WB200_OVERLAP_PREVIOUS 0x80u /* the caller asserts that b and b_scale_packed are NOT written by the kernel that
+                                     precedes this call in the stream: the GEMM is then launched as a programmatic
+                                     dependent of that kernel, so that its set-up and first weight loads overlap the
+                                     kernel's tail; everything else (a, scales of a, c, workspace) is touched only after
+                                     the preceding kernel has completed. Back-to-back GEMMs of a decode loop overlap
+                                     their tails and heads this way. */
+
 /* Library version (major * 1000 + minor). */
 int wb200_version(void);
 

@@ -748,3 +748,30 @@ def test_split_k_tile_path_refuses_what_it_cannot_do():
     with pytest.raises(RuntimeError):  # plenty of tiles: not a split-K shape
         ops.scaled_gemm_packed(a.to(DEV), ops.repack_scales(a_s.to(DEV)), b.to(DEV), ops.repack_scales(b_s.to(DEV)), c,
                                _lib.PATH_TILE_SPLITK)
+
+
+@pytest.mark.parametrize("shape", [(16, 4096, 2048), (100, 1000, 992), (512, 768, 1024)])
+def test_overlap_previous_chain_gives_the_same_bits(shape):
+    """Back-to-back calls flagged WB200_OVERLAP_PREVIOUS (each launched as a programmatic dependent of the one
+    before it, sharing scratch and workspace) against the same calls launched one after the other."""
+    M, N, K = shape
+    kernel, options = wb.get_tagged_mxfp4_gemm(shape, output_dtype=wb.bf16)
+    plain = wb.wave_compile(wb.set_default_run_config(options), kernel)
+    kernel2, options2 = wb.get_tagged_mxfp4_gemm(shape, output_dtype=wb.bf16)
+    options2.overlap_previous = True
+    chained = wb.wave_compile(wb.set_default_run_config(options2), kernel2)
+    probs = [random_problem(M, N, K, seed=500 + i) for i in range(4)]
+    dev_probs = [[t.to(DEV) for t in p] for p in probs]
+    ref_out = [torch.empty(M, N, dtype=torch.bfloat16, device=DEV) for _ in probs]
+    for p, c in zip(dev_probs, ref_out):
+        plain(p[0], p[1], p[2], p[3], c)
+        torch.cuda.synchronize()
+    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in probs]
+    for rep in range(3):  # no synchronisation between the calls
+        for p, c in zip(dev_probs, outs):
+            chained(p[0], p[1], p[2], p[3], c)
+    torch.cuda.synchronize()
+    for c, r in zip(outs, ref_out):
+        assert torch.equal(c.view(torch.int16), r.view(torch.int16))
+    check_bf16(outs[0], orc.scaled_gemm(*probs[0]))
+    ops.check_device_status()

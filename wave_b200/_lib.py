@@ -32,6 +32,7 @@ PATH_MASK = 0xF
 TILE_N128 = 0x10
 TILE_N192 = 0x40
 ACCUMULATE = 0x20
+OVERLAP_PREVIOUS = 0x80
 E4M3 = 0
 E5M2 = 1
 

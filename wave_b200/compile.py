@@ -70,6 +70,10 @@ class WaveCompileOptions:
     kernel_hash: Optional[str] = None
     # wave_b200 only: force a kernel path (a PATH_* flag of the C ABI), 0 = choose by shape
     kernel_path: int = _lib.PATH_AUTO
+    # wave_b200 only: the caller asserts that b and b_scale are not written by the kernel that precedes the call
+    # in the stream (weights of a layer), so the GEMM may start streaming them while that kernel drains
+    # (WB200_OVERLAP_PREVIOUS: programmatic dependent launch)
+    overlap_previous: bool = False
 
 
 def get_default_arch() -> str:
@@ -206,6 +210,8 @@ class ScaledGemmKernel:
         flags = self.options.kernel_path
         if t.accumulate:
             flags |= _lib.ACCUMULATE
+        if self.options.overlap_previous:
+            flags |= _lib.OVERLAP_PREVIOUS
         plain = type(a_scale) is torch.Tensor and type(b_scale) is torch.Tensor
         if plain:
             self._check_scale(a_scale, M, K, "a_scale")

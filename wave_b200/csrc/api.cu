@@ -122,6 +122,12 @@ CUresult encode_2d(CUtensorMap* map, const MapKey& k) {
   return r;
 }
 
+// True while a launch is to be made a programmatic dependent of the kernel before it in the stream: the GEMM
+// behind the repack kernel of wb200_mxfp4_gemm_repack_a, and every launch of a call flagged
+// WB200_OVERLAP_PREVIOUS. A dependent kernel starts while its predecessor drains and executes
+// griddepcontrol.wait before touching anything but the weights.
+static thread_local bool tl_dependent_launch = false;
+
 // [rows, row_bytes] uint8 matrix (rows pitch_bytes apart; 0 = dense), box = 128 bytes x box_rows, 128-byte swizzle, zero fill.
 int make_operand_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_rows,
                      long long pitch_bytes = 0) {
@@ -200,11 +206,6 @@ int make_output_map(CUtensorMap* map, void* c, int M, int N, long long ldc, int 
 }
 
 // EB: bits per operand element (4: MXFP4, 8: MXFP8 with elem_format 0 = E4M3 / 1 = E5M2).
-// Set by wb200_mxfp4_gemm_repack_a around its GEMM launch: the GEMM is then launched as a programmatic
-// dependent of the repack kernel before it (its set-up and weight loads overlap that kernel; it waits for
-// the kernel's completion before reading the packed scales).
-static thread_local bool tl_dependent_launch = false;
-
 template <int CG, int BN, typename OutT, int EB = 4>
 int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                 const void* bs, void* c, long long ldc, int sfa_row_blocks, int sfb_row_blocks, int accumulate,
@@ -701,9 +702,17 @@ static int repack_scales_impl(const void* src, long long src_row_stride, int row
   if (rc) return rc;
   const int k_atoms = wb::sf_k_atoms(K);
   dim3 grid((k_atoms + 7) / 8, wb::sf_row_blocks(rows));
-  wb::repack_scales_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint8_t*>(src), src_row_stride, rows, K / 32, k_atoms, static_cast<uint8_t*>(dst), broadcast);
-  WB_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tl_dependent_launch ? 1 : 0;
+  WB_CUDA(cudaLaunchKernelEx(&cfg, wb::repack_scales_kernel, static_cast<const uint8_t*>(src), src_row_stride, rows, K / 32,
+                             k_atoms, static_cast<uint8_t*>(dst), broadcast, tl_dependent_launch));
   return WB200_OK;
 }
 
@@ -971,7 +980,14 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   unsigned path = flags & WB200_PATH_MASK;
-  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_TILE_N192 | WB200_ACCUMULATE)) != 0) return fail(WB200_ERR_INVALID_ARG, "unknown flag bits %#x", flags);
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_TILE_N192 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS)) != 0)
+    return fail(WB200_ERR_INVALID_ARG, "unknown flag bits %#x", flags);
+  // restores the previous value on every return path
+  struct DependentScope {
+    bool saved;
+    explicit DependentScope(bool on) : saved(tl_dependent_launch) { if (on) tl_dependent_launch = true; }
+    ~DependentScope() { tl_dependent_launch = saved; }
+  } dependent_scope((flags & WB200_OVERLAP_PREVIOUS) != 0);
   if (path > WB200_PATH_TILE_SPLITK) return fail(WB200_ERR_INVALID_ARG, "unknown path flag %u", path);
   if ((flags & WB200_TILE_N128) && (flags & WB200_TILE_N192)) return fail(WB200_ERR_INVALID_ARG, "two tile widths forced at once");
   const int accumulate = (flags & WB200_ACCUMULATE) ? 1 : 0;
@@ -1034,7 +1050,9 @@ int wb200_mxfp4_gemm_repack_a(int M, int N, int K, const void* a, const void* a_
                               void* a_scale_scratch, const void* b, const void* b_scale_packed, void* c, int c_dtype,
                               long long ldc, void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
   if (!a_scale_scratch) return fail(WB200_ERR_INVALID_ARG, "gemm_repack_a: null scratch for the packed activation scales");
+  tl_dependent_launch = (flags & WB200_OVERLAP_PREVIOUS) != 0;  // the repack kernel itself overlaps the previous kernel's tail
   int rc = wb200_repack_scales(a_scale, a_scale_stride, M, K, a_scale_scratch, stream);
+  tl_dependent_launch = false;
   if (rc) return rc;
   tl_dependent_launch = true;  // the GEMM is the repack kernel's programmatic dependent
   rc = wb200_mxfp4_gemm(M, N, K, a, a_scale_scratch, b, b_scale_packed, c, c_dtype, ldc, workspace, workspace_bytes, flags, stream);

@@ -288,6 +288,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  pdl_launch_dependents();  // a kernel launched behind this one as a programmatic dependent may take SMs as they free up
   const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
   const bool leader = (rank == 0);
 
