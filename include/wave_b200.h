@@ -208,6 +208,12 @@ int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
                      const void* b_scale_packed, void* c, int c_dtype, long long ldc, int elem_format, unsigned flags,
                      void* stream);
 
+/* MXFP8 activation quantiser: as wb200_quantize_mxfp4 with one byte per element (q [rows, K]) of elem_format;
+ * block scale exponent floor(log2(amax)) - 8 (E4M3, largest value 448) or - 15 (E5M2, 57344); values rounded to
+ * nearest even and saturated by the conversion. Not in the reference (its MXFP8 test feeds random values). */
+int wb200_quantize_mxfp8(const void* x, int x_dtype, long long ldx, int rows, int K, int elem_format, void* q,
+                         void* scale_rowmajor, void* scale_packed, void* stream);
+
 /* Allocation-free variant of the skinny (M <= 16) GEMM. No counterpart in the reference.
  *
  * For callers that may not allocate device memory at the point of the call and have no spare buffer

@@ -41,3 +41,21 @@ def torch_scaled_gemm_mxfp8(x, w, x_scales, w_scales) -> torch.Tensor:
     w_f32 = w.to(torch.float32) * e8m0_to_f32(
         w_scales.repeat_interleave(SCALE_GROUP_SIZE, dim=1).to(torch.float32)).T   # :88-90
     return torch.mm(x_f32, w_f32)                                                   # :91
+
+
+def quantize_mxfp8(x: torch.Tensor, dtype=torch.float8_e5m2):
+    """f32 [R, K] -> (f8 [R, K], scales [R, K/32] uint8). Not in the reference (its MXFP8 test feeds random values,
+    tests/kernel/wave_gemm_mxfp_test.py:64-77); the block rule of the MXFP4 harness quantiser carried over:
+    e = floor(log2(amax)) - emax_elem (8 for E4M3, whose largest value is 448 = 1.75 * 2^8; 15 for E5M2, 57344 =
+    1.75 * 2^15), scale byte clamp(e + 127, 0, 254), amax == 0 -> 127; values x * 2^-e clamped to the largest
+    finite value and rounded to nearest even by the type conversion."""
+    R, K = x.shape
+    assert K % SCALE_GROUP_SIZE == 0
+    emax, vmax = (8, 448.0) if dtype == torch.float8_e4m3fn else (15, 57344.0)
+    xb = x.reshape(R, K // 32, 32).to(torch.float32)
+    amax = xb.abs().amax(dim=2)
+    e = torch.floor(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)))) - float(emax)
+    e = torch.where(amax > 0, e, torch.zeros_like(e))
+    sb = torch.clamp(e + 127.0, 0, 254)
+    y = torch.clamp(xb / torch.pow(torch.tensor(2.0), sb - 127.0).unsqueeze(2), -vmax, vmax)
+    return y.reshape(R, K).to(dtype), sb.to(torch.uint8)

@@ -121,3 +121,21 @@ def test_full_size_8192_sampled():
     ops.scaled_gemm_mxfp8_packed(a, ops.repack_scales(a_s), b, ops.repack_scales(b_s), c)
     rows = torch.arange(0, M, 331, device=DEV)
     check(c[rows], a[rows].cpu(), a_s[rows].cpu(), b.cpu(), b_s.cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.float8_e5m2, torch.float8_e4m3fn])
+@pytest.mark.parametrize("rows,K,src", [(64, 256, torch.float32), (300, 1184, torch.bfloat16), (1, 32, torch.float32)])
+def test_quantize_mxfp8_bit_exact_and_feeds_the_gemm(dtype, rows, K, src):
+    g = torch.Generator().manual_seed(rows + K)
+    x = (torch.randn(rows, K, generator=g) * torch.logspace(-6, 6, rows).unsqueeze(1)).to(src)
+    x[0, :32] = 0  # an all-zero block
+    q, s, packed = ops.quantize_mxfp8(x.to(DEV), dtype)
+    q_ref, s_ref = orc8.quantize_mxfp8(x.float(), dtype)
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    assert torch.equal(packed.data.cpu(), orc.pack_scales(s_ref))
+    if rows >= 64:  # the quantised activations against quantised weights through the GEMM
+        w, w_s = orc8.quantize_mxfp8(torch.randn(96, K, generator=g), dtype)
+        c = torch.empty(rows, 96, dtype=torch.float32, device=DEV)
+        ops.scaled_gemm_mxfp8_packed(q, packed, w.to(DEV), ops.repack_scales(w_s.to(DEV)), c)
+        check(c, q_ref, s_ref, w, w_s)

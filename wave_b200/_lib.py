@@ -53,6 +53,7 @@ EXPORTED_SYMBOLS = (
     "wb200_mxfp4_gemm",
     "wb200_mxfp4_gemm_repack_a",
     "wb200_mxfp8_gemm",
+    "wb200_quantize_mxfp8",
     "wb200_mxfp4_gemm_skinny_noalloc",
     "wb200_mxfp4_grouped_gemm",
     "wb200_mxfp4_moe_gemm",
@@ -132,6 +133,8 @@ def load() -> ctypes.CDLL:
     lib.wb200_mxfp8_gemm.restype = c_int
     lib.wb200_mxfp8_gemm.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_ll,
                                      c_int, c_uint, c_void_p]
+    lib.wb200_quantize_mxfp8.restype = c_int
+    lib.wb200_quantize_mxfp8.argtypes = [c_void_p, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.wb200_mxfp4_gemm_skinny_noalloc.restype = c_int
     lib.wb200_mxfp4_gemm_skinny_noalloc.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                     c_int, c_ll, c_uint, c_void_p]

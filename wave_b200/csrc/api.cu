@@ -913,6 +913,41 @@ int wb200_moe_combine(const void* y, long long ldy, int dtype, const int* row_of
   return WB200_OK;
 }
 
+int wb200_quantize_mxfp8(const void* x, int x_dtype, long long ldx, int rows, int K, int elem_format, void* q,
+                         void* scale_rowmajor, void* scale_packed, void* stream) {
+  if (rows <= 0 || K <= 0 || K % 32 != 0)
+    return fail(WB200_ERR_INVALID_ARG, "quantize_mxfp8: rows = %d, K = %d (K must be a positive multiple of 32)", rows, K);
+  if (!x || !q || (!scale_rowmajor && !scale_packed)) return fail(WB200_ERR_INVALID_ARG, "quantize_mxfp8: null pointer");
+  if (x_dtype != WB200_F32 && x_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "quantize_mxfp8: unknown input dtype %d", x_dtype);
+  if (elem_format != WB200_E4M3 && elem_format != WB200_E5M2) return fail(WB200_ERR_INVALID_ARG, "quantize_mxfp8: unknown element format %d", elem_format);
+  if (ldx < K) return fail(WB200_ERR_INVALID_ARG, "quantize_mxfp8: ldx = %lld is smaller than K = %d", ldx, K);
+  const int esz = (x_dtype == WB200_F32) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(q) & 7))
+    return fail(WB200_ERR_ALIGNMENT, "quantize_mxfp8: x rows must be 16-byte aligned and q 8-byte aligned");
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int k_atoms = wb::sf_k_atoms(K);
+  if (scale_packed && (rows % 128 != 0 || (K / 32) % 8 != 0)) {
+    const int rbs = wb::sf_row_blocks(rows);
+    const long long total = (long long)rbs * k_atoms * 512;
+    wb::fill_scale_padding_kernel<<<unsigned((total + 255) / 256), 256, 0, s>>>(static_cast<uint8_t*>(scale_packed), rows,
+                                                                                  K / 32, k_atoms, rbs);
+  }
+  const dim3 blocks(rows, (K / 32 + 63) / 64);
+  if (x_dtype == WB200_F32)
+    wb::quantize_mxfp8_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), ldx, rows, K, elem_format,
+                                                            static_cast<uint8_t*>(q), static_cast<uint8_t*>(scale_rowmajor),
+                                                            static_cast<uint8_t*>(scale_packed), k_atoms);
+  else
+    wb::quantize_mxfp8_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, K, elem_format,
+                                                                    static_cast<uint8_t*>(q), static_cast<uint8_t*>(scale_rowmajor),
+                                                                    static_cast<uint8_t*>(scale_packed), k_atoms);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
 int wb200_moe_quantize_scatter(const void* x, int x_dtype, long long ldx, int tokens, int K, int top_k, const int* dst_rows,
                                void* q, void* scale_rowmajor, void* stream) {
   if (tokens <= 0 || K <= 0 || K % 32 != 0 || top_k <= 0)

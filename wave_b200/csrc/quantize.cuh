@@ -109,6 +109,53 @@ quantize_mxfp4_kernel(const InT* __restrict__ x, long long ldx, int rows, int K,
   mxfp4_encode_group<8>(v, active, r, kb, sub, K, kblocks, k_atoms, q, scale_rm, scale_packed);
 }
 
+// MXFP8 counterpart: f32 or bf16 [rows, K] -> one byte per element (E4M3 when fmt == 0, E5M2 when fmt == 1) plus
+// E8M0 scales, e = floor(log2(amax)) - 8 (E4M3: largest value 448) or - 15 (E5M2: 57344); the rounding and the
+// saturation are the hardware conversion's (cvt.rn.satfinite). Same thread layout as the MXFP4 quantiser.
+__device__ __forceinline__ uint32_t f8x2_code(float lo, float hi, int fmt) {
+  uint16_t r;
+  if (fmt == 0) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return uint32_t(r);
+}
+
+template <typename InT>
+__global__ void __launch_bounds__(256)
+quantize_mxfp8_kernel(const InT* __restrict__ x, long long ldx, int rows, int K, int fmt, uint8_t* __restrict__ q,
+                      uint8_t* __restrict__ scale_rm, uint8_t* __restrict__ scale_packed, int k_atoms) {
+  const int sub = threadIdx.x & 3;
+  const int kblocks = K >> 5;
+  const int r = blockIdx.x;
+  const int kb = blockIdx.y * 64 + (threadIdx.x >> 2);
+  const bool active = r < rows && kb < kblocks;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (active) load8(x + (long long)r * ldx + kb * 32 + sub * 8, v);
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  int sb = 127;
+  if (amax > 0.f) {
+    sb = int((__float_as_uint(amax) >> 23) & 0xff) - (fmt == 0 ? 8 : 15);
+    sb = max(0, min(254, sb));
+  }
+  const int ie = 127 - sb;
+  const float inv = (ie == -127) ? __int_as_float(0x00400000) : __int_as_float((ie + 127) << 23);
+  if (!active) return;
+  uint2 out;
+  out.x = f8x2_code(v[0] * inv, v[1] * inv, fmt) | (f8x2_code(v[2] * inv, v[3] * inv, fmt) << 16);
+  out.y = f8x2_code(v[4] * inv, v[5] * inv, fmt) | (f8x2_code(v[6] * inv, v[7] * inv, fmt) << 16);
+  *reinterpret_cast<uint2*>(q + (long long)r * K + kb * 32 + sub * 8) = out;
+  if (sub == 0) {
+    if (scale_rm) scale_rm[(long long)r * kblocks + kb] = uint8_t(sb);
+    if (scale_packed) {
+      const size_t off = (size_t(r >> 7) * k_atoms + (kb >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (kb & 3);
+      scale_packed[off] = uint8_t(sb);
+    }
+  }
+}
+
 // Quantise-and-scatter for routed tokens: row t of x is quantised once and written to the `copies` output rows
 // dst_rows[t * copies + j] (negative entries are skipped): the tokens of a mixture-of-experts layer go straight
 // to their expert-sorted rows without a separate gather pass. Scales are written row-major.

@@ -167,6 +167,28 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
 _FP8_FORMATS = {torch.float8_e5m2: _lib.E5M2, torch.float8_e4m3fn: _lib.E4M3}
 
 
+def quantize_mxfp8(x: torch.Tensor, dtype: torch.dtype = torch.float8_e5m2, want_rowmajor: bool = True, want_packed: bool = True):
+    """f32 or bf16 [rows, K] -> (f8 [rows, K] of `dtype`, scales [rows, K/32] uint8 or None, PackedScales or None)."""
+    lib = _lib.load()
+    if not x.is_cuda or x.dtype not in _DTYPE_CODE or x.dim() != 2:
+        raise ValueError(f"x must be a 2-D float32 or bfloat16 CUDA tensor, got {x.dtype} {tuple(x.shape)}")
+    if dtype not in _FP8_FORMATS:
+        raise ValueError(f"dtype must be torch.float8_e5m2 or torch.float8_e4m3fn, got {dtype}")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    rows, K = x.shape
+    if K % SCALE_GROUP_SIZE or not (want_rowmajor or want_packed):
+        raise ValueError("K must be a multiple of 32 and at least one scale layout asked for")
+    q = torch.empty(rows, K, dtype=torch.uint8, device=x.device)
+    s_rm = torch.empty(rows, K // SCALE_GROUP_SIZE, dtype=torch.uint8, device=x.device) if want_rowmajor else None
+    s_pk = torch.empty(packed_scale_bytes(rows, K), dtype=torch.uint8, device=x.device) if want_packed else None
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wb200_quantize_mxfp8(x.data_ptr(), _DTYPE_CODE[x.dtype], x.stride(0) if rows > 1 else K, rows, K,
+                                            _FP8_FORMATS[dtype], q.data_ptr(), s_rm.data_ptr() if want_rowmajor else None,
+                                            s_pk.data_ptr() if want_packed else None, _stream()))
+    return q.view(dtype), s_rm, (PackedScales(s_pk, rows, K) if want_packed else None)
+
+
 def scaled_gemm_mxfp8_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_sf: PackedScales, c: torch.Tensor,
                              elem_format: int | None = None, flags: int = 0) -> None:
     """c [M, N] = dequant(a) @ dequant(b)^T for 8-bit operands a [M, K], b [N, K] (torch float8 tensors, or
