@@ -200,13 +200,14 @@ int wb200_mxfp4_gemm_repack_a(int M, int N, int K, const void* a, const void* a_
 /* MXFP8: the same block-scaled GEMM with 8-bit operands, a [M, K] and b [N, K] bytes of E5M2
  * (elem_format WB200_E5M2, what the reference's testScaledGemmMXFP8 feeds,
  * tests/kernel/wave_gemm_mxfp_test.py:64-77, 416-501) or E4M3 (WB200_E4M3), one E8M0 scale per 32
- * elements, scales packed by wb200_repack_scales exactly as for MXFP4. Tile paths only: flags may
- * hold WB200_PATH_AUTO / TILE_1CTA / TILE_2CTA, WB200_TILE_N128 and WB200_ACCUMULATE. */
+ * elements, scales packed by wb200_repack_scales exactly as for MXFP4. flags may hold WB200_PATH_AUTO /
+ * TILE_1CTA / TILE_2CTA / SKINNY, WB200_TILE_N128 and WB200_ACCUMULATE; the skinny path (M <= 128, chosen by
+ * AUTO when a workspace is passed) takes the workspace of wb200_mxfp4_gemm_workspace_bytes(M, N, K). */
 #define WB200_E4M3 0
 #define WB200_E5M2 1
 int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,
-                     const void* b_scale_packed, void* c, int c_dtype, long long ldc, int elem_format, unsigned flags,
-                     void* stream);
+                     const void* b_scale_packed, void* c, int c_dtype, long long ldc, int elem_format, void* workspace,
+                     size_t workspace_bytes, unsigned flags, void* stream);
 
 /* MXFP8 activation quantiser: as wb200_quantize_mxfp4 with one byte per element (q [rows, K]) of elem_format;
  * block scale exponent floor(log2(amax)) - 8 (E4M3, largest value 448) or - 15 (E5M2, 57344); values rounded to

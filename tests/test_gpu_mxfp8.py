@@ -139,3 +139,37 @@ def test_quantize_mxfp8_bit_exact_and_feeds_the_gemm(dtype, rows, K, src):
         c = torch.empty(rows, 96, dtype=torch.float32, device=DEV)
         ops.scaled_gemm_mxfp8_packed(q, packed, w.to(DEV), ops.repack_scales(w_s.to(DEV)), c)
         check(c, q_ref, s_ref, w, w_s)
+
+
+@pytest.mark.parametrize("M", [1, 16, 40, 100, 128])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (1000, 992), (4096, 384)])
+@pytest.mark.parametrize("out_dtype,elem", [(torch.float32, torch.float8_e5m2), (torch.bfloat16, torch.float8_e4m3fn)])
+def test_skinny_path_mxfp8(M, N, K, out_dtype, elem):
+    """M <= 128 with 8-bit operands: the stream-K weight-streaming kernel (chosen automatically, and forced)."""
+    a, a_s, b, b_s = problem(M, N, K, seed=3 * M + N + K, dtype=elem)
+    ad, bd = a.to(DEV), b.to(DEV)
+    asp, bsp = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
+    c = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_mxfp8_packed(ad, asp, bd, bsp, c)
+    check(c, a, a_s, b, b_s)
+    forced = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_mxfp8_packed(ad, asp, bd, bsp, forced, flags=_lib.PATH_SKINNY)
+    assert torch.equal(forced.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32),
+                       c.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32))
+    tiles = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_mxfp8_packed(ad, asp, bd, bsp, tiles, flags=_lib.PATH_TILE_1CTA)
+    check(tiles, a, a_s, b, b_s)
+
+
+def test_decode_shape_mxfp8_sampled():
+    """M = 16, N = 28672, K = 8192 with E4M3 operands (235 MB of weights): column blocks against the oracle."""
+    M, N, K = 16, 28672, 8192
+    g = torch.Generator(device=DEV).manual_seed(9)
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.float8_e4m3fn)
+    b = (torch.randn(N, K, device=DEV, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    a_s = torch.randint(124, 129, (M, K // 32), dtype=torch.uint8, device=DEV, generator=g)
+    b_s = torch.randint(120, 126, (N, K // 32), dtype=torch.uint8, device=DEV, generator=g)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.scaled_gemm_mxfp8_packed(a, ops.repack_scales(a_s), b, ops.repack_scales(b_s), c)
+    for n0 in (0, 14336, N - 1024):
+        check(c[:, n0:n0 + 1024].contiguous(), a.cpu(), a_s.cpu(), b[n0:n0 + 1024].cpu(), b_s[n0:n0 + 1024].cpu())

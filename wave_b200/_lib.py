@@ -132,7 +132,7 @@ def load() -> ctypes.CDLL:
                                               c_void_p, c_int, c_ll, c_void_p, c_size_t, c_uint, c_void_p]
     lib.wb200_mxfp8_gemm.restype = c_int
     lib.wb200_mxfp8_gemm.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_ll,
-                                     c_int, c_uint, c_void_p]
+                                     c_int, c_void_p, c_size_t, c_uint, c_void_p]
     lib.wb200_quantize_mxfp8.restype = c_int
     lib.wb200_quantize_mxfp8.argtypes = [c_void_p, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.wb200_mxfp4_gemm_skinny_noalloc.restype = c_int

@@ -551,18 +551,20 @@ size_t skinny_workspace_bytes(int sm_count, int M) {
   return kCounterBytes + size_t(2) * sm_count * M * 128 * sizeof(float);
 }
 
-template <int NP, int STAGES, typename OutT>
+template <int NP, int STAGES, typename OutT, int EB = 4>
 int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
-                  const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream) {
-  using Cfg = wb::SkinnyCfg<NP, STAGES>;
+                  const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream,
+                  int elem_format = 0) {
+  using Cfg = wb::SkinnyCfg<NP, STAGES, EB>;
   CUtensorMap tmW, tmX, tmSFW, tmSFX;
-  int rc = make_operand_map(&tmW, b, N, K / 2, 128);
+  const long long row_bytes = (long long)K * EB / 8;
+  int rc = make_operand_map(&tmW, b, N, row_bytes, 128);
   if (rc) return rc;
-  rc = make_operand_map(&tmX, a, M, K / 2, NP);
+  rc = make_operand_map(&tmX, a, M, row_bytes, NP);
   if (rc) return rc;
-  rc = make_scale_map(&tmSFW, bs, wb::sf_row_blocks(N), wb::sf_k_atoms(K), 1);
+  rc = make_scale_map(&tmSFW, bs, wb::sf_row_blocks(N), wb::sf_k_atoms(K), 1, Cfg::SF_ATOMS);
   if (rc) return rc;
-  rc = make_scale_map(&tmSFX, as, 1, wb::sf_k_atoms(K), 1);
+  rc = make_scale_map(&tmSFX, as, 1, wb::sf_k_atoms(K), 1, Cfg::SF_ATOMS);
   if (rc) return rc;
   wb::SkinnyParams p;
   p.c = c;
@@ -571,11 +573,12 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   p.M = M; p.N = N; p.K = K;
   p.ldc = int(ldc);
   p.tiles_n = (N + 127) / 128;
-  p.num_kb = (K + 255) / 256;
+  p.num_kb = (K + Cfg::BK - 1) / Cfg::BK;
   p.accumulate = accumulate;
   p.dependent = tl_dependent_launch ? 1 : 0;
+  p.elem_format = elem_format;
   p.status = dev.status_ptr;
-  auto kernel = wb::mxfp4_skinny_kernel<NP, STAGES, OutT>;
+  auto kernel = wb::mxfp4_skinny_kernel<NP, STAGES, OutT, EB>;
   static bool smem_set[kMaxDevices] = {};
   rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
   if (rc) return rc;
@@ -596,13 +599,14 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   return WB200_OK;
 }
 
-template <typename OutT>
+template <typename OutT, int EB = 4>
 int dispatch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
-                    const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream) {
-  if (M <= 16) return launch_skinny<16, 10, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
-  if (M <= 32) return launch_skinny<32, 9, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
-  if (M <= 64) return launch_skinny<64, 8, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
-  return launch_skinny<128, 6, OutT>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream);
+                    const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream,
+                    int elem_format = 0) {
+  if (M <= 16) return launch_skinny<16, 10, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+  if (M <= 32) return launch_skinny<32, 9, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+  if (M <= 64) return launch_skinny<64, 8, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+  return launch_skinny<128, 6, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1108,8 +1112,8 @@ static int launch_mxfp8(int c_dtype, const DeviceInfo& dev, int M, int N, int K,
 }  // extern "C++"
 
 int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,
-                     const void* b_scale_packed, void* c, int c_dtype, long long ldc, int elem_format, unsigned flags,
-                     void* stream) {
+                     const void* b_scale_packed, void* c, int c_dtype, long long ldc, int elem_format, void* workspace,
+                     size_t workspace_bytes, unsigned flags, void* stream) {
   int rc = check_common(M, N, K, a, a_scale_packed, b, b_scale_packed, c, c_dtype, ldc);
   if (rc) return rc;
   if (elem_format != WB200_E4M3 && elem_format != WB200_E5M2)
@@ -1117,14 +1121,26 @@ int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE)) != 0)
     return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown flag bits %#x", flags);
   unsigned path = flags & WB200_PATH_MASK;
-  if (path == WB200_PATH_SKINNY || path > WB200_PATH_SKINNY)
-    return fail(WB200_ERR_UNSUPPORTED, "mxfp8_gemm runs on the tile paths only (path flag %u)", path);
+  if (path > WB200_PATH_SKINNY)
+    return fail(WB200_ERR_UNSUPPORTED, "mxfp8_gemm has the tile paths and the skinny path (path flag %u)", path);
   DeviceInfo* dev;
   rc = get_device(&dev);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int accumulate = (flags & WB200_ACCUMULATE) ? 1 : 0;
-  if (path == WB200_PATH_AUTO) path = (M > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
+  const bool ws_ok = workspace && workspace_bytes >= skinny_workspace_bytes(dev->sm_count, M) &&
+                     (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
+  if (path == WB200_PATH_AUTO) path = (M <= 128 && ws_ok) ? WB200_PATH_SKINNY : (M > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
+  if (path == WB200_PATH_SKINNY) {
+    if (M > 128) return fail(WB200_ERR_UNSUPPORTED, "the skinny path handles M <= 128 (got %d)", M);
+    if (N > 4096 * 128) return fail(WB200_ERR_UNSUPPORTED, "the skinny path handles N <= 524288 (got %d)", N);
+    if (!ws_ok)
+      return fail(WB200_ERR_WORKSPACE, "the skinny path needs a 16-byte aligned workspace of %zu bytes (got %zu)",
+                  skinny_workspace_bytes(dev->sm_count, M), workspace ? workspace_bytes : size_t(0));
+    if (c_dtype == WB200_F32)
+      return dispatch_skinny<float, 8>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, accumulate, s, elem_format);
+    return dispatch_skinny<__nv_bfloat16, 8>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, workspace, accumulate, s, elem_format);
+  }
   bool n128 = (flags & WB200_TILE_N128) != 0;
   if (!n128 && (flags & WB200_PATH_MASK) == WB200_PATH_AUTO)
     n128 = (long long)((M + 127) / 128) * ((N + 255) / 256) < dev->sm_count;

@@ -23,14 +23,18 @@
 
 namespace wb {
 
-template <int NP_, int STAGES_>
+// EB: bits per operand element, 4 (MXFP4) or 8 (MXFP8); a stage is one 128-byte swizzle row of every operand row
+// either way: 256 or 128 K elements, 2 or 1 scale-factor atoms per 128 rows.
+template <int NP_, int STAGES_, int EB = 4>
 struct SkinnyCfg {
+  static_assert(EB == 4 || EB == 8, "operand elements are 4 or 8 bits");
   static constexpr int NP = NP_;  // padded M = MMA N
   static constexpr int STAGES = STAGES_;
-  static constexpr int BK = 256;
+  static constexpr int BK = 1024 / EB;
+  static constexpr int SF_ATOMS = BK / 128;
   static constexpr int W_BYTES = 128 * 128;
   static constexpr int X_BYTES = NP * 128;
-  static constexpr int SF_BYTES = 1024;
+  static constexpr int SF_BYTES = SF_ATOMS * 512;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;
   static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 64;
@@ -53,6 +57,7 @@ struct SkinnyParams {
   int num_kb;    // ceil(K / 256)
   int accumulate;  // add to the values already in C instead of overwriting them
   int dependent;   // launched as the programmatic dependent of the kernel that writes the activations' packed scales
+  int elem_format; // 8-bit operands only: 0 = E4M3, 1 = E5M2
   int* status;
 };
 
@@ -72,12 +77,12 @@ __device__ __forceinline__ int skinny_owner(long long total, int g, int u) {
   return c;
 }
 
-template <int NP, int STAGES, typename OutT>
+template <int NP, int STAGES, typename OutT, int EB = 4>
 __global__ void __launch_bounds__(192, 1)
 mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmSFW, const __grid_constant__ CUtensorMap tmSFX,
                     const SkinnyParams p) {
-  using Cfg = SkinnyCfg<NP, STAGES>;
+  using Cfg = SkinnyCfg<NP, STAGES, EB>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -149,11 +154,11 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (part != 1) mbar_expect_tx(fb, Cfg::STAGE_BYTES);
         if (part != 2) {
           tma_load_2d_hint(sW, &tmW, p_kb * 128, p_tile * 128, fb, stream_policy);
-          tma_load_2d(sSFW, &tmSFW, p_kb * 256, p_tile, fb);
+          tma_load_2d(sSFW, &tmSFW, p_kb * (Cfg::SF_ATOMS * 128), p_tile, fb);
         }
         if (part != 1) {
           tma_load_2d_hint(sX, &tmX, p_kb * 128, 0, fb, keep_policy);
-          tma_load_2d(sSFX, &tmSFX, p_kb * 256, 0, fb);
+          tma_load_2d(sSFX, &tmSFX, p_kb * (Cfg::SF_ATOMS * 128), 0, fb);
         }
       }
       __syncwarp();
@@ -198,7 +203,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     produce(0x7fffffff, true, 0);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = make_idesc_mxf4(128, NP);
+    const uint32_t idesc = (EB == 4) ? make_idesc_mxf4(128, NP) : make_idesc_mxf8(128, NP, uint32_t(p.elem_format));
     uint32_t stage = 0, phase = 0, sf_set = 0;
     for (int seg = 0; seg < nseg; ++seg) {
       int tile, kbs, kbe;
@@ -224,15 +229,19 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         const uint64_t sfx_desc = make_desc_sf_atom(sSFX);
         if (elect_one()) {
 #pragma unroll
-          for (int a = 0; a < 2; ++a) {
+          for (int a = 0; a < Cfg::SF_ATOMS; ++a) {
             utccp_sf_atom<1>(t_sfw + a * 4, sfw_desc + uint64_t(a * 32));
             utccp_sf_atom<1>(t_sfx + a * 4, sfx_desc + uint64_t(a * 32));
           }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            mma_mxf4<1>(d_tmem, w_desc + uint64_t(k * 2), x_desc + uint64_t(k * 2),
-                        idesc_with_sf_id(idesc, (k & 1) * 2), t_sfw + (k >> 1) * 4, t_sfx + (k >> 1) * 4,
-                        (kb > kbs || k > 0) ? 1u : 0u);
+            if constexpr (EB == 4)
+              mma_mxf4<1>(d_tmem, w_desc + uint64_t(k * 2), x_desc + uint64_t(k * 2),
+                          idesc_with_sf_id(idesc, (k & 1) * 2), t_sfw + (k >> 1) * 4, t_sfx + (k >> 1) * 4,
+                          (kb > kbs || k > 0) ? 1u : 0u);
+            else  // 32 8-bit values per instruction, one scale each: byte k of the atom's column
+              mma_mxf8<1>(d_tmem, w_desc + uint64_t(k * 2), x_desc + uint64_t(k * 2), idesc_with_sf_id(idesc, k), t_sfw,
+                          t_sfx, (kb > kbs || k > 0) ? 1u : 0u);
           }
           tc_commit<1>(empty_bar(stage));
           if (kb == kbe - 1) tc_commit<1>(acc_full_bar(as));

@@ -207,10 +207,14 @@ def scaled_gemm_mxfp8_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tenso
         raise ValueError("operand and scale shapes do not agree")
     if c.dtype not in _DTYPE_CODE or tuple(c.shape) != (M, N) or c.stride(1) != 1:
         raise ValueError(f"c must be f32 or bf16 [{M}, {N}] with unit column stride")
+    ws_ptr = ws_bytes = 0
+    if M <= 128:  # the skinny stream-K path needs its workspace
+        ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
+        ws_ptr = _workspace(a.device, ws_bytes).data_ptr()
     with torch.cuda.device(a.device):
         _lib.check(lib.wb200_mxfp8_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
-                                        c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0) if M > 1 else N, elem_format, flags,
-                                        _stream()))
+                                        c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0) if M > 1 else N, elem_format, ws_ptr,
+                                        ws_bytes, flags, _stream()))
 
 
 class WeightScaleCache:
