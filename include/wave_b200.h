@@ -201,7 +201,7 @@ int wb200_mxfp4_gemm_repack_a(int M, int N, int K, const void* a, const void* a_
  * (elem_format WB200_E5M2, what the reference's testScaledGemmMXFP8 feeds,
  * tests/kernel/wave_gemm_mxfp_test.py:64-77, 416-501) or E4M3 (WB200_E4M3), one E8M0 scale per 32
  * elements, scales packed by wb200_repack_scales exactly as for MXFP4. flags may hold WB200_PATH_AUTO /
- * TILE_1CTA / TILE_2CTA / SKINNY, WB200_TILE_N128 and WB200_ACCUMULATE; the skinny path (M <= 128, chosen by
+ * TILE_1CTA / TILE_2CTA / SKINNY, WB200_TILE_N128, WB200_ACCUMULATE and WB200_OVERLAP_PREVIOUS; the skinny path (M <= 128, chosen by
  * AUTO when a workspace is passed) takes the workspace of wb200_mxfp4_gemm_workspace_bytes(M, N, K). */
 #define WB200_E4M3 0
 #define WB200_E5M2 1

@@ -173,3 +173,21 @@ def test_decode_shape_mxfp8_sampled():
     ops.scaled_gemm_mxfp8_packed(a, ops.repack_scales(a_s), b, ops.repack_scales(b_s), c)
     for n0 in (0, 14336, N - 1024):
         check(c[:, n0:n0 + 1024].contiguous(), a.cpu(), a_s.cpu(), b[n0:n0 + 1024].cpu(), b_s[n0:n0 + 1024].cpu())
+
+
+def test_overlapped_chain_of_mxfp8_decode_calls_gives_the_same_bits():
+    M, N, K = 16, 4096, 2048
+    probs = [problem(M, N, K, seed=900 + i, dtype=torch.float8_e4m3fn) for i in range(3)]
+    dev = [(a.to(DEV), ops.repack_scales(a_s.to(DEV)), b.to(DEV), ops.repack_scales(b_s.to(DEV))) for a, a_s, b, b_s in probs]
+    ref = [torch.empty(M, N, dtype=torch.bfloat16, device=DEV) for _ in probs]
+    for p, c in zip(dev, ref):
+        ops.scaled_gemm_mxfp8_packed(*p, c)
+        torch.cuda.synchronize()
+    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in probs]
+    for _ in range(3):
+        for p, c in zip(dev, outs):
+            ops.scaled_gemm_mxfp8_packed(*p, c, flags=_lib.OVERLAP_PREVIOUS)
+    torch.cuda.synchronize()
+    for c, r in zip(outs, ref):
+        assert torch.equal(c.view(torch.int16), r.view(torch.int16))
+    ops.check_device_status()

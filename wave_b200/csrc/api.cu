@@ -1118,8 +1118,13 @@ int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   if (rc) return rc;
   if (elem_format != WB200_E4M3 && elem_format != WB200_E5M2)
     return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown element format %d", elem_format);
-  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE)) != 0)
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS)) != 0)
     return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown flag bits %#x", flags);
+  struct DependentScope {  // restores the previous value on every return path
+    bool saved;
+    explicit DependentScope(bool on) : saved(tl_dependent_launch) { if (on) tl_dependent_launch = true; }
+    ~DependentScope() { tl_dependent_launch = saved; }
+  } dependent_scope((flags & WB200_OVERLAP_PREVIOUS) != 0);
   unsigned path = flags & WB200_PATH_MASK;
   if (path > WB200_PATH_SKINNY)
     return fail(WB200_ERR_UNSUPPORTED, "mxfp8_gemm has the tile paths and the skinny path (path flag %u)", path);
