@@ -145,6 +145,52 @@ def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, devi
     return rows
 
 
+def time_mxfp8(iters=20, device="cuda:0"):
+    """MXFP8 (E4M3 operands, E8M0 block scales, bf16 output): large tile shapes and the decode shapes, three rotating
+    operand sets (> L2 for the decode shapes), launches replayed from a CUDA graph."""
+    from . import ops
+    rows = []
+    shapes = [(8192, 8192, 8192), (4096, 4096, 4096), (8192, 8192, 16000)] + [(M, 28672, 8192) for M in (1, 16, 64, 128)]
+    for M, N, K in shapes:
+        g = torch.Generator(device=device).manual_seed(1)
+        sets = []
+        for _ in range(3):
+            a = torch.randn(M, K, device=device, generator=g).to(torch.float8_e4m3fn)
+            b = torch.randn(N, K, device=device, generator=g).to(torch.float8_e4m3fn)
+            a_sf = ops.repack_scales(torch.randint(124, 128, (M, K // 32), dtype=torch.uint8, device=device, generator=g))
+            b_sf = ops.repack_scales(torch.randint(124, 128, (N, K // 32), dtype=torch.uint8, device=device, generator=g))
+            sets.append((a, a_sf, b, b_sf, torch.empty(M, N, dtype=torch.bfloat16, device=device)))
+        for st in sets:
+            ops.scaled_gemm_mxfp8_packed(*st)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for st in sets:
+                ops.scaled_gemm_mxfp8_packed(*st)
+        graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        reps = max(iters // 3, int(20.0 / max(e0.elapsed_time(e1), 1e-3)))  # ~20 ms of warm-up, then ~20 ms timed
+        for _ in range(reps):
+            graph.replay()
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (3 * reps)
+        nbytes = M * K + M * K // 32 + N * K + N * K // 32 + M * N * 2
+        rows.append({"M": M, "N": N, "K": K, "runtime_us": round(us, 1), "tflops": round(runtime_us_to_tflops(M, N, K, us), 1),
+                     "gbytes_per_s": round(nbytes / us / 1e3, 1)})
+        print(rows[-1], flush=True)
+        del sets, graph
+    ops.check_device_status()
+    return rows
+
+
 def compare_cublaslt(shapes=((8192, 8192, 8192), (4096, 4096, 4096), (2048, 8192, 8192), (16384, 16384, 16384)), iters=20,
                      device="cuda:0"):
     """Context only, never a product path: the vendor library's block-scaled FP4 GEMM (cuBLASLt through
@@ -264,12 +310,16 @@ def main(argv=None):
     ap.add_argument("--validate", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--mxfp8", action="store_true", help="time the MXFP8 GEMM (tile shapes and decode shapes)")
     ap.add_argument("--compare-cublaslt", action="store_true", help="context: time cuBLASLt's block-scaled FP4 GEMM on the same operands")
     ap.add_argument("--k-sharded", action="store_true", help="under torchrun: time the K-sharded GEMM against GEMM + NCCL reduce-scatter")
     ap.add_argument("--moe", action="store_true", help="time the steps of the MXFP4 expert MLP instead of the shape sweep")
     args = ap.parse_args(argv)
     if args.moe:
         time_moe(iters=args.iters)
+        return
+    if args.mxfp8:
+        time_mxfp8(iters=args.iters)
         return
     if args.compare_cublaslt:
         compare_cublaslt(iters=args.iters)
