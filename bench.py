@@ -36,7 +36,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu
 # capture (profiles/), scaled to the full workload where the capture ran a smaller case.
-NCU_TRAFFIC_BYTES = {"c2": 201.6e6, "c3": 129.5e6}
+NCU_TRAFFIC_BYTES = {"c2": 201.6e6, "c3": 130.7e6}
 
 WORKLOADS = {
     "c2": dict(M=8192, N=8192, K=8192, std_b=1.0, seed_a=1002, seed_b=2002,
