@@ -130,6 +130,53 @@ def pack_scales(scale: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------------------------
+# The reference's AMD pre-shuffles, stated as index maps (mxfp_utils.py:98-128). The B200 kernels do not use
+# these layouts; they are restated so that data a caller holds in them can be recognised and undone.
+# ---------------------------------------------------------------------------------------------
+def amd_e8m0_shuffle(scale: torch.Tensor) -> torch.Tensor:
+    """wave_lang/kernel/wave/utils/mxfp_utils.py:113-128. The scale matrix, zero-padded to multiples of
+    (256, 8), is read as [R, 2, 16, C, 2, 4] (row = 32 R + 16 h + l, column = 8 C + 4 g + e) and written out in the
+    order [R, C, e, l, g, h]; the result is clipped back to the input shape."""
+    s = scale.numpy()
+    m, n = s.shape
+    sm, sn = (m + 255) // 256 * 256, (n + 7) // 8 * 8
+    src = np.zeros((sm, sn), dtype=s.dtype)
+    src[:m, :n] = s
+    flat = np.empty(sm * sn, dtype=s.dtype)
+    r, c = np.divmod(np.arange(sm * sn), sn)
+    R, h, l = r // 32, (r // 16) % 2, r % 16
+    C, g, e = c // 8, (c // 4) % 2, c % 4
+    dst = ((((R * (sn // 8) + C) * 4 + e) * 16 + l) * 2 + g) * 2 + h
+    flat[dst] = src.reshape(-1)
+    return torch.from_numpy(np.ascontiguousarray(flat.reshape(sm, sn)[:m, :n]))
+
+
+def amd_b_preshuffle(b: torch.Tensor) -> torch.Tensor:
+    """wave_lang/kernel/wave/utils/mxfp_utils.py:98-110. Inside every 16-row x 32-byte tile the bytes move from
+    [row, half, byte] order to [half, row, byte] order (half = which 16 bytes of the 32)."""
+    x = b.numpy()
+    N, kp = x.shape
+    r, c = np.divmod(np.arange(N * kp), kp)
+    tile_r, row = r // 16, r % 16
+    tile_c, half, byte = c // 32, (c // 16) % 2, c % 16
+    dst = (((tile_r * (kp // 32) + tile_c) * 2 + half) * 16 + row) * 16 + byte
+    flat = np.empty(N * kp, dtype=x.dtype)
+    flat[dst] = x.reshape(-1)
+    return torch.from_numpy(flat.reshape(N, kp))
+
+
+def amd_b_unshuffle(b_shuffled: torch.Tensor) -> torch.Tensor:
+    """Inverse of amd_b_preshuffle: the row-major [N, K/2] bytes the B200 kernels read."""
+    x = b_shuffled.numpy()
+    N, kp = x.shape
+    r, c = np.divmod(np.arange(N * kp), kp)
+    tile_r, row = r // 16, r % 16
+    tile_c, half, byte = c // 32, (c // 16) % 2, c % 16
+    src = (((tile_r * (kp // 32) + tile_c) * 2 + half) * 16 + row) * 16 + byte
+    return torch.from_numpy(np.ascontiguousarray(x.reshape(-1)[src].reshape(N, kp)))
+
+
+# ---------------------------------------------------------------------------------------------
 # Harness quantiser (not in the reference, which only feeds random codes): f32 -> MXFP4
 # ---------------------------------------------------------------------------------------------
 def quantize_mxfp4(x: torch.Tensor):

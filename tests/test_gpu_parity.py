@@ -319,10 +319,11 @@ def test_noncontiguous_inputs_are_copied():
 # ---------------------------------------------------------------------------------------------
 # full-size configurations: sampled oracle rows plus size-independent properties
 # ---------------------------------------------------------------------------------------------
-def test_config2_8192_cubed_bf16_sampled_rows_and_scaling_property():
-    """M = N = K = 8192, operands quantised from N(0, 1), bf16 output. The oracle is evaluated for 64
-    sampled rows of A against all of B; the whole output is checked through an exact property:
-    raising every A scale by one doubles C bit for bit (power-of-two scaling is exact)."""
+def test_config2_8192_cubed_bf16_whole_matrix_and_scaling_property():
+    """M = N = K = 8192, operands quantised from N(0, 1), bf16 output. The whole output is compared with the
+    oracle, 512 rows of A at a time (the reference's tests compare whole outputs too,
+    tests/kernel/wave_gemm_mxfp_test.py:184-201), and through an exact property: raising every A scale by one
+    doubles C bit for bit (power-of-two scaling is exact)."""
     M = N = K = 8192
     a, a_s, b, b_s = quantized_problem(M, N, K, 1002, 2002)
     ad, asd, bd, bsd = a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV)
@@ -330,9 +331,12 @@ def test_config2_8192_cubed_bf16_sampled_rows_and_scaling_property():
     gemm = wb.wave_compile(options, kernel)
     c = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     gemm(ad, asd, bd, bsd, c)
-    rows = torch.arange(0, M, 128) + torch.arange(64).remainder(128)
-    ref = orc.scaled_gemm(a[rows], a_s[rows], b, b_s)
-    check_bf16(c[rows.to(DEV)], ref)
+    c_host = c.cpu()
+    b_deq = orc.dequant_mxfp4(b, b_s)  # once: 256 MB of f32
+    for r0 in range(0, M, 512):
+        ref = orc.dequant_mxfp4(a[r0:r0 + 512], a_s[r0:r0 + 512]) @ b_deq.T
+        check_bf16(c_host[r0:r0 + 512], ref)
+    del b_deq
     c2 = torch.empty_like(c)
     gemm(ad, asd + 1, bd, bsd, c2)
     assert torch.equal((c.float() * 2).to(torch.bfloat16), c2)
@@ -355,9 +359,62 @@ def test_config3_decode_shapes_bf16(M):
     a, a_s, b, b_s = _config3_operands()
     a, a_s = a[:M].contiguous(), a_s[:M].contiguous()
     c = run(a, a_s, b, b_s, torch.bfloat16)
-    for n0 in (0, 12288, N - 2048):
+    # every column block at M = 16 (the shape the bandwidth target is quoted on), three of them otherwise
+    blocks = range(0, N, 2048) if M == 16 else (0, 12288, N - 2048)
+    for n0 in blocks:
         ref = orc.scaled_gemm(a, a_s, b[n0:n0 + 2048], b_s[n0:n0 + 2048])
         check_bf16(c[:, n0:n0 + 2048].contiguous(), ref)
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("M,N,K,out_dtype,accumulate", [
+    (16, 28672, 2048, torch.bfloat16, False),   # one static round, 76 dealt tiles in main / closer parts
+    (16, 28672 + 72, 1024, torch.float32, False),  # ragged last tile among the dealt ones
+    (100, 19200, 1536, torch.bfloat16, False),  # 150 tiles: 2 dealt tiles only
+    (4, 18944, 512, torch.float32, True),       # a whole number of rounds; accumulate into c
+    (16, 38000, 256, torch.bfloat16, False),    # one K block per tile: nothing to cut
+])
+def test_skinny_path_with_dealt_parts(M, N, K, out_dtype, accumulate):
+    """Shapes with at least as many N tiles as SMs: whole static tiles plus main / closer parts taken from the
+    atomic work list, whoever arrives last at a tile adding the parts. Checked against the oracle; and because
+    which CTA computes which part varies from run to run while the parts and their order do not, repeated
+    launches must give the same bits."""
+    a, a_s, b, b_s = random_problem(M, N, K, seed=M + N + K, lo=124, hi=128)
+    ref = orc.scaled_gemm(a, a_s, b, b_s)
+    ad, bd = a.to(DEV), b.to(DEV)
+    a_sf, b_sf = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
+    flags = _lib.PATH_SKINNY | (_lib.ACCUMULATE if accumulate else 0)
+    outs = []
+    for _ in range(4):
+        c = torch.full((M, N), 1.0 if accumulate else float("nan"), dtype=out_dtype, device=DEV)
+        ops.scaled_gemm_packed(ad, a_sf, bd, b_sf, c, flags)
+        outs.append(c)
+    check(outs[0], a, a_s, b, b_s, ref + 1.0 if accumulate else ref)
+    bits = torch.int16 if out_dtype == torch.bfloat16 else torch.int32
+    for c in outs[1:]:
+        assert torch.equal(outs[0].view(bits), c.view(bits))
+
+
+def test_two_streams_run_skinny_gemms_at_the_same_time():
+    """Two decode-shaped GEMMs launched on two streams with nothing ordering them: each call gets its own
+    workspace (counters and partial tiles belong to one running GEMM), so both match the oracle however the
+    GPU interleaves them."""
+    M, N, K = 16, 20480, 1024
+    probs = [random_problem(M, N, K, seed=s, lo=124, hi=128) for s in (11, 12)]
+    refs = [orc.scaled_gemm(*p) for p in probs]
+    kernel, options = wb.get_tagged_mxfp4_gemm((M, N, K), output_dtype=wb.bf16)
+    gemm = wb.wave_compile(options, kernel)  # ONE kernel object, used from both streams
+    dev = [[t.to(DEV) for t in p] for p in probs]
+    outs = [torch.empty(M, N, dtype=torch.bfloat16, device=DEV) for _ in probs]
+    streams = [torch.cuda.Stream(DEV) for _ in probs]
+    torch.cuda.synchronize()
+    for rep in range(20):
+        for i, st in enumerate(streams):
+            with torch.cuda.stream(st):
+                gemm(*dev[i], outs[i])
+    torch.cuda.synchronize()
+    for i in range(2):
+        check_bf16(outs[i], refs[i])
     ops.check_device_status()
 
 

@@ -147,3 +147,4 @@ def test_perf_formulas_match_the_reference_benchmark_driver():
     assert abs(perf.runtime_us_to_tflops(8192, 8192, 8192, 122.17) - 9000) < 1
     shapes = perf.default_shapes()
     assert (8192, 8192, 8192) in shapes and all(k % 32 == 0 for _, _, k in shapes)
+

@@ -153,3 +153,17 @@ def test_mxfp8_oracle_matches_reference_outputs():
     torch.set_num_threads(1)
     out = mxfp8_oracle.torch_scaled_gemm_mxfp8(x, w, xs, ws)
     assert np.array_equal(out.numpy(), g["out"])
+
+
+def test_amd_preshuffle_index_maps_match_reference_outputs():
+    """The reference's AMD scale and B pre-shuffles (mxfp_utils.py:98-128), restated as index maps, against the
+    outputs the reference itself produced (tests/golden/preshuffle.npz, written by make_golden.py)."""
+    g = np.load(GOLDEN / "preshuffle.npz")
+    scale, b = torch.from_numpy(g["scale"]), torch.from_numpy(g["b"])
+    assert torch.equal(orc.amd_e8m0_shuffle(scale), torch.from_numpy(g["scale_shuffled"]))
+    assert torch.equal(orc.amd_b_preshuffle(b), torch.from_numpy(g["b_shuffled"]))
+    # a caller who holds weights in the reference's pre-shuffled order gets the row-major bytes back
+    assert torch.equal(orc.amd_b_unshuffle(torch.from_numpy(g["b_shuffled"])), b)
+    # on aligned shapes the scale shuffle is a permutation
+    s2 = torch.randint(0, 255, (512, 64), dtype=torch.uint8, generator=torch.Generator().manual_seed(3))
+    assert sorted(orc.amd_e8m0_shuffle(s2).reshape(-1).tolist()) == sorted(s2.reshape(-1).tolist())

@@ -114,6 +114,7 @@ class ScaledGemmKernel:
         self.asm = ""  # the reference exposes generated code here; nothing is generated at run time
         self._weight_scales = ops.WeightScaleCache()
         self._a_scale_buf: dict[int, torch.Tensor] = {}
+        self._workspaces = ops.WorkspacePool()  # this object's own: calls through another object may overlap with these
         self._plans: dict = {}
         self._lib = _lib.load()
         self._static = None
@@ -128,9 +129,10 @@ class ScaledGemmKernel:
         # Fast path: plain tensors whose (shape, dtype, stride, device) signature was validated before.
         # The signature check is what stands between the caller and the C ABI on every call, so it is
         # done once per distinct signature and remembered.
-        if type(a_scale) is torch.Tensor and type(b_scale) is torch.Tensor:
+        if type(a_scale) is torch.Tensor and type(b_scale) is torch.Tensor and a.is_cuda:
+            # (the stream is part of the signature: the plan holds a workspace, and calls on different streams may overlap)
             sig = (a.shape, a.stride(), a.dtype, a_scale.shape, a_scale.stride(), b.shape, b.stride(), b_scale.shape,
-                   c.shape, c.stride(), c.dtype, a.device)
+                   c.shape, c.stride(), c.dtype, a.device, torch.cuda.current_stream(a.device).cuda_stream)
             plan = self._plans.get(sig)
             if plan is not None:
                 return self._launch(plan, a, a_scale, b, b_scale, c)
@@ -223,13 +225,13 @@ class ScaledGemmKernel:
             ws = None  # the plan keeps the workspace tensor alive: it holds its address
             ws_bytes = int(self._lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
             if ws_bytes:
-                ws = ops._workspace(a.device, ws_bytes)
+                ws = ops._workspace(a.device, ws_bytes, "skinny" if M <= 128 else "splitk", self._workspaces)
                 ws_ptr = ws.data_ptr()
             idx = a.device.index if a.device.index is not None else torch.cuda.current_device()
             a_buf = self._a_scale_buffer(a.device, M, K)
             plan = (M, N, K, a_buf, ws_ptr, ws_bytes, flags, ops._DTYPE_CODE[c.dtype], idx, ws)
             sig = (a.shape, a.stride(), a.dtype, a_scale.shape, a_scale.stride(), b.shape, b.stride(), b_scale.shape,
-                   c.shape, c.stride(), c.dtype, a.device)
+                   c.shape, c.stride(), c.dtype, a.device, torch.cuda.current_stream(a.device).cuda_stream)
             self._plans[sig] = plan
             return self._launch(plan, a, a_scale, b, b_scale, c)
         a_sf = self._pack_activation_scales(a_scale, M, K)

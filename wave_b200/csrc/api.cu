@@ -996,10 +996,24 @@ int wb200_mxfp4_dequant(const void* q, const void* scale, int rows, int K, float
 
 size_t wb200_mxfp4_gemm_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  // 148 SMs on B200; the skinny path's buffer is sized for up to 160 so that it fits any sm_100 part.
+  // The skinny path's buffer is sized for up to 160 SMs so that it fits any sm_100 part. The split-K slice count
+  // depends on the SM count: take the largest need over the current device's count, when there is one, and the
+  // counts of the sm_100 parts, so that the size serves whichever of them runs the call.
   if (M <= 128) return skinny_workspace_bytes(160, M);
-  const int slices = splitk_slices(148, M, N, K);
-  return slices ? splitk_workspace_bytes(slices, M, N) : 0;
+  int counts[4] = {132, 148, 160, 0};
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess)
+    counts[3] = sms;
+  else
+    (void)cudaGetLastError();
+  size_t need = 0;
+  for (int sm : counts) {
+    if (sm <= 0) continue;
+    const int slices = splitk_slices(sm, M, N, K);
+    const size_t n = slices ? splitk_workspace_bytes(slices, M, N) : 0;
+    if (n > need) need = n;
+  }
+  return need;
 }
 
 int wb200_workspace_init(void* workspace, size_t bytes, void* stream) {

@@ -107,18 +107,50 @@ def dequant_mxfp4(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     return out
 
 
-# One skinny-path workspace per device, created on first use.
-_workspaces: dict[int, torch.Tensor] = {}
+class WorkspacePool:
+    """Workspaces of the skinny (M <= 128) and split-K paths, one per (device, stream, kind).
+
+    A workspace holds counters and partial tiles that a running GEMM owns, so two GEMMs that may overlap on
+    the GPU (different streams) must not share one; and the skinny path expects its partial-tile region in the
+    state `wb200_workspace_init` leaves it in (which it restores after every launch), so it does not share
+    with the split-K path, which leaves partial products there. Each kernel object has its own pool, and the
+    functional entry points share a module-level one.
+
+    Workspaces are created and initialised eagerly. While a stream is being captured into a CUDA graph nothing
+    is allocated: the call uses the workspace an earlier eager call (the warm-up) made for that device and kind.
+    """
+
+    def __init__(self):
+        self._by_key: dict = {}
+
+    def get(self, device: torch.device, nbytes: int, kind: str) -> torch.Tensor:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        capturing = torch.cuda.is_current_stream_capturing()
+        key = (idx, torch.cuda.current_stream(idx).cuda_stream, kind)
+        ws = self._by_key.get(key)
+        if ws is not None and ws.numel() >= nbytes:
+            return ws
+        if capturing:
+            for (d, _, k), w in self._by_key.items():
+                if d == idx and k == kind and w.numel() >= nbytes:
+                    return w
+            raise RuntimeError("this GEMM needs a workspace, which cannot be created while a CUDA graph is being captured: "
+                               "call it once eagerly (with the same shapes) before the capture")
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", idx))
+        with torch.cuda.device(idx):
+            _lib.check(_lib.load().wb200_workspace_init(ws.data_ptr(), nbytes, _stream()))
+        self._by_key[key] = ws
+        return ws
+
+    def clear(self) -> None:
+        self._by_key.clear()
 
 
-def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _workspaces.get(idx)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _lib.check(_lib.load().wb200_workspace_init(ws.data_ptr(), nbytes, _stream()))
-        _workspaces[idx] = ws
-    return ws
+_pool = WorkspacePool()
+
+
+def _workspace(device: torch.device, nbytes: int, kind: str = "skinny", pool: WorkspacePool | None = None) -> torch.Tensor:
+    return (pool or _pool).get(device, nbytes, kind)
 
 
 _DTYPE_CODE = {torch.float32: _lib.WB200_F32, torch.bfloat16: _lib.WB200_BF16}
@@ -151,7 +183,7 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
     if M <= 128 or (flags & _lib.PATH_MASK) == _lib.PATH_TILE_SPLITK or split_k_pays():
         ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))  # skinny shapes and split-K shapes use one
         if ws_bytes:
-            ws_ptr = _workspace(a.device, ws_bytes).data_ptr()
+            ws_ptr = _workspace(a.device, ws_bytes, "skinny" if M <= 128 else "splitk").data_ptr()
     dev_index = a.device.index
     if dev_index is None or dev_index == torch.cuda.current_device():
         rc = lib.wb200_mxfp4_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
@@ -210,7 +242,7 @@ def scaled_gemm_mxfp8_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tenso
     ws_ptr = ws_bytes = 0
     if M <= 128:  # the skinny stream-K path needs its workspace
         ws_bytes = int(lib.wb200_mxfp4_gemm_workspace_bytes(M, N, K))
-        ws_ptr = _workspace(a.device, ws_bytes).data_ptr()
+        ws_ptr = _workspace(a.device, ws_bytes, "skinny").data_ptr()
     with torch.cuda.device(a.device):
         _lib.check(lib.wb200_mxfp8_gemm(M, N, K, a.data_ptr(), a_sf.data.data_ptr(), b.data_ptr(), b_sf.data.data_ptr(),
                                         c.data_ptr(), _DTYPE_CODE[c.dtype], c.stride(0) if M > 1 else N, elem_format, ws_ptr,
