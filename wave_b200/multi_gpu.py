@@ -96,16 +96,27 @@ class ShardedScaledGemm:
             if self.local_n:
                 self._kernel(a, a_scale, self._b, self._b_sf, c)
             return c
-        # Full C on every rank. Every rank computes into its slot of a [world, M, widest shard] buffer
-        # (narrower shards leave the tail columns of their slot unused), one all-gather fills the other
-        # slots, and one strided copy per shard lays the column blocks side by side.
-        wmax = max(n1 - n0 for n0, n1 in self.bounds)
-        stacked = torch.empty(self.world_size, M, wmax, dtype=self.out.torch_dtype, device=a.device)
+        # Full C on every rank: every rank computes into its slot of a [world, M, widest shard] buffer (narrower
+        # shards leave the tail columns of their slot unused); gather_slots does the rest.
+        stacked = self.slot_buffer(M, a.device)
         if self.local_n:
             self._kernel(a, a_scale, self._b, self._b_sf, stacked[self.rank][:, : self.local_n])
+        return self.gather_slots(stacked, out=out)
+
+    def slot_buffer(self, M: int, device) -> torch.Tensor:
+        """[world, M, widest shard] buffer of the output type; rank r's GEMM result belongs in slot r."""
+        wmax = max(n1 - n0 for n0, n1 in self.bounds)
+        return torch.empty(self.world_size, M, wmax, dtype=self.out.torch_dtype, device=device)
+
+    def gather_slots(self, stacked: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The exchange step on its own: this rank's slot of `stacked` holds its column block of C; one all-gather
+        fills the other slots, and one strided copy per shard lays the column blocks side by side in [M, N].
+        The reference merges per-device output slices the same way, without a collective, inside one process
+        (wave_lang/kernel/compiler/host_utils.py:330-376)."""
+        M, wmax = stacked.shape[1], stacked.shape[2]
         if self.world_size > 1:
             dist.all_gather_into_tensor(stacked.view(-1), stacked[self.rank].reshape(-1), group=self.group)
-        full = out if out is not None else torch.empty(M, self.N, dtype=self.out.torch_dtype, device=a.device)
+        full = out if out is not None else torch.empty(M, self.N, dtype=self.out.torch_dtype, device=stacked.device)
         if all(n1 - n0 == wmax for n0, n1 in self.bounds):
             full.view(M, self.world_size, wmax).copy_(stacked.permute(1, 0, 2))
         else:
