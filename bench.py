@@ -297,6 +297,24 @@ def sharded_record(dev, rank, world, dist):
     ev[3].record()
     barrier()
     gather_ms = ev[2].elapsed_time(ev[3]) / greps
+    # the product's exchange: the block computed in place in a matrix the ranks share over CUDA IPC, then pushed to the
+    # peers by the copy engines (no collective library, no interleaving pass)
+    so = op.shared_output(M, dev)
+    c_inplace = so.tensor[:, n0:n1]
+    op(a, a_s, out=c_inplace)
+    op.push_blocks(so)
+    barrier()
+    pev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    pev[0].record()
+    for _ in range(greps):
+        op.push_blocks(so)
+    pev[1].record()
+    barrier()
+    push_ms = pev[0].elapsed_time(pev[1]) / greps
+    push_equal = bool(torch.equal(so.tensor, full))
+    barrier()
+    so.close()
+    del so, c_inplace
     ops.check_device_status()
     # parity, outside the timed regions: 48 sampled rows of a against two 512-column blocks of this rank's shard,
     # on the gathered C (which also checks that the gather put this rank's block where it belongs)
@@ -309,23 +327,74 @@ def sharded_record(dev, rank, world, dist):
         d = orc.bf16_ulp_distance(got, ref)
         worst, over = max(worst, int(d.max())), over + int((d > 1).sum())
     # one more block that another rank computed (exists only when there is more than one rank): bit-equal across ranks
-    stats = torch.tensor([gemm_ms, gather_ms, float(worst), float(over)], device=dev, dtype=torch.float64)
+    stats = torch.tensor([gemm_ms, gather_ms, float(worst), float(over), push_ms, 0.0 if push_equal else 1.0], device=dev, dtype=torch.float64)
     if world > 1:
         t = stats.clone()
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         stats = t
-    gemm_ms, gather_ms, worst, over = (float(x) for x in stats)
+    gemm_ms, gather_ms, worst, over, push_ms, push_bad = (float(x) for x in stats)
     flops = 2.0 * M * N * K
     recv = (world - 1) / world * M * N * 2
-    return {"config": f"C5: M={M}, N={N}, K={K}, bf16 out, b row-sharded {world}-way ({op.local_n} rows on rank 0), a replicated before timing",
+    # The same problem through the one-call, one-process form (wave_compile with num_devices = G, the reference's
+    # MultiDeviceLaunchable): rank 0 drives all the GPUs of the job while the other ranks wait at a barrier; its
+    # result must equal the per-rank launcher's bit for bit.
+    native = None
+    if torch.cuda.device_count() >= world:
+        # The other ranks wait on the HOST (a key in the job's store), with nothing of theirs queued on their GPU: a
+        # collective's kernel spinning on GPU g while rank 0's GEMM runs there from another process would time-slice
+        # against it.
+        torch.cuda.synchronize()
+        store = dist.distributed_c10d._get_default_store() if world > 1 else None
+        if rank == 0:
+            del stacked, b_shard, bs_shard
+            torch.cuda.empty_cache()
+            qs, ss = [], []
+            for r0 in range(0, N, blk):
+                q, s = gpu_quantised(min(blk, N - r0), K, SHARDED["seed_b"] * 1000 + r0 // blk, 1.0, dev)
+                qs.append(q)
+                ss.append(s)
+            b_full, bs_full = torch.cat(qs), torch.cat(ss)
+            del qs, ss
+            kernel, options = wb.get_tagged_mxfp4_gemm((M, N, K), output_dtype=wb.bf16)
+            options.num_devices = world
+            md = wb.wave_compile(wb.set_default_run_config(options), kernel)
+            c1 = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            for _ in range(2):
+                md(a, a_s, b_full, bs_full, c1)
+                md.synchronize()
+            g_ms, c_ms = [], []
+            for _ in range(4):
+                md.invoke(a, a_s, b_full, bs_full, c1, timed=True)
+                md.synchronize()
+                g_ms.append(md.last_gemm_ms)
+                c_ms.append(md.last_gather_ms)
+            native = {"through": "wave_compile(options with num_devices = G)(a, a_scale, b, b_scale, c): one process, wb200_multi_gpu_* (tensors on GPU 0 in, merged c on GPU 0 out)",
+                      "gemm_ms": sum(g_ms) / len(g_ms), "merge_ms": sum(c_ms) / len(c_ms),
+                      "merge_note": "2-D copy-engine copies of the column blocks into c on GPU 0 (no collective)",
+                      "merge_received_bytes": recv, "merge_GBps": (recv / (sum(c_ms) / len(c_ms) * 1e-3) / 1e9) if world > 1 else None,
+                      "bit_equal_to_per_rank_launcher": bool(torch.equal(c1, full)), "timing": "CUDA events per GPU, longest over the GPUs, mean of 4 calls"}
+            del md, c1, b_full, bs_full
+            torch.cuda.synchronize()
+            if store is not None:
+                store.set("one_process_launcher_done", "1")
+        elif store is not None:
+            store.wait(["one_process_launcher_done"])
+        barrier()
+    out = {"config": f"C5: M={M}, N={N}, K={K}, bf16 out, b row-sharded {world}-way ({op.local_n} rows on rank 0), a replicated before timing",
             "through": "wave_b200.multi_gpu.ShardedScaledGemm (public call: activation-scale repack + GEMM per rank, no collective)",
             "gemm_ms": gemm_ms, "tflops": flops / (gemm_ms * 1e-3) / 1e12, "frac_of_nominal_per_gpu": flops / world / (gemm_ms * 1e-3) / 1e12 / NOMINAL_FP4_TFLOPS,
-            "allgather_ms": gather_ms, "allgather_received_bytes_per_gpu": recv,
-            "allgather_GBps_per_gpu": (recv / (gather_ms * 1e-3) / 1e9) if world > 1 else None,
-            "allgather_note": "NCCL all-gather of the bf16 column blocks plus the copy that interleaves them into [M, N]; with one rank only the copy",
+            "allgather_ms": push_ms, "allgather_received_bytes_per_gpu": recv,
+            "allgather_GBps_per_gpu": (recv / (push_ms * 1e-3) / 1e9) if world > 1 else None,
+            "allgather_note": "ShardedScaledGemm.push_blocks: every rank's column block, computed in place in a matrix shared over CUDA IPC, copied by the copy engines into every other rank's matrix, then a stream-ordered barrier",
+            "allgather_equals_nccl_result": push_bad == 0.0,
+            "allgather_nccl_ms": gather_ms, "allgather_nccl_GBps_per_gpu": (recv / (gather_ms * 1e-3) / 1e9) if world > 1 else None,
+            "allgather_nccl_note": "the library baseline: NCCL all-gather of the column blocks plus the copy that interleaves them into [M, N]; with one rank only the copy",
             "parity_ok": bool(worst <= 1), "parity_max_ulp": worst, "parity_entries_over_1ulp": over,
             "parity_sample": "per rank: 48 rows of a x 2 blocks of 512 columns of its shard, read from the gathered C, against the CPU oracle",
             "timing": f"CUDA events, {reps} GEMM calls / {greps} gathers, max over ranks", "data": "operands generated and quantised on the GPU (seeded)"}
+    if native:
+        out["one_process_launcher"] = native
+    return out
 
 
 def copy_ceiling(host, c_host, dev, steps):

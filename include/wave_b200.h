@@ -273,10 +273,72 @@ int wb200_peer_buffer_open(const void* handle64, void** ptr);
 int wb200_peer_buffer_close(void* ptr);
 int wb200_peer_buffer_destroy(void* ptr);
 
+/* rows x width_bytes from src (row pitch src_pitch bytes) to dst (row pitch dst_pitch), asynchronous on `stream`, by the
+ * copy engines. Either side may be another GPU's memory (a wb200_peer_buffer_open mapping, or peer access): this is how
+ * a rank of the N-sharded GEMM deposits its column block of C in every other rank's [M, N] matrix, in place, with no
+ * collective library and no interleaving pass afterwards. The reference merges per-device output slices into the
+ * result on the host side of its wrapper (wave_lang/kernel/compiler/host_utils.py:330-376). */
+int wb200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows, void* stream);
+
 /* out[i] = slots[0][i] + slots[1][i] + ... (f32, slot order, i < count; slot s starts at slots + s * slot_stride),
  * rounded once to out_dtype: the reduction over the ranks' partial products. */
 int wb200_sum_slots(const float* slots, int num_slots, long long slot_stride, long long count, void* out, int out_dtype,
                     void* stream);
+
+/* ---- N-sharded GEMM over the GPUs of one node, driven by ONE process --------------------------------
+ *
+ * Replaces the reference's multi-device launch: `DeviceConstraint` tiles M / N over devices
+ * (wave_lang/kernel/wave/constraints.py:1105-1180), the host wrapper slices the inputs per device,
+ * dispatches one kernel per device and merges the output slices (wave_lang/kernel/compiler/host_utils.py:158-376),
+ * and `MultiDeviceLaunchable` owns one device object per GPU and invokes once
+ * (wave_lang/runtime/multi_device_launch.py:38-273). Here device g owns the rows [n_bounds[g], n_bounds[g+1]) of b
+ * (a column block of C) and keeps them resident; a is copied to every device; every device runs one GEMM on its
+ * own stream; the column blocks are laid side by side wherever the whole C is wanted. No collective library is
+ * involved and no kernel reads another GPU's memory: the GPUs exchange data through copy-engine copies only.
+ * All memory is the caller's: the handle owns streams and events, nothing else. */
+typedef struct wb200_multi_gpu wb200_multi_gpu_t;
+
+typedef struct {
+  void* a;                    /* [M, K/2] on this device: filled by wb200_multi_gpu_broadcast_a */
+  void* a_scale;              /* [M, K/32] row-major on this device: filled by wb200_multi_gpu_broadcast_a */
+  void* a_scale_packed;       /* wb200_packed_scale_bytes(M, K) on this device: written by wb200_multi_gpu_gemm */
+  const void* b;              /* this device's rows of b, [n_g, K/2] */
+  const void* b_scale_packed; /* their scales, packed once by the caller (wb200_repack_scales on this device) */
+  void* c;                    /* [M, n_g] on this device, row pitch ldc elements */
+  long long ldc;
+  void* workspace;            /* wb200_mxfp4_gemm_workspace_bytes(M, n_g, K) on this device, initialised; may be null when 0 */
+  size_t workspace_bytes;
+} wb200_device_operands;
+
+/* One stream per listed device; peer access is enabled between every pair that supports it. */
+int wb200_multi_gpu_create(int num_devices, const int* device_ids, wb200_multi_gpu_t** out);
+int wb200_multi_gpu_destroy(wb200_multi_gpu_t* h);
+int wb200_multi_gpu_num_devices(const wb200_multi_gpu_t* h);
+/* Rows of b owned by device `index` of `num_devices` (multiples of `granule`, 128 = the scale-factor atom height). Host only. */
+int wb200_multi_gpu_shard_bounds(int N, int num_devices, int index, int granule, int* n0, int* n1);
+/* Every device stream waits for the work queued so far on `stream` of device `device` (the producer of a): the
+ * reference's launch is ordered after the caller's stream in the same way (run_utils.py:87). */
+int wb200_multi_gpu_wait_for(wb200_multi_gpu_t* h, int device, void* stream);
+/* Copy a [M, K/2] and a_scale [M, K/32] (contiguous; on device src_device, or in pinned host memory when
+ * src_device < 0) into ops[g].a / ops[g].a_scale of every device, on the devices' streams. */
+int wb200_multi_gpu_broadcast_a(wb200_multi_gpu_t* h, int M, int K, const void* a, const void* a_scale, int src_device,
+                                const wb200_device_operands* ops);
+/* On every device g: pack ops[g].a_scale, then c_g = a * b_g^T (wb200_mxfp4_gemm_repack_a), on the device's stream.
+ * n_bounds: num_devices + 1 row offsets of the shards; a device with an empty shard is skipped. */
+int wb200_multi_gpu_gemm(wb200_multi_gpu_t* h, int M, int K, const int* n_bounds, const wb200_device_operands* ops,
+                         int c_dtype, unsigned flags);
+/* Lay the column blocks side by side: for every destination j (a matrix [M, N] with row pitch dst_ld elements on
+ * device dst_devices[j], or in pinned host memory when dst_devices[j] < 0), device g copies its block into columns
+ * [n_bounds[g], n_bounds[g+1]) on its own stream, after its GEMM (2-D copy-engine copies; one per device and destination). */
+int wb200_multi_gpu_gather_c(wb200_multi_gpu_t* h, int M, const int* n_bounds, const wb200_device_operands* ops, int c_dtype,
+                             int num_dst, void* const* dst_ptrs, const int* dst_devices, long long dst_ld);
+/* `stream` of device `device` waits for everything queued on the devices' streams; the host does not block. */
+int wb200_multi_gpu_join(wb200_multi_gpu_t* h, int device, void* stream);
+/* Host waits for every device stream; returns the first device-side status that is not clean. */
+int wb200_multi_gpu_synchronize(wb200_multi_gpu_t* h);
+/* Timing brackets on every device stream: end() synchronises and returns the largest elapsed time over the devices. */
+int wb200_multi_gpu_time_begin(wb200_multi_gpu_t* h);
+int wb200_multi_gpu_time_end(wb200_multi_gpu_t* h, float* max_ms);
 
 #ifdef __cplusplus
 }

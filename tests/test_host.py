@@ -115,7 +115,12 @@ def test_template_surface_matches_reference_names(lib):
     with pytest.raises(TypeError):
         wb.wave_compile(wb.WaveCompileOptions(), object())
     with pytest.raises(ValueError):
-        wb.wave_compile(wb.WaveCompileOptions(num_devices=2), kernel)
+        wb.wave_compile(wb.WaveCompileOptions(num_devices=0), kernel)
+    # num_devices > 1 asks for the multi-device launcher (wave_lang/kernel/wave/compile.py:194-201): without that many
+    # GPUs it fails loudly, it does not fall back to anything
+    if torch.cuda.device_count() < 2:
+        with pytest.raises(RuntimeError, match="GPU"):
+            wb.wave_compile(wb.WaveCompileOptions(num_devices=2), kernel)
 
 
 def test_splitk_preconditions_match_reference():
@@ -148,3 +153,21 @@ def test_perf_formulas_match_the_reference_benchmark_driver():
     shapes = perf.default_shapes()
     assert (8192, 8192, 8192) in shapes and all(k % 32 == 0 for _, _, k in shapes)
 
+
+
+def test_native_shard_bounds_match_the_python_rule(lib):
+    """The native launcher and the torch.distributed launcher must agree on who owns which rows of b."""
+    from wave_b200 import multi_device, multi_gpu
+    for N in (128, 1000, 8192, 53248, 28672 + 5):
+        for G in (1, 2, 3, 4, 8):
+            got = [multi_device.shard_bounds(N, G, g) for g in range(G)]
+            assert got == [multi_gpu.shard_bounds(N, G, g) for g in range(G)]
+            assert got[0][0] == 0 and got[-1][1] == N and all(a[1] == b[0] for a, b in zip(got, got[1:]))
+            assert all(n0 % 128 == 0 for n0, n1 in got if n1 > n0)
+    import ctypes as C
+    n0, n1 = C.c_int(), C.c_int()
+    assert lib.wb200_multi_gpu_shard_bounds(0, 2, 0, 128, C.byref(n0), C.byref(n1)) == _lib.WB200_ERR_INVALID_ARG
+    assert lib.wb200_multi_gpu_shard_bounds(1024, 2, 2, 128, C.byref(n0), C.byref(n1)) == _lib.WB200_ERR_INVALID_ARG
+    h = C.c_void_p()
+    assert lib.wb200_multi_gpu_create(0, None, C.byref(h)) == _lib.WB200_ERR_INVALID_ARG
+    assert lib.wb200_multi_gpu_num_devices(None) == 0 and lib.wb200_multi_gpu_destroy(None) == 0

@@ -169,6 +169,18 @@ def _gpu_rank_body(rank, world, port, out_queue):
     stacked = op.slot_buffer(M, dev)
     stacked[rank][:, : op.local_n].copy_(local)
     ok = ok and torch.equal(op.gather_slots(stacked), full)
+    # the same exchange with copy-engine pushes into matrices the ranks share over CUDA IPC: compute in place, push
+    so = op.shared_output(M, dev)
+    for _ in range(2):
+        so.tensor.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()  # nobody pushes into a matrix that is still being filled
+        op(a.to(dev), a_s.to(dev), out=so.tensor[:, op.n0:op.n1])
+        pushed = op.push_blocks(so)
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(pushed, full)
+    dist.barrier()
+    so.close()
     out_queue.put((rank, bool(ok), ""))
     dist.barrier()
     dist.destroy_process_group()
@@ -341,3 +353,50 @@ def test_gpu_ranks_k_sharded_scatter_and_sum():
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     _run_gpu_ranks(_gpu_rank_ksharded, world, timeout_s=180)
+
+
+# ---------------------------------------------------------------------------------------------
+# one process, several GPUs: the reference's single-call multi-device form
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("where", ["device0", "host"])
+def test_one_call_multi_device_gemm(where):
+    """wave_compile(options with num_devices = G)(a, a_scale, b, b_scale, c) with the tensors in one place, as
+    tests/kernel/dist_gemm_test.py:60-101 calls the reference's distributed GEMM: b is split over the GPUs, every
+    GPU computes its column block, c comes back merged. Checked against the oracle and, bit for bit, against the
+    single-GPU kernel (same kernel, same K order)."""
+    G = min(torch.cuda.device_count(), 4)
+    if G < 2:
+        pytest.skip("needs at least 2 GPUs")
+    sys.path.insert(0, str(ROOT))
+    from oracle import mxfp4_oracle as orc
+    import wave_b200 as wb
+    for (M, N, K, dtype) in [(300, 1024 * G + 256, 1024, wb.bf16), (16, 4096, 2048, wb.f32)]:
+        g = torch.Generator().manual_seed(23)
+        a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, generator=g)
+        b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+        a_s = torch.randint(124, 131, (M, K // 32), dtype=torch.uint8, generator=g)
+        b_s = torch.randint(124, 131, (N, K // 32), dtype=torch.uint8, generator=g)
+        ref = orc.scaled_gemm(a, a_s, b, b_s)
+        kernel, options = wb.get_tagged_mxfp4_gemm((M, N, K), output_dtype=dtype)
+        options.num_devices = G
+        gemm = wb.wave_compile(wb.set_default_run_config(options), kernel)
+        if where == "host":
+            t = [x.pin_memory() for x in (a, a_s, b, b_s)]
+            c = torch.empty(M, N, dtype=dtype.torch_dtype).pin_memory()
+        else:
+            t = [x.to("cuda:0") for x in (a, a_s, b, b_s)]
+            c = torch.full((M, N), float("nan"), dtype=dtype.torch_dtype, device="cuda:0")
+        for _ in range(2):  # the second call reuses the sharded weights
+            gemm(*t, c)
+            gemm.synchronize()
+        if dtype is wb.bf16:
+            assert int(orc.bf16_ulp_distance(c, ref).max()) <= 1
+        else:
+            tol = orc.f32_tolerance(orc.dequant_mxfp4(a, a_s), orc.dequant_mxfp4(b, b_s), ref, K)
+            assert bool(((c.float().cpu() - ref).abs() <= tol).all())
+        k1, o1 = wb.get_tagged_mxfp4_gemm((M, N, K), output_dtype=dtype)
+        single = torch.empty(M, N, dtype=dtype.torch_dtype, device="cuda:0")
+        wb.wave_compile(o1, k1)(*[x.to("cuda:0") for x in (a, a_s, b, b_s)], single)
+        torch.cuda.synchronize()
+        assert torch.equal(single.cpu(), c.cpu())

@@ -68,6 +68,19 @@ EXPORTED_SYMBOLS = (
     "wb200_peer_buffer_close",
     "wb200_peer_buffer_destroy",
     "wb200_sum_slots",
+    "wb200_copy_2d",
+    "wb200_multi_gpu_create",
+    "wb200_multi_gpu_destroy",
+    "wb200_multi_gpu_num_devices",
+    "wb200_multi_gpu_shard_bounds",
+    "wb200_multi_gpu_wait_for",
+    "wb200_multi_gpu_broadcast_a",
+    "wb200_multi_gpu_gemm",
+    "wb200_multi_gpu_gather_c",
+    "wb200_multi_gpu_join",
+    "wb200_multi_gpu_synchronize",
+    "wb200_multi_gpu_time_begin",
+    "wb200_multi_gpu_time_end",
 )
 
 
@@ -172,6 +185,42 @@ def load() -> ctypes.CDLL:
     lib.wb200_peer_buffer_destroy.argtypes = [c_void_p]
     lib.wb200_sum_slots.restype = c_int
     lib.wb200_sum_slots.argtypes = [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p]
+    lib.wb200_copy_2d.restype = c_int
+    lib.wb200_copy_2d.argtypes = [c_void_p, c_size_t, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p]
+
+    class DeviceOperands(ctypes.Structure):
+        """wb200_device_operands of include/wave_b200.h."""
+        _fields_ = [("a", c_void_p), ("a_scale", c_void_p), ("a_scale_packed", c_void_p), ("b", c_void_p),
+                    ("b_scale_packed", c_void_p), ("c", c_void_p), ("ldc", c_ll), ("workspace", c_void_p),
+                    ("workspace_bytes", c_size_t)]
+
+    lib.DeviceOperands = DeviceOperands
+    p_int = ctypes.POINTER(c_int)
+    p_ops = ctypes.POINTER(DeviceOperands)
+    lib.wb200_multi_gpu_create.restype = c_int
+    lib.wb200_multi_gpu_create.argtypes = [c_int, p_int, ctypes.POINTER(c_void_p)]
+    lib.wb200_multi_gpu_destroy.restype = c_int
+    lib.wb200_multi_gpu_destroy.argtypes = [c_void_p]
+    lib.wb200_multi_gpu_num_devices.restype = c_int
+    lib.wb200_multi_gpu_num_devices.argtypes = [c_void_p]
+    lib.wb200_multi_gpu_shard_bounds.restype = c_int
+    lib.wb200_multi_gpu_shard_bounds.argtypes = [c_int, c_int, c_int, c_int, p_int, p_int]
+    lib.wb200_multi_gpu_wait_for.restype = c_int
+    lib.wb200_multi_gpu_wait_for.argtypes = [c_void_p, c_int, c_void_p]
+    lib.wb200_multi_gpu_broadcast_a.restype = c_int
+    lib.wb200_multi_gpu_broadcast_a.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, p_ops]
+    lib.wb200_multi_gpu_gemm.restype = c_int
+    lib.wb200_multi_gpu_gemm.argtypes = [c_void_p, c_int, c_int, p_int, p_ops, c_int, c_uint]
+    lib.wb200_multi_gpu_gather_c.restype = c_int
+    lib.wb200_multi_gpu_gather_c.argtypes = [c_void_p, c_int, p_int, p_ops, c_int, c_int, ctypes.POINTER(c_void_p), p_int, c_ll]
+    lib.wb200_multi_gpu_join.restype = c_int
+    lib.wb200_multi_gpu_join.argtypes = [c_void_p, c_int, c_void_p]
+    lib.wb200_multi_gpu_synchronize.restype = c_int
+    lib.wb200_multi_gpu_synchronize.argtypes = [c_void_p]
+    lib.wb200_multi_gpu_time_begin.restype = c_int
+    lib.wb200_multi_gpu_time_begin.argtypes = [c_void_p]
+    lib.wb200_multi_gpu_time_end.restype = c_int
+    lib.wb200_multi_gpu_time_end.argtypes = [c_void_p, ctypes.POINTER(ctypes.c_float)]
     _lib = lib
     return lib
 

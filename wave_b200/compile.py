@@ -92,8 +92,8 @@ def set_default_run_config(options: WaveCompileOptions) -> WaveCompileOptions:
 def validate_options(options: WaveCompileOptions) -> None:
     """Reject option combinations this library cannot honour (the reference's validate_options,
     wave_lang/kernel/wave/compile.py:1489-1500, raises ValueError in the same way)."""
-    if options.num_devices != 1:
-        raise ValueError("num_devices > 1 is served by wave_b200.multi_gpu.ShardedScaledGemm, not by wave_compile")
+    if options.num_devices < 1:
+        raise ValueError(f"num_devices must be at least 1, got {options.num_devices}")
     if options.kernel_path not in (_lib.PATH_AUTO, _lib.PATH_TILE_1CTA, _lib.PATH_TILE_2CTA, _lib.PATH_SKINNY, _lib.PATH_TILE_SPLITK):
         raise ValueError(f"unknown kernel_path {options.kernel_path}")
 
@@ -275,4 +275,10 @@ def wave_compile(options: WaveCompileOptions, kernel, schedule=None) -> ScaledGe
         raise TypeError("wave_compile here only compiles the MXFP4 scaled-GEMM templates of wave_b200.templates")
     validate_options(options)
     _lib.load()  # fail now, not at the first call, when the CUDA library is missing
+    if options.num_devices > 1:
+        # the reference returns a multi-device launchable in this case (compile.py:194-201, 1141-1142)
+        from .multi_device import MultiDeviceScaledGemm
+        if kernel.element_bits != 4 or kernel.broadcast_a_scale or kernel.preshuffled_scales:
+            raise ValueError("the multi-device form serves the plain MXFP4 scaled-GEMM templates")
+        return MultiDeviceScaledGemm(kernel, options)
     return ScaledGemmKernel(kernel, options)

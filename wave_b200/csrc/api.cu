@@ -4,6 +4,7 @@
 #include "../../include/wave_b200.h"
 #include "gemm_sm100.cuh"
 #include "moe.cuh"
+#include "multi_gpu.cuh"
 #include "quantize.cuh"
 #include "scales.cuh"
 #include "skinny_sm100.cuh"
@@ -1287,6 +1288,13 @@ int wb200_peer_buffer_destroy(void* ptr) {
   return WB200_OK;
 }
 
+int wb200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows, void* stream) {
+  if (!dst || !src || width_bytes == 0 || rows == 0 || dst_pitch < width_bytes || src_pitch < width_bytes)
+    return fail(WB200_ERR_INVALID_ARG, "copy_2d: null pointer, empty copy or a pitch smaller than the row width");
+  WB_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+  return WB200_OK;
+}
+
 int wb200_sum_slots(const float* slots, int num_slots, long long slot_stride, long long count, void* out, int out_dtype,
                     void* stream) {
   if (!slots || !out || num_slots <= 0 || count <= 0 || slot_stride < count)
@@ -1347,6 +1355,206 @@ int wb200_mxfp4_grouped_gemm(int num_groups, const int* row_offsets, const int* 
                        wb::sf_row_blocks(Mg), wb::sf_row_blocks(N), 0, static_cast<cudaStream_t>(stream));
     if (rc) return rc;
   }
+  return WB200_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// N-sharded GEMM over several GPUs driven by one process
+// ------------------------------------------------------------------------------------------
+struct wb200_multi_gpu {
+  wb::MultiGpu m;
+};
+
+int wb200_multi_gpu_shard_bounds(int N, int num_devices, int index, int granule, int* n0, int* n1) {
+  if (N <= 0 || num_devices <= 0 || index < 0 || index >= num_devices || granule <= 0 || !n0 || !n1)
+    return fail(WB200_ERR_INVALID_ARG, "shard_bounds: N = %d, num_devices = %d, index = %d, granule = %d", N, num_devices, index, granule);
+  wb::shard_bounds(N, num_devices, index, granule, n0, n1);
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_num_devices(const wb200_multi_gpu_t* h) { return h ? int(h->m.devices.size()) : 0; }
+
+int wb200_multi_gpu_destroy(wb200_multi_gpu_t* h) {
+  if (!h) return WB200_OK;
+  for (size_t g = 0; g < h->m.devices.size(); ++g) {
+    wb::DeviceScope scope(h->m.devices[g]);
+    if (g < h->m.streams.size() && h->m.streams[g]) {
+      cudaStreamSynchronize(h->m.streams[g]);
+      cudaStreamDestroy(h->m.streams[g]);
+    }
+    if (g < h->m.done.size() && h->m.done[g]) cudaEventDestroy(h->m.done[g]);
+    if (g < h->m.t_begin.size() && h->m.t_begin[g]) cudaEventDestroy(h->m.t_begin[g]);
+    if (g < h->m.t_end.size() && h->m.t_end[g]) cudaEventDestroy(h->m.t_end[g]);
+  }
+  delete h;
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_create(int num_devices, const int* device_ids, wb200_multi_gpu_t** out) {
+  if (num_devices <= 0 || num_devices > kMaxDevices || !device_ids || !out)
+    return fail(WB200_ERR_INVALID_ARG, "multi_gpu_create: num_devices = %d (1..%d) with a list of device ids", num_devices, kMaxDevices);
+  int count = 0;
+  WB_CUDA(cudaGetDeviceCount(&count));
+  for (int i = 0; i < num_devices; ++i) {
+    if (device_ids[i] < 0 || device_ids[i] >= count)
+      return fail(WB200_ERR_INVALID_ARG, "multi_gpu_create: device id %d, but this process sees %d device(s)", device_ids[i], count);
+    for (int j = 0; j < i; ++j)
+      if (device_ids[j] == device_ids[i]) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_create: device %d listed twice", device_ids[i]);
+  }
+  wb200_multi_gpu_t* h = new wb200_multi_gpu_t;
+  h->m.devices.assign(device_ids, device_ids + num_devices);
+  h->m.streams.assign(num_devices, nullptr);
+  h->m.done.assign(num_devices, nullptr);
+  h->m.t_begin.assign(num_devices, nullptr);
+  h->m.t_end.assign(num_devices, nullptr);
+  auto bail = [&](int rc) { wb200_multi_gpu_destroy(h); return rc; };
+  for (int g = 0; g < num_devices; ++g) {
+    wb::DeviceScope scope(device_ids[g]);
+    if (!scope.ok) return bail(fail(WB200_ERR_CUDA, "multi_gpu_create: cannot make device %d current", device_ids[g]));
+    DeviceInfo* info;
+    int rc = get_device(&info);  // one-time set-up of the library on this device (and the sm_100 check)
+    if (rc) return bail(rc);
+    cudaError_t e = cudaStreamCreateWithFlags(&h->m.streams[g], cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->m.done[g], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->m.t_begin[g]);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->m.t_end[g]);
+    if (e != cudaSuccess) return bail(fail(WB200_ERR_CUDA, "multi_gpu_create: %s on device %d", cudaGetErrorString(e), device_ids[g]));
+    for (int j = 0; j < num_devices; ++j) {
+      if (j == g) continue;
+      int can = 0;
+      if (cudaDeviceCanAccessPeer(&can, device_ids[g], device_ids[j]) == cudaSuccess && can) {
+        e = cudaDeviceEnablePeerAccess(device_ids[j], 0);
+        if (e != cudaSuccess) (void)cudaGetLastError();  // already enabled, or not possible: copies then go through the host
+      }
+    }
+  }
+  *out = h;
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_wait_for(wb200_multi_gpu_t* h, int device, void* stream) {
+  if (!h) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_wait_for: null handle");
+  cudaEvent_t ev = nullptr;
+  {
+    wb::DeviceScope scope(device);
+    if (!scope.ok) return fail(WB200_ERR_CUDA, "multi_gpu_wait_for: cannot make device %d current", device);
+    WB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    WB_CUDA(cudaEventRecord(ev, static_cast<cudaStream_t>(stream)));
+  }
+  for (size_t g = 0; g < h->m.devices.size(); ++g) {
+    wb::DeviceScope scope(h->m.devices[g]);
+    WB_CUDA(cudaStreamWaitEvent(h->m.streams[g], ev, 0));
+  }
+  WB_CUDA(cudaEventDestroy(ev));  // released once the waits queued above have been satisfied
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_broadcast_a(wb200_multi_gpu_t* h, int M, int K, const void* a, const void* a_scale, int src_device,
+                                const wb200_device_operands* ops) {
+  if (!h || !a || !a_scale || !ops || M <= 0 || K <= 0 || K % 32 != 0)
+    return fail(WB200_ERR_INVALID_ARG, "multi_gpu_broadcast_a: M = %d, K = %d (a multiple of 32) and non-null arguments", M, K);
+  (void)src_device;  // the copies take the direction from the addresses (unified addressing)
+  const size_t a_bytes = size_t(M) * (K / 2), s_bytes = size_t(M) * (K / 32);
+  for (size_t g = 0; g < h->m.devices.size(); ++g) {
+    if (!ops[g].a || !ops[g].a_scale) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_broadcast_a: device %zu has no buffer for a", g);
+    wb::DeviceScope scope(h->m.devices[g]);
+    if (ops[g].a != a) WB_CUDA(cudaMemcpyAsync(ops[g].a, a, a_bytes, cudaMemcpyDefault, h->m.streams[g]));
+    if (ops[g].a_scale != a_scale) WB_CUDA(cudaMemcpyAsync(ops[g].a_scale, a_scale, s_bytes, cudaMemcpyDefault, h->m.streams[g]));
+  }
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_gemm(wb200_multi_gpu_t* h, int M, int K, const int* n_bounds, const wb200_device_operands* ops,
+                         int c_dtype, unsigned flags) {
+  if (!h || !n_bounds || !ops) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_gemm: null argument");
+  const int G = int(h->m.devices.size());
+  for (int g = 0; g < G; ++g)
+    if (n_bounds[g + 1] < n_bounds[g] || (n_bounds[g + 1] > n_bounds[g] && n_bounds[g] % 128 != 0))
+      return fail(WB200_ERR_INVALID_ARG, "multi_gpu_gemm: shard %d must start at a multiple of 128 rows and not end before it starts", g);
+  for (int g = 0; g < G; ++g) {
+    const int n_g = n_bounds[g + 1] - n_bounds[g];
+    if (n_g == 0) continue;
+    wb::DeviceScope scope(h->m.devices[g]);
+    if (!scope.ok) return fail(WB200_ERR_CUDA, "multi_gpu_gemm: cannot make device %d current", h->m.devices[g]);
+    const int rc = wb200_mxfp4_gemm_repack_a(M, n_g, K, ops[g].a, ops[g].a_scale, K / 32, ops[g].a_scale_packed, ops[g].b,
+                                             ops[g].b_scale_packed, ops[g].c, c_dtype, ops[g].ldc, ops[g].workspace,
+                                             ops[g].workspace_bytes, flags, h->m.streams[g]);
+    if (rc) return rc;
+  }
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_gather_c(wb200_multi_gpu_t* h, int M, const int* n_bounds, const wb200_device_operands* ops, int c_dtype,
+                             int num_dst, void* const* dst_ptrs, const int* dst_devices, long long dst_ld) {
+  if (!h || !n_bounds || !ops || num_dst < 0 || (num_dst > 0 && !dst_ptrs) || M <= 0)
+    return fail(WB200_ERR_INVALID_ARG, "multi_gpu_gather_c: null argument");
+  if (c_dtype != WB200_F32 && c_dtype != WB200_BF16) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_gather_c: unknown dtype %d", c_dtype);
+  (void)dst_devices;  // unified addressing: the copy finds its way from the addresses
+  const size_t esz = (c_dtype == WB200_F32) ? 4 : 2;
+  const int G = int(h->m.devices.size());
+  if (dst_ld < n_bounds[G]) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_gather_c: dst_ld = %lld is smaller than N = %d", dst_ld, n_bounds[G]);
+  for (int j = 0; j < num_dst; ++j) {
+    if (!dst_ptrs[j]) continue;
+    for (int g = 0; g < G; ++g) {
+      const int n_g = n_bounds[g + 1] - n_bounds[g];
+      if (n_g == 0) continue;
+      uint8_t* dst = static_cast<uint8_t*>(dst_ptrs[j]) + size_t(n_bounds[g]) * esz;
+      if (dst == ops[g].c && dst_ld == ops[g].ldc) continue;  // the block was computed in place
+      wb::DeviceScope scope(h->m.devices[g]);
+      WB_CUDA(cudaMemcpy2DAsync(dst, size_t(dst_ld) * esz, ops[g].c, size_t(ops[g].ldc) * esz, size_t(n_g) * esz, size_t(M),
+                                cudaMemcpyDefault, h->m.streams[g]));
+    }
+  }
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_join(wb200_multi_gpu_t* h, int device, void* stream) {
+  if (!h) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_join: null handle");
+  for (size_t g = 0; g < h->m.devices.size(); ++g) {
+    wb::DeviceScope scope(h->m.devices[g]);
+    WB_CUDA(cudaEventRecord(h->m.done[g], h->m.streams[g]));
+  }
+  wb::DeviceScope scope(device);
+  if (!scope.ok) return fail(WB200_ERR_CUDA, "multi_gpu_join: cannot make device %d current", device);
+  for (size_t g = 0; g < h->m.devices.size(); ++g) WB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), h->m.done[g], 0));
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_synchronize(wb200_multi_gpu_t* h) {
+  if (!h) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_synchronize: null handle");
+  int first = WB200_OK;
+  for (size_t g = 0; g < h->m.devices.size(); ++g) {
+    wb::DeviceScope scope(h->m.devices[g]);
+    const int rc = wb200_check_device_status(h->m.streams[g], nullptr);  // synchronises the stream, reads the device's status word
+    if (rc && !first) first = rc;
+  }
+  return first;
+}
+
+int wb200_multi_gpu_time_begin(wb200_multi_gpu_t* h) {
+  if (!h) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_time_begin: null handle");
+  for (size_t g = 0; g < h->m.devices.size(); ++g) {
+    wb::DeviceScope scope(h->m.devices[g]);
+    WB_CUDA(cudaEventRecord(h->m.t_begin[g], h->m.streams[g]));
+  }
+  return WB200_OK;
+}
+
+int wb200_multi_gpu_time_end(wb200_multi_gpu_t* h, float* max_ms) {
+  if (!h || !max_ms) return fail(WB200_ERR_INVALID_ARG, "multi_gpu_time_end: null argument");
+  for (size_t g = 0; g < h->m.devices.size(); ++g) {
+    wb::DeviceScope scope(h->m.devices[g]);
+    WB_CUDA(cudaEventRecord(h->m.t_end[g], h->m.streams[g]));
+  }
+  float worst = 0.f;
+  for (size_t g = 0; g < h->m.devices.size(); ++g) {
+    wb::DeviceScope scope(h->m.devices[g]);
+    WB_CUDA(cudaEventSynchronize(h->m.t_end[g]));
+    float ms = 0.f;
+    WB_CUDA(cudaEventElapsedTime(&ms, h->m.t_begin[g], h->m.t_end[g]));
+    if (ms > worst) worst = ms;
+  }
+  *max_ms = worst;
   return WB200_OK;
 }
 

@@ -103,6 +103,32 @@ class ShardedScaledGemm:
             self._kernel(a, a_scale, self._b, self._b_sf, stacked[self.rank][:, : self.local_n])
         return self.gather_slots(stacked, out=out)
 
+    def shared_output(self, M: int, device) -> SharedOutput:
+        """A full-width [M, N] output on every rank that the other ranks can write (collective). Compute into
+        `out.tensor[:, n0:n1]` (pass it as `out=`), then `push_blocks(out)`."""
+        return SharedOutput(M, self.N, self.out.torch_dtype, device, self.group)
+
+    def push_blocks(self, out: SharedOutput) -> torch.Tensor:
+        """The exchange without a collective library: this rank's column block of `out.tensor`, already computed in
+        place, is copied by the copy engines into the same columns of every other rank's matrix (one 2-D copy per
+        peer, on the current stream, starting with the next rank so that the ranks do not all write to the same peer
+        at once); a stream-ordered barrier follows, after which `out.tensor` holds the whole C on every rank. No
+        interleaving pass: the blocks land where they belong. A rank that is still reading `out.tensor` when a peer
+        pushes the NEXT call's block would see it change: alternate two SharedOutputs, or order the calls."""
+        from . import _lib
+        lib = _lib.load()
+        if self.local_n and self.world_size > 1:
+            esz = out.row_bytes // out.N
+            off, width = self.n0 * esz, self.local_n * esz
+            stream = torch.cuda.current_stream(out.device).cuda_stream
+            with torch.cuda.device(out.device):
+                for i in range(1, self.world_size):
+                    r = (self.rank + i) % self.world_size
+                    _lib.check(lib.wb200_copy_2d(out.peers[r] + off, out.row_bytes, out.ptr + off, out.row_bytes, width, out.M, stream))
+        if self.world_size > 1:
+            dist.all_reduce(out._flag, group=self.group)  # stream-ordered: every rank's copies have landed
+        return out.tensor
+
     def slot_buffer(self, M: int, device) -> torch.Tensor:
         """[world, M, widest shard] buffer of the output type; rank r's GEMM result belongs in slot r."""
         wmax = max(n1 - n0 for n0, n1 in self.bounds)
@@ -124,6 +150,64 @@ class ShardedScaledGemm:
                 if n1 > n0:
                     full[:, n0:n1].copy_(stacked[r][:, : n1 - n0])
         return full
+
+
+class _DeviceArray:
+    """Lets torch view device memory it did not allocate (a buffer made by wb200_peer_buffer_create)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class SharedOutput:
+    """An [M, N] output matrix per rank that the OTHER ranks can write: allocated by the library (cudaMalloc, so that
+    it can be exported), exchanged as CUDA IPC handles, mapped by every peer. `ShardedScaledGemm.push_blocks` uses
+    it to build the full C on every rank with nothing but copy-engine copies: every rank computes its column block
+    in place and copies it into the same columns of every other rank's matrix. Collective to create and to close."""
+
+    def __init__(self, M: int, N: int, torch_dtype: torch.dtype, device, group=None):
+        import ctypes
+        from . import _lib
+        self.M, self.N, self.dtype, self.group = M, N, torch_dtype, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device)
+        esz = torch.empty(0, dtype=torch_dtype).element_size()
+        self.row_bytes = N * esz
+        lib = _lib.load()
+        handle = ctypes.create_string_buffer(64)
+        base = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.wb200_peer_buffer_create(M * N * esz, ctypes.byref(base), handle))
+        self.ptr = base.value
+        self._opened = []
+        self.peers = [self.ptr] * self.world  # base address of every rank's matrix as seen from this process
+        if self.world > 1:
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, handle.raw, group=group)
+            with torch.cuda.device(self.device):
+                for r in range(self.world):
+                    if r == self.rank:
+                        continue
+                    p = ctypes.c_void_p()
+                    _lib.check(lib.wb200_peer_buffer_open(ctypes.create_string_buffer(gathered[r], 64), ctypes.byref(p)))
+                    self._opened.append(p.value)
+                    self.peers[r] = p.value
+        words = {2: "<i2", 4: "<f4"}[esz]
+        t = torch.as_tensor(_DeviceArray(self.ptr, (M, N), words), device=self.device)
+        self.tensor = t.view(torch_dtype) if t.dtype != torch_dtype else t
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def close(self) -> None:
+        """Unmap the peers' matrices and free this rank's. Call on every rank, after a barrier; the tensor is dead afterwards."""
+        from . import _lib
+        lib = _lib.load()
+        for p in self._opened:
+            lib.wb200_peer_buffer_close(p)
+        self._opened = []
+        if self.ptr:
+            lib.wb200_peer_buffer_destroy(self.ptr)
+            self.ptr = None
 
 
 class KShardedScaledGemm:
