@@ -832,3 +832,19 @@ def test_overlap_previous_chain_gives_the_same_bits(shape):
         assert torch.equal(c.view(torch.int16), r.view(torch.int16))
     check_bf16(outs[0], orc.scaled_gemm(*probs[0]))
     ops.check_device_status()
+
+
+def test_run_bench_option_reports_kernel_time(tmp_path):
+    """options.run_bench: after the call the kernel is timed on the device and the report goes to
+    benchmark_results_file (the reference hands its module to a benchmark tool, compile.py:317-329)."""
+    import json
+    a, a_s, b, b_s = random_problem(128, 256, 512, seed=3)
+    kernel, options = wb.get_tagged_mxfp4_gemm((128, 256, 512), output_dtype=wb.bf16)
+    options.run_bench, options.benchmark_batch_size, options.benchmark_repetitions = True, 5, 3
+    options.benchmark_results_file = str(tmp_path / "bench.json")
+    gemm = wb.wave_compile(options, kernel)
+    c = torch.empty(128, 256, dtype=torch.bfloat16, device=DEV)
+    gemm(a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV), c)
+    check(c, a, a_s, b, b_s)
+    rep = json.loads((tmp_path / "bench.json").read_text())["benchmarks"][0]
+    assert rep["time_unit"] == "us" and rep["iterations"] == 3 and 0 < rep["min_time"] <= rep["real_time"] < 1e5

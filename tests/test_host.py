@@ -171,3 +171,22 @@ def test_native_shard_bounds_match_the_python_rule(lib):
     h = C.c_void_p()
     assert lib.wb200_multi_gpu_create(0, None, C.byref(h)) == _lib.WB200_ERR_INVALID_ARG
     assert lib.wb200_multi_gpu_num_devices(None) == 0 and lib.wb200_multi_gpu_destroy(None) == 0
+
+
+def test_profile_python_wrapper_times_the_host_side(capsys):
+    """options.profile_python_wrapper: warm-up calls, then the repetitions under timeit or cProfile, as the reference's
+    invoke_with_profile (wave_lang/kernel/wave/compile.py:341-365). Exercised on a stand-in for invoke: no GPU needed."""
+    from wave_b200 import compile as wc
+    calls = []
+    opts = wb.WaveCompileOptions(profile_python_wrapper=True, profile_python_cprofile=False, profile_python_warmup=2,
+                                 profile_python_repetitions=5)
+    assert wc.invoke_with_profile(opts, lambda x: calls.append(x) or "done", 7) == "done"
+    assert len(calls) == 2 + 5 + 1  # warm-up, timed, and the call whose result is returned
+    assert "per iteration" in capsys.readouterr().out
+    opts.profile_python_cprofile = True
+    calls.clear()
+    wc.invoke_with_profile(opts, lambda x: calls.append(x), 7)
+    assert len(calls) == 2 + 5 and "cumulative" in capsys.readouterr().out
+    kernel, options = wb.get_tagged_mxfp4_gemm((64, 64, 64))
+    options.profile_python_wrapper = True
+    assert isinstance(wb.wave_compile(options, kernel), wc.ScaledGemmKernelWithProfile)

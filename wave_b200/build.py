@@ -27,12 +27,18 @@ def needs_build() -> bool:
     return any(p.stat().st_mtime > t for p in SOURCES + HEADERS)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources. Returns its path."""
-    if not force and not needs_build():
+TRACE_OUT = PKG / "libwave_b200_trace.so"
+
+
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Path:
+    """Compile the library if it is missing or older than its sources. Returns its path.
+    `trace`: the measurement variant with per-CTA timeline marks in the skinny kernel (-DWB200_TRACE), written to
+    libwave_b200_trace.so; load it with WAVE_B200_LIB=... (see `python -m wave_b200.perf --timeline`)."""
+    out = TRACE_OUT if trace else OUT
+    if not trace and not force and not needs_build():
         return OUT
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, "-o", str(OUT), *map(str, SOURCES)]
+    cmd = [nvcc, *NVCC_FLAGS, *(["-DWB200_TRACE"] if trace else []), "-o", str(out), *map(str, SOURCES)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -42,8 +48,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
     if verbose:
         print(res.stderr)
-    return OUT
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

@@ -55,6 +55,9 @@ class WaveCompileOptions:
     benchmark_repetitions: Optional[int] = None
     benchmark_results_file: Optional[str] = None
     profile_python_wrapper: bool = False
+    profile_python_cprofile: bool = True  # False: timeit instead of cProfile
+    profile_python_warmup: int = 1
+    profile_python_repetitions: int = 1000
     # performance options (no effect unless noted)
     wave_runtime: bool = True
     use_buffer_ops: bool = False
@@ -126,6 +129,14 @@ class ScaledGemmKernel:
         return self.invoke(*args)
 
     def invoke(self, a, a_scale, b, b_scale, c) -> None:
+        if self.options.run_bench and not getattr(self, "_in_bench", False):
+            self._in_bench = True
+            try:
+                self.invoke(a, a_scale, b, b_scale, c)
+                run_bench(self.options, self.invoke, a, a_scale, b, b_scale, c)
+            finally:
+                self._in_bench = False
+            return None
         # Fast path: plain tensors whose (shape, dtype, stride, device) signature was validated before.
         # The signature check is what stands between the caller and the C ABI on every call, so it is
         # done once per distinct signature and remembered.
@@ -262,6 +273,68 @@ class ScaledGemmKernel:
         return ops.repack_scales(a_scale, out=self._a_scale_buffer(a_scale.device, M, K))
 
 
+def invoke_with_profile(options: WaveCompileOptions, invoke, *args, **kwargs):
+    """Measure the HOST side of a call, as the reference does for its own wrapper
+    (wave_lang/kernel/wave/compile.py:341-365): `profile_python_warmup` untimed calls, then
+    `profile_python_repetitions` calls under cProfile (statistics printed, sorted by cumulative time) or, with
+    `profile_python_cprofile` off, under timeit (one "Time: ...s, ...s per iteration" line). For a decode-shaped GEMM
+    the wrapper costs about as much as the kernel runs, which is what this is for. Launches are asynchronous, so
+    what is measured is argument checking, marshalling and the launch calls, not GPU time."""
+    for _ in range(options.profile_python_warmup):
+        invoke(*args, **kwargs)
+    repetitions = options.profile_python_repetitions
+    if options.profile_python_cprofile:
+        import cProfile
+
+        with cProfile.Profile() as pr:
+            for _ in range(repetitions):
+                res = invoke(*args, **kwargs)
+        pr.print_stats(sort="cumulative")
+        return res
+    import timeit
+
+    seconds = timeit.timeit(lambda: invoke(*args, **kwargs), number=repetitions)
+    print(f"Time: {seconds:.3f}s, {seconds / repetitions:.6f}s per iteration")
+    return invoke(*args, **kwargs)
+
+
+class ScaledGemmKernelWithProfile(ScaledGemmKernel):
+    """What `wave_compile` returns when `options.profile_python_wrapper` is set (the reference's
+    WaveKernelWithProfile, wave_lang/kernel/wave/compile.py:368-371)."""
+
+    def __call__(self, *args, **kwargs):
+        return invoke_with_profile(self.options, self.invoke, *args, **kwargs)
+
+
+def run_bench(options: WaveCompileOptions, invoke, *args) -> dict:
+    """`options.run_bench`: time the kernel on the device after the call, as the reference does by handing the compiled
+    module to its benchmark tool (wave_lang/kernel/wave/compile.py:317-329): `benchmark_repetitions` (default 10)
+    batches of `benchmark_batch_size` (default 20) launches between CUDA events; the result, in the shape of that
+    tool's report, goes to `benchmark_results_file` or is printed."""
+    import json
+
+    batch = options.benchmark_batch_size or 20
+    reps = options.benchmark_repetitions or 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(reps):
+        e0.record()
+        for _ in range(batch):
+            invoke(*args)
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / batch)
+    result = {"benchmarks": [{"name": options.func_name, "real_time": sum(times) / len(times), "min_time": min(times),
+                              "time_unit": "us", "iterations": reps, "batch_size": batch}]}
+    text = json.dumps(result, sort_keys=True, indent=4)
+    if options.benchmark_results_file:
+        with open(options.benchmark_results_file, "w") as f:
+            f.write(text)
+    else:
+        print(text)
+    return result
+
+
 def wave_compile(options: WaveCompileOptions, kernel, schedule=None) -> ScaledGemmKernel:
     """wave_lang/kernel/wave/compile.py:1021: (options, kernel[, schedule]) -> callable.
     `schedule` objects from wave_b200.schedules are accepted and have no effect."""
@@ -281,4 +354,5 @@ def wave_compile(options: WaveCompileOptions, kernel, schedule=None) -> ScaledGe
         if kernel.element_bits != 4 or kernel.broadcast_a_scale or kernel.preshuffled_scales:
             raise ValueError("the multi-device form serves the plain MXFP4 scaled-GEMM templates")
         return MultiDeviceScaledGemm(kernel, options)
-    return ScaledGemmKernel(kernel, options)
+    cls = ScaledGemmKernelWithProfile if options.profile_python_wrapper else ScaledGemmKernel
+    return cls(kernel, options)

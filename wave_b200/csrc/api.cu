@@ -1288,6 +1288,18 @@ int wb200_peer_buffer_destroy(void* ptr) {
   return WB200_OK;
 }
 
+#ifdef WB200_TRACE
+// Measurement builds only (-DWB200_TRACE): copies the skinny kernel's per-CTA timeline of the last launch on the
+// current device into `out` (8-byte words; returns the number of words per CTA, 0 on error). See skinny_sm100.cuh.
+int wb200_trace_read(unsigned long long* out, int max_ctas) {
+  if (!out || max_ctas <= 0 || max_ctas > 256) return 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return 0;
+  if (cudaMemcpyFromSymbol(out, wb::g_skinny_trace, sizeof(unsigned long long) * size_t(max_ctas) * wb::kTraceWords) != cudaSuccess)
+    return 0;
+  return wb::kTraceWords;
+}
+#endif
+
 int wb200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows, void* stream) {
   if (!dst || !src || width_bytes == 0 || rows == 0 || dst_pitch < width_bytes || src_pitch < width_bytes)
     return fail(WB200_ERR_INVALID_ARG, "copy_2d: null pointer, empty copy or a pitch smaller than the row width");

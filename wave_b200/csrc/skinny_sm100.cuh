@@ -23,6 +23,28 @@
 
 namespace wb {
 
+// Per-CTA timeline of a launch, compiled in with -DWB200_TRACE only (`python -m wave_b200.build --trace`): a
+// measurement aid that writes globaltimer marks to a device array which wb200_trace_read copies out. Words per CTA:
+// [0] entry, [1] exit, [2] segments, [3] first stage landed, [4] first ring of loads issued, then per segment (up to
+// kTraceSegments): tile, last stage landed, accumulator seen complete by the epilogue, epilogue done (bit 62: this CTA
+// knew it was last and reduced from registers; bit 63: whole tile).
+#ifdef WB200_TRACE
+constexpr int kTraceSegments = 8;
+constexpr int kTraceHead = 8;
+constexpr int kTraceWords = kTraceHead + 4 * kTraceSegments;
+__device__ unsigned long long g_skinny_trace[256 * kTraceWords];
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define WB_TRACE_SET(idx, val) do { g_skinny_trace[size_t(blockIdx.x) * kTraceWords + (idx)] = (val); } while (0)
+#define WB_TRACE_SEG(seg, field, val) do { if ((seg) < kTraceSegments) g_skinny_trace[size_t(blockIdx.x) * kTraceWords + kTraceHead + 4 * (seg) + (field)] = (val); } while (0)
+#else
+#define WB_TRACE_SET(idx, val) do { } while (0)
+#define WB_TRACE_SEG(seg, field, val) do { } while (0)
+#endif
+
 // EB: bits per operand element, 4 (MXFP4) or 8 (MXFP8); a stage is one 128-byte swizzle row of every operand row
 // either way: 256 or 128 K elements, 2 or 1 scale-factor atoms per 128 rows.
 template <int NP_, int STAGES_, int EB = 4>
@@ -89,6 +111,9 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   pdl_launch_dependents();  // a kernel launched behind this one as a programmatic dependent may take SMs as they free up
+#ifdef WB200_TRACE
+  if (threadIdx.x == 0) WB_TRACE_SET(0, trace_now());
+#endif
 
   const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -187,6 +212,9 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     } else {
       produce(STAGES, false, 0);
     }
+#ifdef WB200_TRACE
+    if (lane == 0) { WB_TRACE_SET(4, trace_now()); WB_TRACE_SET(2, (unsigned long long)nseg); }
+#endif
   }
   if (warp == 1) {
     tmem_alloc<1>(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -219,6 +247,12 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (++sf_set == Cfg::SF_SETS) sf_set = 0;
         mbar_wait(full_bar(stage), phase, ctx, WB_DEV_TIMEOUT_MMA_FULL);
         tc_fence_after_sync();
+#ifdef WB200_TRACE
+        if (lane == 0) {
+          if (seg == 0 && kb == kbs) WB_TRACE_SET(3, trace_now());
+          if (kb == kbe - 1) { WB_TRACE_SEG(seg, 0, (unsigned long long)tile); WB_TRACE_SEG(seg, 1, trace_now()); }
+        }
+#endif
         const uint32_t sW = smem_base + stage * Cfg::STAGE_BYTES;
         const uint32_t sX = sW + Cfg::W_BYTES;
         const uint32_t sSFW = sX + Cfg::X_BYTES;
@@ -324,6 +358,9 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
       mbar_wait(acc_full_bar(as), uint32_t(seg >> 1) & 1u, ctx, WB_DEV_TIMEOUT_EPILOGUE);
       tc_fence_after_sync();
+#ifdef WB200_TRACE
+      if (threadIdx.x == 64) WB_TRACE_SEG(seg, 2, trace_now());
+#endif
       const uint32_t t_acc = tmem_base + (uint32_t(quad * 32) << 16) + (as ? Cfg::ACC_COL1 : 0);
 #pragma unroll 1
       for (int c0 = 0; c0 < NP; c0 += 16) {
@@ -422,6 +459,9 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is reused by the next segment
       }
+#ifdef WB200_TRACE
+      if (threadIdx.x == 64) WB_TRACE_SEG(seg, 3, trace_now() | (known_last ? (1ull << 62) : 0ull) | (whole ? (1ull << 63) : 0ull));
+#endif
     }
   }
 
@@ -432,6 +472,9 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     tc_fence_after_sync();
     tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
   }
+#ifdef WB200_TRACE
+  if (threadIdx.x == 0) WB_TRACE_SET(1, trace_now());
+#endif
 }
 
 }  // namespace wb

@@ -305,6 +305,63 @@ def time_k_sharded(M=8192, N=8192, k_per_rank=8192, iters=20):
     dist.destroy_process_group()
 
 
+def skinny_timeline(M: int, N: int, K: int, launches: int = 12, save: str | None = None, device="cuda:0"):
+    """Per-CTA timeline of the skinny kernel (M <= 128), from the marks of the measurement build of the library:
+    build it with `python -m wave_b200.build --trace` and run
+    `WAVE_B200_LIB=wave_b200/libwave_b200_trace.so python -m wave_b200.perf --timeline M N K`.
+    Launches rotate over three weight sets (nothing in L2) and are synchronised one by one, so the figures describe
+    an isolated cold launch. Prints microseconds after the first CTA's entry: min / median / max over the CTAs."""
+    import ctypes
+
+    import numpy as np
+
+    from . import _lib, ops
+    lib = _lib.load()
+    if not hasattr(lib, "wb200_trace_read"):
+        raise SystemExit("this library has no timeline marks: build with `python -m wave_b200.build --trace` and set WAVE_B200_LIB to it")
+    lib.wb200_trace_read.restype = ctypes.c_int
+    lib.wb200_trace_read.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    dev = torch.device(device)
+    sets = []
+    for i in range(3):
+        g = torch.Generator(device=dev).manual_seed(100 + i)
+        a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev, generator=g)
+        b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
+        a_s = torch.randint(124, 128, (M, K // 32), dtype=torch.uint8, device=dev, generator=g)
+        b_s = torch.randint(124, 128, (N, K // 32), dtype=torch.uint8, device=dev, generator=g)
+        sets.append((a, ops.repack_scales(a_s), b, ops.repack_scales(b_s), torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+    ctas = torch.cuda.get_device_properties(dev).multi_processor_count
+    records = []
+    for it in range(launches):
+        a, a_sf, b, b_sf, c = sets[it % 3]
+        ops.scaled_gemm_packed(a, a_sf, b, b_sf, c, _lib.PATH_SKINNY)
+        buf = np.zeros(ctas * 64, dtype=np.uint64)
+        words = lib.wb200_trace_read(buf.ctypes.data, ctas)
+        if words <= 0:
+            raise SystemExit("wb200_trace_read failed")
+        records.append(buf[: ctas * words].reshape(ctas, words).astype(np.int64))
+    ops.check_device_status()
+    if save:
+        np.save(save, np.stack(records))
+
+    def stats(x):
+        return f"{x.min():7.2f} {np.median(x):7.2f} {x.max():7.2f}"
+
+    print(f"M={M} N={N} K={K}: us after the first CTA's entry, min / median / max over the CTAs that ran (last {min(4, launches)} launches)")
+    for r in records[-4:]:
+        live = r[:, 0] > 0
+        r = r[live]
+        t0 = r[:, 0].min()
+        nseg = np.clip(r[:, 2], 1, 8)
+        last = 8 + 4 * (nseg - 1)
+        rows = np.arange(r.shape[0])
+        landed = (r[rows, last + 1] - t0) / 1e3
+        done = ((r[rows, last + 3] & ((1 << 62) - 1)) - t0) / 1e3
+        print(f"  entry {stats((r[:, 0] - t0) / 1e3)} | first ring issued {stats((r[:, 4] - t0) / 1e3)} | first stage landed {stats((r[:, 3] - t0) / 1e3)}"
+              f" | last stage landed {stats(landed)} | last epilogue done {stats(done)} | exit {stats((r[:, 1] - t0) / 1e3)}")
+    return records
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--validate", action="store_true")
@@ -314,7 +371,13 @@ def main(argv=None):
     ap.add_argument("--compare-cublaslt", action="store_true", help="context: time cuBLASLt's block-scaled FP4 GEMM on the same operands")
     ap.add_argument("--k-sharded", action="store_true", help="under torchrun: time the K-sharded GEMM against GEMM + NCCL reduce-scatter")
     ap.add_argument("--moe", action="store_true", help="time the steps of the MXFP4 expert MLP instead of the shape sweep")
+    ap.add_argument("--timeline", nargs=3, type=int, metavar=("M", "N", "K"),
+                    help="per-CTA timeline of the skinny kernel (needs the --trace build of the library, see skinny_timeline)")
+    ap.add_argument("--save", default=None, help="with --timeline: write the raw marks to this .npy file")
     args = ap.parse_args(argv)
+    if args.timeline:
+        skinny_timeline(*args.timeline, save=args.save)
+        return
     if args.moe:
         time_moe(iters=args.iters)
         return
