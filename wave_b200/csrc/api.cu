@@ -8,6 +8,7 @@
 #include "quantize.cuh"
 #include "scales.cuh"
 #include "skinny_sm100.cuh"
+#include "skinny_whole_sm100.cuh"
 
 #include <cudaTypedefs.h>
 #include <cstdarg>
@@ -600,10 +601,76 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   return WB200_OK;
 }
 
+// Whole N tiles taken from an atomic counter instead of a K split (skinny_whole_sm100.cuh), when there is at least one
+// tile per SM. For M > 16 always: the K-split kernel's partial tiles (M x 128 f32 each) cost more than any imbalance
+// (M = 128: 24.6 us against 29.4 us even at 150 tiles, where only two tiles are left for the second round). For M <= 16
+// only when the tiles left over after the full rounds are none, or at least half a round, or a small part of the whole:
+// a few stragglers alone run at one SM's bandwidth (150 tiles: 21.9 us whole against 19.2 us K-split; 185 tiles: 22.5
+// against 19.9; 224 tiles: 23.3 against 24.9; 148 tiles: 15.7 against 16.4).
+bool skinny_takes_whole_tiles(int sm_count, int M, int N) {
+  const int tiles = (N + 127) / 128, rest = tiles % sm_count;
+  if (tiles < sm_count) return false;
+  if (M > 16) return true;
+  return rest == 0 || rest * 2 >= sm_count || tiles >= 4 * sm_count;
+}
+
+template <int NP, int STAGES, typename OutT, int EB = 4>
+int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
+                        const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream,
+                        int elem_format = 0) {
+  using Base = wb::SkinnyCfg<NP, STAGES, EB>;
+  using Cfg = wb::SkinnyWholeCfg<NP, STAGES, EB>;
+  CUtensorMap tmW, tmX, tmSFW, tmSFX;
+  const long long row_bytes = (long long)K * EB / 8;
+  int rc = make_operand_map(&tmW, b, N, row_bytes, 128);
+  if (rc) return rc;
+  rc = make_operand_map(&tmX, a, M, row_bytes, NP);
+  if (rc) return rc;
+  rc = make_scale_map(&tmSFW, bs, wb::sf_row_blocks(N), wb::sf_k_atoms(K), 1, Base::SF_ATOMS);
+  if (rc) return rc;
+  rc = make_scale_map(&tmSFX, as, 1, wb::sf_k_atoms(K), 1, Base::SF_ATOMS);
+  if (rc) return rc;
+  wb::SkinnyWholeParams p;
+  p.c = c;
+  p.counters = static_cast<unsigned int*>(ws);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = int(ldc);
+  p.tiles_n = (N + 127) / 128;
+  p.num_kb = (K + Base::BK - 1) / Base::BK;
+  p.accumulate = accumulate;
+  p.dependent = tl_dependent_launch ? 1 : 0;
+  p.elem_format = elem_format;
+  p.c_vec = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * (long long)sizeof(OutT)) % 16 == 0) ? 1 : 0;
+  p.status = dev.status_ptr;
+  auto kernel = wb::mxfp4_skinny_whole_kernel<NP, STAGES, OutT, EB>;
+  static bool smem_set[kMaxDevices] = {};
+  rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
+  if (rc) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(dev.sm_count, 1, 1);  // one CTA per SM; every CTA's first tile is its own index (tiles >= SMs)
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tl_dependent_launch ? 1 : 0;
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmW, tmX, tmSFW, tmSFX, p));
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+}
+
 template <typename OutT, int EB = 4>
 int dispatch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                     const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream,
                     int elem_format = 0) {
+  if (skinny_takes_whole_tiles(dev.sm_count, M, N)) {
+    if (M <= 16) return launch_skinny_whole<16, 10, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+    if (M <= 32) return launch_skinny_whole<32, 9, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+    if (M <= 64) return launch_skinny_whole<64, 8, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+    return launch_skinny_whole<128, 6, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+  }
   if (M <= 16) return launch_skinny<16, 10, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
   if (M <= 32) return launch_skinny<32, 9, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
   if (M <= 64) return launch_skinny<64, 8, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
@@ -1193,9 +1260,8 @@ int wb200_mxfp4_gemm_skinny_noalloc(int M, int N, int K, const void* a, const vo
   rc = noalloc_scratch(&scratch);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // The array keeps whatever the previous call left; the tile counters must start at zero.
-  const size_t counter_bytes = size_t((N + 127) / 128) * sizeof(unsigned int);
-  WB_CUDA(cudaMemsetAsync(scratch, 0, counter_bytes, s));
+  // The array keeps whatever the previous call left; the counters at its head must start at zero.
+  WB_CUDA(cudaMemsetAsync(scratch, 0, kCounterBytes, s));
   const int accumulate = (flags & WB200_ACCUMULATE) ? 1 : 0;
   if (c_dtype == WB200_F32)
     return dispatch_skinny<float>(*dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc, scratch, accumulate, s);
