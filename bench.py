@@ -50,7 +50,8 @@ FALLBACK_HBM_GBS = 6650.0
 # kernel was captured: the figure describes that kernel, not necessarily the one timed now.
 NCU_TRAFFIC = {
     "c2": {"bytes": 201.6e6, "kernel": "mxfp4_gemm_kernel<2,256,bf16>", "captured_at_commit": "42ea90d"},
-    "c3": {"bytes": 130.7e6, "kernel": "mxfp4_skinny_kernel<16,10,bf16>", "captured_at_commit": "d7dae49"},
+    "c3": {"bytes": 128.6e6, "kernel": "mxfp4_skinny_whole_kernel<16,10,bf16>", "captured_at_commit": "53ffb24"},
+    "c3_m128": {"bytes": 128.9e6, "kernel": "mxfp4_skinny_whole_kernel<128,6,bf16>", "captured_at_commit": "53ffb24"},
 }
 
 WORKLOADS = {
@@ -58,6 +59,8 @@ WORKLOADS = {
                desc="C2 prefill projection: MXFP4 GEMM M=N=K=8192, block 32, operands quantised from seeded N(0,1), bf16 out"),
     "c3": dict(M=16, N=28672, K=8192, std_b=0.02, seed_a=1003, seed_b=2003,
                desc="C3 decode: MXFP4 GEMM M=16, N=28672, K=8192, weights from N(0,0.02), activations from N(0,1), bf16 out"),
+    "c3_m128": dict(M=128, N=28672, K=8192, std_b=0.02, seed_a=1003, seed_b=2003,
+                    desc="C3 decode shape at the top of the M <= 128 range: MXFP4 GEMM M=128, N=28672, K=8192, bf16 out"),
 }
 DECODE = dict(N=28672, K=8192, Ms=(1, 4, 16, 64, 128), std_b=0.02, seed_a=1003, seed_b=2003)
 SHARDED = dict(M=16384, N=53248, K=16384, seed_a=1005, seed_b=2005, block=6656)

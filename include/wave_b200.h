@@ -58,10 +58,22 @@ extern "C" {
 
 #define WB200_OVERLAP_PREVIOUS 0x80u /* the caller asserts that b and b_scale_packed are NOT written by the kernel that
                                      precedes this call in the stream: the GEMM is then launched as a programmatic
-                                     dependent of that kernel, so that its set-up and first weight loads overlap the
-                                     kernel's tail; everything else (a, scales of a, c, workspace) is touched only after
-                                     the preceding kernel has completed. Back-to-back GEMMs of a decode loop overlap
-                                     their tails and heads this way. */
+                                     dependent of that kernel. On the skinny path (M <= 128) its set-up AND the first
+                                     ring of weight loads overlap that kernel's tail; on the tile paths only the set-up
+                                     (barriers, tensor-memory allocation, descriptor prefetch) does, and every load
+                                     waits for the preceding kernel. Everything else (a, scales of a, c, workspace) is
+                                     touched only after the preceding kernel has completed. Back-to-back GEMMs of a
+                                     decode loop overlap their tails and heads this way. */
+/* Tile order of the tile paths: output tiles are visited in groups of g N tiles (256 columns each, 128 / 192 with the
+ * narrower tiles), each group swept down M with N fastest, so that the CTAs running at one time share few b tiles
+ * and all of a group's a tiles in L2. This is the templates' `reorder_workgroups` / `group_size_n` pair
+ * (tagged_mxfp4_gemm.py:38-60 and its _reorder_mxfp4_workgroups). g = 1..254 in bits 8..15; 0 keeps the default
+ * (16); WB200_GROUP_N_ALL puts every N tile in one group, which is the plain row-major order the templates use
+ * with reorder_workgroups = False. The result does not depend on the order. */
+#define WB200_GROUP_N_SHIFT 8
+#define WB200_GROUP_N_MASK 0xFF00u
+#define WB200_GROUP_N(g) (((unsigned)(g) << WB200_GROUP_N_SHIFT) & WB200_GROUP_N_MASK)
+#define WB200_GROUP_N_ALL WB200_GROUP_N(255)
 
 /* Library version (major * 1000 + minor). */
 int wb200_version(void);

@@ -192,6 +192,38 @@ def test_skinny_path(M, N, K, out_dtype):
                        c2.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32))
 
 
+@pytest.mark.parametrize("shape", [(1024, 2304, 512), (640, 5120, 256)])
+def test_raster_group_changes_the_tile_order_not_the_result(shape):
+    """WB200_GROUP_N (the templates' reorder_workgroups / group_size_n): every group size gives the bits of the default."""
+    M, N, K = shape
+    a, a_s, b, b_s = random_problem(M, N, K, seed=4242)
+    ad, bd = a.to(DEV), b.to(DEV)
+    asp, bsp = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
+    for path in (_lib.PATH_TILE_1CTA, _lib.PATH_TILE_2CTA):
+        base = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.scaled_gemm_packed(ad, asp, bd, bsp, base, path)
+        check(base, a, a_s, b, b_s)
+        for group in (_lib.GROUP_N(1), _lib.GROUP_N(3), _lib.GROUP_N(32), _lib.GROUP_N(254), _lib.GROUP_N_ALL):
+            c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+            ops.scaled_gemm_packed(ad, asp, bd, bsp, c, path | group)
+            assert torch.equal(c.view(torch.int16), base.view(torch.int16))
+
+
+def test_template_group_size_reaches_the_kernel():
+    """get_tagged_mxfp4_gemm(group_size_n=..., reorder_workgroups=...) compiles to the matching raster flags and
+    still matches the oracle."""
+    M, N, K = 512, 2048, 512
+    a, a_s, b, b_s = random_problem(M, N, K, seed=77)
+    for kwargs, want in ((dict(group_size_n=4), _lib.GROUP_N(4)), (dict(group_size_n=8, block_shape=(256, 128, 256)), _lib.GROUP_N(4)),
+                         (dict(reorder_workgroups=False), _lib.GROUP_N_ALL), (dict(), 0)):
+        tpl, options = wb.templates.get_tagged_mxfp4_gemm((M, N, K), output_dtype=wb.bf16, **kwargs)
+        gemm = wb.wave_compile(options, tpl)
+        assert gemm._raster_flags() == want
+        c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        gemm(a.to(DEV), a_s.to(DEV), b.to(DEV), b_s.to(DEV), c)
+        check(c, a, a_s, b, b_s)
+
+
 def test_many_tiles_per_cta_and_accumulator_reuse():
     """More tiles than SMs on every path, so each CTA runs several tiles through both accumulators."""
     M, N, K = 2048, 6144, 512
@@ -375,10 +407,9 @@ def test_config3_decode_shapes_bf16(M):
     (16, 38000, 256, torch.bfloat16, False),    # one K block per tile: nothing to cut
 ])
 def test_skinny_path_with_dealt_parts(M, N, K, out_dtype, accumulate):
-    """Shapes with at least as many N tiles as SMs: whole static tiles plus main / closer parts taken from the
-    atomic work list, whoever arrives last at a tile adding the parts. Checked against the oracle; and because
-    which CTA computes which part varies from run to run while the parts and their order do not, repeated
-    launches must give the same bits."""
+    """Shapes with at least as many N tiles as SMs: the kernel that deals whole N tiles from an atomic counter.
+    Checked against the oracle; and because which CTA computes which tile varies from run to run while each
+    tile's sum over K does not, repeated launches must give the same bits."""
     a, a_s, b, b_s = random_problem(M, N, K, seed=M + N + K, lo=124, hi=128)
     ref = orc.scaled_gemm(a, a_s, b, b_s)
     ad, bd = a.to(DEV), b.to(DEV)

@@ -143,6 +143,25 @@ def test_tile_order_is_a_permutation_grouped_by_n():
             assert len({m for m, _ in seen[:g]}) == 1
 
 
+def test_raster_group_flags_follow_the_template_arguments():
+    header = (ROOT / "include" / "wave_b200.h").read_text()
+    assert re.search(r"#define WB200_GROUP_N_SHIFT 8\b", header) and re.search(r"#define WB200_GROUP_N_MASK 0xFF00u", header)
+    assert _lib.GROUP_N(1) == 0x100 and _lib.GROUP_N(254) == 0xFE00 and _lib.GROUP_N_ALL == 0xFF00
+    with pytest.raises(ValueError):
+        _lib.GROUP_N(255)
+    with pytest.raises(ValueError):
+        _lib.GROUP_N(0)
+    shape = (1024, 1024, 8192)
+    for kwargs, want in ((dict(), 0), (dict(group_size_n=32), _lib.GROUP_N(32)), (dict(group_size_n=1000), _lib.GROUP_N(254)),
+                         (dict(group_size_n=4, block_shape=(128, 128, 256)), _lib.GROUP_N(2)),
+                         (dict(group_size_n=1, block_shape=(128, 128, 256)), _lib.GROUP_N(1)),
+                         (dict(group_size_n=8, reorder_workgroups=False), _lib.GROUP_N_ALL)):
+        tpl, options = templates.get_tagged_mxfp4_gemm_preshuffle_b(shape, **kwargs)
+        assert wb.wave_compile(options, tpl)._raster_flags() == want
+    with pytest.raises(ValueError):
+        templates.get_tagged_mxfp4_gemm(shape, group_size_n=0)
+
+
 def test_perf_formulas_match_the_reference_benchmark_driver():
     """flops and byte counts of wave_lang/kernel/wave/perf/benchmark_mxfp4.py:78-92."""
     from wave_b200 import perf

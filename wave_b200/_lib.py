@@ -33,6 +33,15 @@ TILE_N128 = 0x10
 TILE_N192 = 0x40
 ACCUMULATE = 0x20
 OVERLAP_PREVIOUS = 0x80
+GROUP_N_MASK = 0xFF00
+GROUP_N_ALL = 0xFF00
+
+
+def GROUP_N(g: int) -> int:
+    """Flag bits for a raster group of g N tiles (1..254); include/wave_b200.h, WB200_GROUP_N."""
+    if not 1 <= int(g) <= 254:
+        raise ValueError(f"raster group of {g} N tiles: 1..254 fit the flag bits")
+    return int(g) << 8
 E4M3 = 0
 E5M2 = 1
 

@@ -183,7 +183,7 @@ class ScaledGemmKernel:
         a_sf = a_scale if isinstance(a_scale, ops.PackedScales) else self._pack_activation_scales(a_scale, M, K)
         b_sf = b_scale if isinstance(b_scale, ops.PackedScales) else self._weight_scales.get(self._check_scale(b_scale, N, K, "b_scale"))
         fmt = _lib.E5M2 if t.element_format == "f8e5m2" else _lib.E4M3
-        flags = self.options.kernel_path | (_lib.ACCUMULATE if t.accumulate else 0)
+        flags = self.options.kernel_path | self._raster_flags() | (_lib.ACCUMULATE if t.accumulate else 0)
         ops.scaled_gemm_mxfp8_packed(a, a_sf, b, b_sf, c, fmt, flags)
 
     def _invoke_checked(self, a, a_scale, b, b_scale, c) -> None:
@@ -220,7 +220,7 @@ class ScaledGemmKernel:
             a_scale = ops.repack_scales_broadcast(a_scale, K, out=self._a_scale_buffer(a.device, M, K))
         if t.preshuffled_scales and not (isinstance(a_scale, ops.PackedScales) and isinstance(b_scale, ops.PackedScales)):
             raise ValueError(f"{t.name} takes pre-shuffled scales: pass mxfp_utils.e8m0_shuffle(scale) for a_scale and b_scale")
-        flags = self.options.kernel_path
+        flags = self.options.kernel_path | self._raster_flags()
         if t.accumulate:
             flags |= _lib.ACCUMULATE
         if self.options.overlap_previous:
@@ -255,6 +255,19 @@ class ScaledGemmKernel:
         if tuple(s.shape) != (rows, K // ops.SCALE_GROUP_SIZE):
             raise ValueError(f"{name} must be [{rows}, {K // ops.SCALE_GROUP_SIZE}], got {tuple(s.shape)}")
         return s
+
+    def _raster_flags(self) -> int:
+        """The template's reorder_workgroups / group_size_n as the tile kernels' raster-group bits. The reference
+        counts groups in workgroups of BLOCK_N columns (tagged_mxfp4_gemm.py, _reorder_mxfp4_workgroups); the
+        tile kernels here walk 256-column tiles, so the group keeps its width in columns."""
+        h = self.template.hints
+        if not h.get("reorder_workgroups", True):
+            return _lib.GROUP_N_ALL
+        g = h.get("group_size_n")
+        if g is None:
+            return 0
+        block_n = int(h.get("block_shape", (256, 256, 256))[1])
+        return _lib.GROUP_N(max(1, min(254, (int(g) * block_n) // 256)))
 
     def _a_scale_buffer(self, device, M, K):
         idx = device.index or 0

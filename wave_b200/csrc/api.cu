@@ -129,6 +129,17 @@ CUresult encode_2d(CUtensorMap* map, const MapKey& k) {
 // WB200_OVERLAP_PREVIOUS. A dependent kernel starts while its predecessor drains and executes
 // griddepcontrol.wait before touching anything but the weights.
 static thread_local bool tl_dependent_launch = false;
+// N tiles per raster group of the tile kernels, from the WB200_GROUP_N bits of the call in progress
+static thread_local int tl_group_n = 16;
+static int group_n_from_flags(unsigned flags) {
+  const unsigned g = (flags & WB200_GROUP_N_MASK) >> WB200_GROUP_N_SHIFT;
+  return g == 0 ? 16 : g == 255 ? (1 << 20) : int(g);
+}
+struct GroupNScope {  // restores the previous value on every return path
+  int saved;
+  explicit GroupNScope(unsigned flags) : saved(tl_group_n) { tl_group_n = group_n_from_flags(flags); }
+  ~GroupNScope() { tl_group_n = saved; }
+};
 
 // [rows, row_bytes] uint8 matrix (rows pitch_bytes apart; 0 = dense), box = 128 bytes x box_rows, 128-byte swizzle, zero fill.
 int make_operand_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_rows,
@@ -231,7 +242,7 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   p.ldc = int(ldc);
   p.tiles_m = (M + Cfg::BM * CG - 1) / (Cfg::BM * CG);
   p.tiles_n = (N + BN - 1) / BN;
-  p.group_n = 16;
+  p.group_n = std::max(1, std::min(tl_group_n, p.tiles_n));
   const int esz = int(sizeof(OutT));
   p.vec_ok = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * esz) % 16 == 0) ? 1 : 0;
   p.accumulate = accumulate;
@@ -340,7 +351,7 @@ int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets
   p.ldc = int(ldc);
   p.tiles_m = 0;
   p.tiles_n = tiles_n;
-  p.group_n = 16;
+  p.group_n = std::max(1, std::min(tl_group_n, p.tiles_n));
   p.vec_ok = 1;
   p.tma_store = store_mode;
   p.accumulate = 0;
@@ -403,7 +414,7 @@ int launch_aligned(const DeviceInfo& dev, int num_groups, int max_rows, const in
   p.ldc = int(ldc);
   p.tiles_m = maps.tiles_m_cap;
   p.tiles_n = (N + BN - 1) / BN;
-  p.group_n = 16;
+  p.group_n = std::max(1, std::min(tl_group_n, p.tiles_n));
   p.vec_ok = 1;
   p.tma_store = 1;
   p.accumulate = 0;
@@ -513,7 +524,7 @@ int launch_splitk(const DeviceInfo& dev, int slices, int M, int N, int K, const 
   p.ldc = N;
   p.tiles_m = tiles_m;
   p.tiles_n = tiles_n;
-  p.group_n = 16;
+  p.group_n = std::max(1, std::min(tl_group_n, p.tiles_n));
   p.vec_ok = 1;
   p.tma_store = 1;
   p.accumulate = 0;
@@ -1101,8 +1112,9 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   unsigned path = flags & WB200_PATH_MASK;
-  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_TILE_N192 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS)) != 0)
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_TILE_N192 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS | WB200_GROUP_N_MASK)) != 0)
     return fail(WB200_ERR_INVALID_ARG, "unknown flag bits %#x", flags);
+  GroupNScope group_scope(flags);
   // restores the previous value on every return path
   struct DependentScope {
     bool saved;
@@ -1200,8 +1212,9 @@ int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   if (rc) return rc;
   if (elem_format != WB200_E4M3 && elem_format != WB200_E5M2)
     return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown element format %d", elem_format);
-  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS)) != 0)
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS | WB200_GROUP_N_MASK)) != 0)
     return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown flag bits %#x", flags);
+  GroupNScope group_scope(flags);
   struct DependentScope {  // restores the previous value on every return path
     bool saved;
     explicit DependentScope(bool on) : saved(tl_dependent_launch) { if (on) tl_dependent_launch = true; }

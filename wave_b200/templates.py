@@ -87,11 +87,16 @@ def get_scaled_gemm_mxfp8_kernel(shape, mfma_variant: ScaledMMAType, element_for
     return tpl, _hyperparams(shape, (32, 32, 256), {"ADDRESS_SPACE": SHARED_ADDRESS_SPACE})
 
 
-def _tagged(name, shape, block_shape, wave_shape, mfma_variant, output_dtype, **flags):
+def _tagged(name, shape, block_shape, wave_shape, mfma_variant, output_dtype, reorder_workgroups=True,
+            group_size_n=None, **flags):
     out = as_output_dtype(output_dtype)
-    tpl = ScaledGemmTemplate(name, tuple(shape), out,
-                             hints={"mfma_variant": mfma_variant, "block_shape": tuple(block_shape),
-                                    "wave_shape": tuple(wave_shape)}, **flags)
+    hints = {"mfma_variant": mfma_variant, "block_shape": tuple(block_shape), "wave_shape": tuple(wave_shape),
+             "reorder_workgroups": bool(reorder_workgroups)}
+    if group_size_n is not None:
+        if int(group_size_n) < 1:
+            raise ValueError(f"group_size_n must be at least 1, got {group_size_n}")
+        hints["group_size_n"] = int(group_size_n)
+    tpl = ScaledGemmTemplate(name, tuple(shape), out, hints=hints, **flags)
     options = WaveCompileOptions(subs=_hyperparams(shape, block_shape), canonicalize=True,
                                  schedule=SchedulingType.MANUAL, use_global_to_shared=True,
                                  minimize_shared_allocs=False)
@@ -100,19 +105,27 @@ def _tagged(name, shape, block_shape, wave_shape, mfma_variant, output_dtype, **
 
 def get_tagged_mxfp4_gemm(shape=(1024, 1024, 8192), block_shape=(256, 256, 256), wave_shape=(2, 2),
                           mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4, a_address_space=SHARED_ADDRESS_SPACE,
-                          b_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True, group_size_n=32,
+                          b_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True, group_size_n=None,
                           output_dtype=f32):
-    """(kernel, options); f32 or bf16 output — wave_lang/kernel/wave/templates/tagged_mxfp4_gemm.py:38-145."""
-    return _tagged("tagged_mxfp4_gemm", shape, block_shape, wave_shape, mfma_variant, output_dtype)
+    """(kernel, options); f32 or bf16 output — wave_lang/kernel/wave/templates/tagged_mxfp4_gemm.py:38-145.
+
+    `reorder_workgroups` / `group_size_n` set the order in which the tile kernels visit the output tiles, as in
+    the reference (groups of group_size_n workgroups along N, each swept down M): a group keeps its width in
+    columns, group_size_n * BLOCK_N. group_size_n = None (the default here; the reference's is 32, tuned for its
+    hardware) leaves the kernel's own group of 16 tiles of 256 columns; reorder_workgroups = False walks the
+    tiles row by row. The result does not depend on either."""
+    return _tagged("tagged_mxfp4_gemm", shape, block_shape, wave_shape, mfma_variant, output_dtype,
+                   reorder_workgroups, group_size_n)
 
 
 def get_tagged_mxfp4_gemm_preshuffle_scales(shape=(1024, 1024, 8192), block_shape=(256, 256, 256), wave_shape=(2, 2),
                                             mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
                                             a_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True,
-                                            group_size_n=32, output_dtype=f32):
+                                            group_size_n=None, output_dtype=f32):
     """Scales arrive pre-shuffled: pass the result of `mxfp_utils.e8m0_shuffle` for a_scale and b_scale
     (tagged_mxfp4_gemm.py:334-365). On B200 the shuffle is the tcgen05 scale-factor repack."""
     return _tagged("tagged_mxfp4_gemm_preshuffle_scales", shape, block_shape, wave_shape, mfma_variant, output_dtype,
+                   reorder_workgroups, group_size_n,
                    preshuffled_scales=True)
 
 
@@ -120,18 +133,19 @@ def get_tagged_mxfp4_gemm_preshuffle_scales_and_B(shape=(1024, 1024, 8192), bloc
                                                   wave_shape=(2, 2),
                                                   mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
                                                   a_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True,
-                                                  group_size_n=32, output_dtype=f32):
+                                                  group_size_n=None, output_dtype=f32):
     """tagged_mxfp4_gemm.py:368-403: pre-shuffled scales and pre-shuffled b."""
-    return _tagged("tagged_mxfp4_gemm_preshuffle_scales_and_B", shape, block_shape, wave_shape, mfma_variant,
-                   output_dtype, preshuffled_scales=True, preshuffled_b=True)
+    return _tagged("tagged_mxfp4_gemm_preshuffle_scales_and_B", shape, block_shape, wave_shape, mfma_variant, output_dtype,
+                   reorder_workgroups, group_size_n, preshuffled_scales=True, preshuffled_b=True)
 
 
 def get_tagged_mxfp4_gemm_preshuffle_b(shape=(1024, 1024, 8192), block_shape=(256, 256, 256), wave_shape=(2, 2),
                                        mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
                                        a_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True,
-                                       group_size_n=32, output_dtype=f32):
+                                       group_size_n=None, output_dtype=f32):
     """tagged_mxfp4_gemm.py:950-991."""
     return _tagged("tagged_mxfp4_gemm_preshuffle_b", shape, block_shape, wave_shape, mfma_variant, output_dtype,
+                   reorder_workgroups, group_size_n,
                    preshuffled_scales=True, preshuffled_b=True)
 
 
@@ -139,10 +153,10 @@ def get_tagged_mxfp4_gemm_preshuffle_b_wide_store(shape=(1024, 1024, 8192), bloc
                                                   wave_shape=(2, 2),
                                                   mfma_variant=ScaledMMAType.F32_16x16x128_F8F6F4,
                                                   a_address_space=SHARED_ADDRESS_SPACE, reorder_workgroups=True,
-                                                  group_size_n=32, output_dtype=f32):
+                                                  group_size_n=None, output_dtype=f32):
     """tagged_mxfp4_gemm.py:994-1035; every epilogue here already stores 16 bytes per thread."""
-    return _tagged("tagged_mxfp4_gemm_preshuffle_b_wide_store", shape, block_shape, wave_shape, mfma_variant,
-                   output_dtype, preshuffled_scales=True, preshuffled_b=True)
+    return _tagged("tagged_mxfp4_gemm_preshuffle_b_wide_store", shape, block_shape, wave_shape, mfma_variant, output_dtype,
+                   reorder_workgroups, group_size_n, preshuffled_scales=True, preshuffled_b=True)
 
 
 def _splitk(name, shape, num_splits, block_shape, wave_shape, mfma_variant, output_type, **flags):
