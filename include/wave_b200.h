@@ -93,6 +93,18 @@ int wb200_check_device_status(void* stream, int* detail);
  * The reference has no device-side waits to bound (its errors are host exceptions, runtime.cpp:96-109). */
 int wb200_selftest_wait_timeout(long long limit_cycles, void* stream);
 
+/* Debug-checked build. The reference's `use_bound_check` compile option guards memory accesses with bounds checks that
+ * print and halt (wave_lang/kernel/wave/analysis/generate_bound_checks.py:17-63). Here a second build of this library
+ * (compiled with -DWB200_CHECKS) tests an index predicate in front of every copy-engine issue and every global store of
+ * the GEMM kernels: innermost TMA coordinate and shared-memory alignment, output row / column inside c, workspace
+ * counter index. A failed predicate skips the access and is recorded; nothing traps. wb200_debug_checks synchronises
+ * the current device and returns record[0] = code | CTA << 32 of the first failure (0: none), record[1] = its detail
+ * word (the offending index), record[2] = number of failures since the last reset; reset != 0 clears the record.
+ * wb200_debug_checks_selftest launches one thread that fails a predicate by construction (code 99, detail 1) and skips
+ * the store behind it. Both return WB200_ERR_UNSUPPORTED from a library built without the flag. */
+int wb200_debug_checks(unsigned long long* record, int reset);
+int wb200_debug_checks_selftest(void* stream);
+
 /* Bytes of the packed scale array for a [rows, K/32] scale matrix. */
 size_t wb200_packed_scale_bytes(int rows, int K);
 

@@ -184,7 +184,9 @@ def quantize_mxfp4(x: torch.Tensor):
 
     Per 32-element block: e = floor(log2(amax)) - 2 (E2M1's largest value is 6 = 1.5 * 2^2), scale
     byte clamp(e + 127, 0, 254), amax == 0 -> e = 0; values x * 2^-e clamped to [-6, 6] and rounded
-    to the nearest E2M1 value, ties to the even code; low nibble = even k.
+    to the nearest E2M1 value, ties to the even code; low nibble = even k. A block that holds a NaN or an
+    infinity gets scale byte 255 (the E8M0 NaN that `e8m0_to_f32` reads back as NaN,
+    wave_lang/kernel/wave/utils/mxfp_utils.py:86-95; the OCP MX block rule) and codes 0.
     """
     R, K = x.shape
     assert K % SCALE_GROUP_SIZE == 0
@@ -197,11 +199,15 @@ def quantize_mxfp4(x: torch.Tensor):
     inclusive = (0.75, 1.75, 3.5)
     for r0 in range(0, R, 1024):
         xb = x[r0:r0 + 1024].reshape(-1, K // 32, 32).to(torch.float32)
+        bad = ~torch.isfinite(xb).all(dim=2)
+        xb = torch.where(bad.unsqueeze(2), torch.zeros_like(xb), xb)
         amax = xb.abs().amax(dim=2)
         e = torch.floor(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)))) - 2.0
         e = torch.where(amax > 0, e, torch.zeros_like(e))
         sb = torch.clamp(e + 127.0, 0, 254)
         y = torch.clamp(xb / torch.pow(two, sb - 127.0).unsqueeze(2), -6.0, 6.0)
+        y = torch.where(bad.unsqueeze(2), torch.zeros_like(y), y)  # +0: code 0 whatever the sign of the input
+        sb = torch.where(bad, torch.full_like(sb, 255.0), sb)
         mag = y.abs()
         idx = torch.zeros_like(mag, dtype=torch.uint8)
         for t in strict:

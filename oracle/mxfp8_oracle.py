@@ -48,14 +48,18 @@ def quantize_mxfp8(x: torch.Tensor, dtype=torch.float8_e5m2):
     tests/kernel/wave_gemm_mxfp_test.py:64-77); the block rule of the MXFP4 harness quantiser carried over:
     e = floor(log2(amax)) - emax_elem (8 for E4M3, whose largest value is 448 = 1.75 * 2^8; 15 for E5M2, 57344 =
     1.75 * 2^15), scale byte clamp(e + 127, 0, 254), amax == 0 -> 127; values x * 2^-e clamped to the largest
-    finite value and rounded to nearest even by the type conversion."""
+    finite value and rounded to nearest even by the type conversion. A block that holds a NaN or an infinity gets
+    scale byte 255 (E8M0's NaN) and zero codes, as in the MXFP4 quantiser."""
     R, K = x.shape
     assert K % SCALE_GROUP_SIZE == 0
     emax, vmax = (8, 448.0) if dtype == torch.float8_e4m3fn else (15, 57344.0)
     xb = x.reshape(R, K // 32, 32).to(torch.float32)
+    bad = ~torch.isfinite(xb).all(dim=2)
+    xb = torch.where(bad.unsqueeze(2), torch.zeros_like(xb), xb)
     amax = xb.abs().amax(dim=2)
     e = torch.floor(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)))) - float(emax)
     e = torch.where(amax > 0, e, torch.zeros_like(e))
     sb = torch.clamp(e + 127.0, 0, 254)
     y = torch.clamp(xb / torch.pow(torch.tensor(2.0), sb - 127.0).unsqueeze(2), -vmax, vmax)
+    sb = torch.where(bad, torch.full_like(sb, 255.0), sb)
     return y.reshape(R, K).to(dtype), sb.to(torch.uint8)

@@ -141,6 +141,23 @@ def test_quantize_mxfp8_bit_exact_and_feeds_the_gemm(dtype, rows, K, src):
         check(c, q_ref, s_ref, w, w_s)
 
 
+@pytest.mark.parametrize("dtype", [torch.float8_e5m2, torch.float8_e4m3fn])
+def test_quantize_mxfp8_marks_blocks_with_nan_or_inf(dtype):
+    """Scale byte 255 and zero codes for a block that holds a NaN or an infinity; other blocks bit-exact as before."""
+    rows, K = 33, 256
+    x = torch.randn(rows, K, generator=torch.Generator().manual_seed(8))
+    x[0, 5], x[7, 100], x[32, 255], x[9, 64] = float("nan"), float("inf"), float("-inf"), float("nan")
+    q, s, packed = ops.quantize_mxfp8(x.to(DEV), dtype)
+    q_ref, s_ref = orc8.quantize_mxfp8(x, dtype)
+    assert torch.equal(s.cpu(), s_ref) and torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+    assert torch.equal(packed.data.cpu(), orc.pack_scales(s_ref))
+    bad = torch.zeros(rows, K // 32, dtype=torch.bool)
+    for r, k in ((0, 5), (7, 100), (32, 255), (9, 64)):
+        bad[r, k // 32] = True
+    assert torch.equal(s.cpu() == 255, bad)
+    assert int(q.cpu().view(torch.uint8).reshape(rows, K // 32, 32)[bad].max()) == 0
+
+
 @pytest.mark.parametrize("M", [1, 16, 40, 100, 128])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (1000, 992), (4096, 384)])
 @pytest.mark.parametrize("out_dtype,elem", [(torch.float32, torch.float8_e5m2), (torch.bfloat16, torch.float8_e4m3fn)])

@@ -574,6 +574,36 @@ def test_quantizer_bit_exact_against_oracle(rows, K, dtype):
     assert torch.equal(packed.data.cpu(), orc.pack_scales(es))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_quantizer_marks_blocks_with_nan_or_inf(dtype):
+    """A NaN or an infinity in a block gives scale byte 255 (E8M0's NaN) and codes 0, bit-exact against the oracle;
+    read back through the reference's dequantisation rule the block is NaN, every other block is untouched, and a
+    GEMM on it returns NaN for the row instead of finite numbers."""
+    rows, K, N = 40, 512, 256
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(rows, K, generator=g)
+    planted = {(1, 40): float("nan"), (2, 70): float("-inf"), (3, 0): float("inf"), (39, 511): float("nan"), (5, 100): float("inf")}
+    x[5, 101] = float("nan")  # both kinds in one block
+    for (r, k), v in planted.items():
+        x[r, k] = v
+    x = x.to(dtype)
+    q, s, packed = wb.quantize_mxfp4(x.to(DEV))
+    eq, es = orc.quantize_mxfp4(x.float())
+    assert torch.equal(s.cpu(), es) and torch.equal(q.cpu(), eq)
+    assert torch.equal(packed.data.cpu(), orc.pack_scales(es))
+    bad = torch.zeros(rows, K // 32, dtype=torch.bool)
+    for (r, k) in planted:
+        bad[r, k // 32] = True
+    assert torch.equal(s.cpu() == 255, bad)
+    deq = orc.dequant_mxfp4(q.cpu(), s.cpu()).reshape(rows, K // 32, 32)
+    assert torch.equal(torch.isnan(deq).all(dim=2), bad) and torch.equal(torch.isnan(deq).any(dim=2), bad)
+    w, w_s = orc.quantize_mxfp4(torch.randn(N, K, generator=g))
+    c = torch.zeros(rows, N, dtype=torch.float32, device=DEV)
+    ops.scaled_gemm_packed(q, packed, w.to(DEV), ops.repack_scales(w_s.to(DEV)), c)
+    nan_rows = bad.any(dim=1)
+    assert torch.equal(torch.isnan(c).all(dim=1).cpu(), nan_rows) and torch.equal(torch.isnan(c).any(dim=1).cpu(), nan_rows)
+
+
 def test_mxfp4_linear_module_matches_oracle():
     torch.manual_seed(5)
     N, K = 768, 1024

@@ -51,6 +51,8 @@ EXPORTED_SYMBOLS = (
     "wb200_last_error",
     "wb200_check_device_status",
     "wb200_selftest_wait_timeout",
+    "wb200_debug_checks",
+    "wb200_debug_checks_selftest",
     "wb200_packed_scale_bytes",
     "wb200_repack_scales",
     "wb200_repack_scales_broadcast",
@@ -129,6 +131,10 @@ def load() -> ctypes.CDLL:
     lib.wb200_check_device_status.argtypes = [c_void_p, ctypes.POINTER(c_int)]
     lib.wb200_selftest_wait_timeout.restype = c_int
     lib.wb200_selftest_wait_timeout.argtypes = [c_ll, c_void_p]
+    lib.wb200_debug_checks.restype = c_int
+    lib.wb200_debug_checks.argtypes = [ctypes.POINTER(ctypes.c_ulonglong), c_int]
+    lib.wb200_debug_checks_selftest.restype = c_int
+    lib.wb200_debug_checks_selftest.argtypes = [c_void_p]
     lib.wb200_packed_scale_bytes.restype = c_size_t
     lib.wb200_packed_scale_bytes.argtypes = [c_int, c_int]
     lib.wb200_repack_scales.restype = c_int

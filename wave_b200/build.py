@@ -28,17 +28,25 @@ def needs_build() -> bool:
 
 
 TRACE_OUT = PKG / "libwave_b200_trace.so"
+CHECKS_OUT = PKG / "libwave_b200_checks.so"
 
 
-def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Path:
+def _stale(out: Path) -> bool:
+    return not out.exists() or any(p.stat().st_mtime > out.stat().st_mtime for p in SOURCES + HEADERS)
+
+
+def build(force: bool = False, verbose: bool = False, trace: bool = False, checks: bool = False) -> Path:
     """Compile the library if it is missing or older than its sources. Returns its path.
-    `trace`: the measurement variant with per-CTA timeline marks in the skinny kernel (-DWB200_TRACE), written to
-    libwave_b200_trace.so; load it with WAVE_B200_LIB=... (see `python -m wave_b200.perf --timeline`)."""
-    out = TRACE_OUT if trace else OUT
-    if not trace and not force and not needs_build():
-        return OUT
+    `trace`: the measurement variant with per-CTA timeline marks in the skinny kernels (-DWB200_TRACE), written to
+    libwave_b200_trace.so; load it with WAVE_B200_LIB=... (see `python -m wave_b200.perf --timeline`).
+    `checks`: the debug-checked variant (-DWB200_CHECKS: index predicates in front of every copy-engine issue and
+    global store, see csrc/checks.cuh), written to libwave_b200_checks.so."""
+    out = TRACE_OUT if trace else CHECKS_OUT if checks else OUT
+    if not force and not _stale(out):
+        return out
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, *(["-DWB200_TRACE"] if trace else []), "-o", str(out), *map(str, SOURCES)]
+    variant = ["-DWB200_TRACE"] if trace else ["-DWB200_CHECKS"] if checks else []
+    cmd = [nvcc, *NVCC_FLAGS, *variant, "-o", str(out), *map(str, SOURCES)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -52,4 +60,4 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Pa
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv, checks="--checks" in sys.argv))

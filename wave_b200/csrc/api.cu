@@ -1379,6 +1379,45 @@ int wb200_trace_read(unsigned long long* out, int max_ctas) {
 }
 #endif
 
+extern "C++" {
+// One thread evaluates a predicate that is false by construction and skips the (valid) store behind it: shows that a
+// failed check is recorded and nothing else happens.
+__global__ void checks_selftest_kernel(int* out, int n) {
+  const int i = n;  // one past the end
+  if (WB_CHECK(i < n, wb::kCheckSelfTest, i)) out[0] = 1;
+}
+}
+
+int wb200_debug_checks(unsigned long long* record, int reset) {
+#ifdef WB200_CHECKS
+  if (!record) return fail(WB200_ERR_INVALID_ARG, "debug_checks: null record");
+  WB_CUDA(cudaDeviceSynchronize());
+  WB_CUDA(cudaMemcpyFromSymbol(record, wb::g_check_record, 3 * sizeof(unsigned long long)));
+  if (reset) {
+    const unsigned long long zero[3] = {0, 0, 0};
+    WB_CUDA(cudaMemcpyToSymbol(wb::g_check_record, zero, sizeof(zero)));
+  }
+  return WB200_OK;
+#else
+  (void)record; (void)reset;
+  return fail(WB200_ERR_UNSUPPORTED, "this library was built without -DWB200_CHECKS (python -m wave_b200.build --checks)");
+#endif
+}
+
+int wb200_debug_checks_selftest(void* stream) {
+#ifdef WB200_CHECKS
+  DeviceInfo* dev;
+  int rc = get_device(&dev);
+  if (rc) return rc;
+  checks_selftest_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(dev->status_ptr + 1, 1);
+  WB_CUDA(cudaGetLastError());
+  return WB200_OK;
+#else
+  (void)stream;
+  return fail(WB200_ERR_UNSUPPORTED, "this library was built without -DWB200_CHECKS (python -m wave_b200.build --checks)");
+#endif
+}
+
 int wb200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows, void* stream) {
   if (!dst || !src || width_bytes == 0 || rows == 0 || dst_pitch < width_bytes || src_pitch < width_bytes)
     return fail(WB200_ERR_INVALID_ARG, "copy_2d: null pointer, empty copy or a pitch smaller than the row width");

@@ -534,7 +534,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
             for (int i = 0; i < 8; ++i) {
               const int rr = i * 4 + (lane >> 3), j = lane & 7;
               const int grow = row0 + rr, gcol = scol + j * EPV;
-              if (grow < rows && gcol < p.N) {
+              if (grow < rows && gcol < p.N && WB_CHECK(grow >= 0 && gcol >= 0, kCheckOutputIndex, (long long)grow << 32 | unsigned(gcol))) {
                 const uint4 v = ld_shared_v4(buf + rr * 128 + ((j ^ (rr & 7)) << 4));
                 OutT* dst = cb + size_t(grow) * p.ldc + gcol;
                 if (gcol + EPV <= p.N) {
@@ -561,7 +561,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
             }
             ++store_count;  // the buffers alternate store by store, across tiles too
           }
-        } else if (row < rows && col < p.N) {
+        } else if (row < rows && col < p.N && WB_CHECK(row >= 0 && col >= 0, kCheckOutputIndex, (long long)row << 32 | unsigned(col))) {
           OutT* dst = reinterpret_cast<OutT*>(c_group) + size_t(row) * p.ldc + col;
           const int ncols = min(32, p.N - col);
           if (p.accumulate) add_old_chunk32<OutT>(dst, r, ncols, p.vec_ok != 0);

@@ -12,6 +12,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "checks.cuh"
+
 namespace wb {
 
 // ---------------------------------------------------------------------------------------------
@@ -162,6 +164,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 template <int CTA_GROUP = 1>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* tmap, int x,
                                             int y, uint32_t bar) {
+  if (!WB_CHECK((x & 15) == 0, kCheckTmaLoadCoord, x) || !WB_CHECK((dst_smem & 127u) == 0u, kCheckTmaSmem, dst_smem)) return;
   if constexpr (CTA_GROUP == 1)
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
@@ -177,6 +180,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
 }
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* tmap,
                                                  int x, int y, uint32_t bar, uint64_t policy) {
+  if (!WB_CHECK((x & 15) == 0, kCheckTmaLoadCoord, x) || !WB_CHECK((dst_smem & 127u) == 0u, kCheckTmaSmem, dst_smem)) return;
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
       "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst_smem),
@@ -186,6 +190,7 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtens
 // src and dst 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes,
                                           uint32_t bar) {
+  if (!WB_CHECK(((reinterpret_cast<uintptr_t>(src) | dst_smem | bytes) & 15u) == 0u, kCheckBulkCopy, bytes)) return;
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
           "r"(dst_smem),
@@ -194,6 +199,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t src_smem, int x,
                                              int y) {
+  if (!WB_CHECK(x >= 0 && y >= 0 && (x & 3) == 0, kCheckTmaStoreCoord, x) || !WB_CHECK((src_smem & 127u) == 0u, kCheckTmaSmem, src_smem)) return;
   asm volatile(
       "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
       "r"(src_smem), "r"(x), "r"(y)
@@ -201,6 +207,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t s
 }
 __device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* tmap, uint32_t src_smem, int x, int y,
                                                   uint64_t policy) {
+  if (!WB_CHECK(x >= 0 && y >= 0 && (x & 3) == 0, kCheckTmaStoreCoord, x) || !WB_CHECK((src_smem & 127u) == 0u, kCheckTmaSmem, src_smem)) return;
   asm volatile(
       "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(tmap),
       "r"(src_smem), "r"(x), "r"(y), "l"(policy)

@@ -8,6 +8,9 @@
 //   e = floor(log2(amax)) - 2 (E2M1's largest value is 6 = 1.5 * 2^2), scale byte clamp(e + 127, 0, 254),
 //   amax == 0 -> byte 127; y = x * 2^-(byte - 127), clamped to [-6, 6], rounded to the nearest E2M1
 //   value, a value on a midpoint going to the neighbour with the even code; even k in the low nibble.
+//   A block that holds a NaN or an infinity gets scale byte 255 (E8M0's NaN: the OCP MX rule, and what the
+//   reference's dequantisation reads as NaN, mxfp_utils.py:86-95) and codes 0, so that the GEMM's outputs for
+//   that row are NaN instead of plausible finite numbers.
 //
 // HBM-bound: 4 lanes share one block (8 values each), so a warp reads 512 contiguous bytes of bf16
 // per load instruction and writes 128 contiguous bytes of codes; the E2M1 rounding is the hardware conversion.
@@ -26,21 +29,35 @@ __device__ __forceinline__ uint32_t e2m1x2_code(float lo, float hi) {
   return uint32_t(r);
 }
 
+// Bit pattern of the largest |v| over the 32 values held by a group of 32 / VPL neighbouring lanes. For
+// non-negative floats the unsigned order of the bit patterns is the numeric order, with the infinity above
+// every finite value and every NaN above the infinity: an integer maximum keeps a NaN that fmaxf would drop.
+template <int VPL>
+__device__ __forceinline__ uint32_t block_amax_bits(const float (&v)[VPL]) {
+  uint32_t m = 0;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) m = max(m, __float_as_uint(fabsf(v[j])));
+#pragma unroll
+  for (int o = 1; o < 32 / VPL; o <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  return m;
+}
+
 // Scale byte and codes of the 32 values held by a group of 32 / VPL neighbouring lanes (v: the VPL consecutive
 // values of this lane; VPL = 4 or 8). All lanes of a warp must call it together (shuffles).
 template <int VPL>
 __device__ __forceinline__ void mxfp4_encode_values(const float (&v)[VPL], uint32_t& packed, int& sb) {
   static_assert(VPL == 4 || VPL == 8, "4 or 8 values per lane");
-  float amax = 0.f;
-#pragma unroll
-  for (int j = 0; j < VPL; ++j) amax = fmaxf(amax, fabsf(v[j]));
-#pragma unroll
-  for (int o = 1; o < 32 / VPL; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const uint32_t amax_bits = block_amax_bits<VPL>(v);
+  if ((amax_bits >> 23) == 0xffu) {  // an infinity or a NaN somewhere in the block
+    sb = 255;
+    packed = 0;
+    return;
+  }
   // floor(log2(amax)) is the unbiased exponent field for normal numbers; subnormal maxima fall
   // below the clamp at 0 either way
   sb = 127;
-  if (amax > 0.f) {
-    sb = int((__float_as_uint(amax) >> 23) & 0xff) - 2;
+  if (amax_bits != 0u) {
+    sb = int(amax_bits >> 23) - 2;
     sb = max(0, min(254, sb));
   }
   // y = x * 2^(127 - sb), exact; 2^127 and 2^-127 are both representable
@@ -130,22 +147,21 @@ quantize_mxfp8_kernel(const InT* __restrict__ x, long long ldx, int rows, int K,
   const bool active = r < rows && kb < kblocks;
   float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (active) load8(x + (long long)r * ldx + kb * 32 + sub * 8, v);
-  float amax = 0.f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  int sb = 127;
-  if (amax > 0.f) {
-    sb = int((__float_as_uint(amax) >> 23) & 0xff) - (fmt == 0 ? 8 : 15);
+  const uint32_t amax_bits = block_amax_bits<8>(v);
+  const bool not_finite = (amax_bits >> 23) == 0xffu;  // an infinity or a NaN in the block: scale byte 255, codes 0
+  int sb = not_finite ? 255 : 127;
+  if (!not_finite && amax_bits != 0u) {
+    sb = int(amax_bits >> 23) - (fmt == 0 ? 8 : 15);
     sb = max(0, min(254, sb));
   }
   const int ie = 127 - sb;
-  const float inv = (ie == -127) ? __int_as_float(0x00400000) : __int_as_float((ie + 127) << 23);
+  const float inv = (ie <= -127) ? __int_as_float(0x00400000) : __int_as_float((ie + 127) << 23);
   if (!active) return;
-  uint2 out;
-  out.x = f8x2_code(v[0] * inv, v[1] * inv, fmt) | (f8x2_code(v[2] * inv, v[3] * inv, fmt) << 16);
-  out.y = f8x2_code(v[4] * inv, v[5] * inv, fmt) | (f8x2_code(v[6] * inv, v[7] * inv, fmt) << 16);
+  uint2 out = make_uint2(0u, 0u);
+  if (!not_finite) {
+    out.x = f8x2_code(v[0] * inv, v[1] * inv, fmt) | (f8x2_code(v[2] * inv, v[3] * inv, fmt) << 16);
+    out.y = f8x2_code(v[4] * inv, v[5] * inv, fmt) | (f8x2_code(v[6] * inv, v[7] * inv, fmt) << 16);
+  }
   *reinterpret_cast<uint2*>(q + (long long)r * K + kb * 32 + sub * 8) = out;
   if (sub == 0) {
     if (scale_rm) scale_rm[(long long)r * kblocks + kb] = uint8_t(sb);

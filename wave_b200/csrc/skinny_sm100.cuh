@@ -69,6 +69,8 @@ struct SkinnyCfg {
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 };
 
+constexpr int kSkinnyCounterWords = 4096;  // 32-bit tile counters at the head of every workspace
+
 struct SkinnyParams {
   void* c;
   float* partials;         // [2 * gridDim.x][M][128] f32
@@ -291,6 +293,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     if (p.dependent) pdl_wait();  // C, the partial tiles and the counters may still be in use by the kernels before this one
     OutT* __restrict__ C = reinterpret_cast<OutT*>(p.c);
     auto store_out = [&](int m, int n, float v) {
+      if (!WB_CHECK(m >= 0 && m < p.M && n >= 0 && n < p.N, kCheckOutputIndex, (long long)m << 32 | unsigned(n))) return;
       OutT* dst = C + size_t(m) * p.ldc + n;
       if constexpr (sizeof(OutT) == 4) {
         if (p.accumulate) v += *dst;
@@ -313,6 +316,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       const int n = tile * 128 + nl;
       const bool whole = (kbs == 0 && kbe == p.num_kb);
       float* part = p.partials + (size_t(2 * blockIdx.x + (tile == first_tile ? 0 : 1)) * p.M) * 128 + nl;
+      (void)WB_CHECK(tile >= 0 && tile < p.tiles_n && tile < kSkinnyCounterWords, kCheckCounter, tile);
 
       // A partial segment: who else contributes to this tile, and have they all published already?
       // If so this CTA is certainly the last one: it keeps its own partial in registers, adds the

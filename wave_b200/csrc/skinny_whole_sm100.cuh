@@ -314,6 +314,7 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w) : "r"(src) : "memory");
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w) : "r"(src + 16u) : "memory");
           OutT* dst = C + size_t(m) * p.ldc + n;
+          if (!WB_CHECK(m >= 0 && m < p.M && n >= 0 && n < p.N, kCheckOutputIndex, (long long)m << 32 | unsigned(n))) continue;
           if (p.c_vec && n + 8 <= p.N) {
             if constexpr (sizeof(OutT) == 4) {
               float4* d4 = reinterpret_cast<float4*>(dst);

@@ -305,6 +305,64 @@ def time_k_sharded(M=8192, N=8192, k_per_rank=8192, iters=20):
     dist.destroy_process_group()
 
 
+def _interleaved_times(launchers, rounds=10, launches_per_replay=8):
+    """Median us per launch of each launcher; one CUDA graph each, replayed in turn round after round so that every
+    setting meets the same clock and power state."""
+    import statistics
+    graphs = []
+    for fn in launchers:
+        fn()
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(launches_per_replay):
+                fn()
+        graphs.append(g)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = [[] for _ in launchers]
+    for _ in range(rounds + 2):
+        for i, g in enumerate(graphs):
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times[i].append(e0.elapsed_time(e1) * 1e3 / launches_per_replay)
+    return [statistics.median(t[2:]) for t in times]
+
+
+def _packed_problem(M, N, K, device):
+    from . import generate_gemm_afp4wfp4_inputs, ops
+    x, w, xs, ws = generate_gemm_afp4wfp4_inputs((M, N, K), device=torch.device(device))
+    w_t = w.T.contiguous()
+    return x, ops.repack_scales(xs), w_t, ops.repack_scales(ws), torch.empty(M, N, dtype=torch.bfloat16, device=device)
+
+
+def sweep_raster_group(shapes=((8192, 8192, 8192), (4096, 8192, 8192), (8192, 4096, 8192), (16384, 6656, 16384),
+                               (8192, 14336, 8192), (4096, 4096, 4096), (8192, 32768, 16000)),
+                       groups=(4, 8, 16, 24, 32, 255), device="cuda:0"):
+    """us per launch for each raster group size (N tiles per group; 255 = one group, plain row-major order)."""
+    from . import _lib, ops
+    for M, N, K in shapes:
+        x, a_sf, w_t, b_sf, c = _packed_problem(M, N, K, device)
+        fl = [_lib.GROUP_N_ALL if g == 255 else _lib.GROUP_N(g) for g in groups]
+        us = _interleaved_times([lambda f=f: ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c, f) for f in fl])
+        print((M, N, K), "N tiles", (N + 255) // 256, " | ".join(f"g={g}: {t:8.1f}" for g, t in zip(groups, us)), flush=True)
+    ops.check_device_status()
+
+
+def tile_variants(M: int, N: int, K: int, device="cuda:0"):
+    """us per launch of one shape on every tile path that takes it, next to the automatic choice."""
+    from . import _lib, ops
+    x, a_sf, w_t, b_sf, c = _packed_problem(M, N, K, device)
+    names = {"auto": _lib.PATH_AUTO, "2cta-256": _lib.PATH_TILE_2CTA, "2cta-192": _lib.PATH_TILE_2CTA | _lib.TILE_N192,
+             "2cta-128": _lib.PATH_TILE_2CTA | _lib.TILE_N128, "1cta-256": _lib.PATH_TILE_1CTA,
+             "1cta-128": _lib.PATH_TILE_1CTA | _lib.TILE_N128}
+    us = _interleaved_times([lambda f=f: ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c, f) for f in names.values()])
+    print((M, N, K), " | ".join(f"{n}: {t:7.1f} us ({runtime_us_to_tflops(M, N, K, t):6.0f} TF)" for n, t in zip(names, us)), flush=True)
+    ops.check_device_status()
+
+
 def skinny_timeline(M: int, N: int, K: int, launches: int = 12, save: str | None = None, device="cuda:0"):
     """Per-CTA timeline of the skinny kernel (M <= 128), from the marks of the measurement build of the library:
     build it with `python -m wave_b200.build --trace` and run
@@ -374,9 +432,19 @@ def main(argv=None):
     ap.add_argument("--timeline", nargs=3, type=int, metavar=("M", "N", "K"),
                     help="per-CTA timeline of the skinny kernel (needs the --trace build of the library, see skinny_timeline)")
     ap.add_argument("--save", default=None, help="with --timeline: write the raw marks to this .npy file")
+    ap.add_argument("--group-sweep", action="store_true", help="time the tile kernel over raster group sizes (WB200_GROUP_N)")
+    ap.add_argument("--variants", nargs=3, type=int, action="append", metavar=("M", "N", "K"),
+                    help="time one shape on every tile path (may be given several times)")
     args = ap.parse_args(argv)
     if args.timeline:
         skinny_timeline(*args.timeline, save=args.save)
+        return
+    if args.group_sweep:
+        sweep_raster_group()
+        return
+    if args.variants:
+        for shape in args.variants:
+            tile_variants(*shape)
         return
     if args.moe:
         time_moe(iters=args.iters)
