@@ -604,6 +604,39 @@ def test_quantizer_marks_blocks_with_nan_or_inf(dtype):
     assert torch.equal(torch.isnan(c).all(dim=1).cpu(), nan_rows) and torch.equal(torch.isnan(c).any(dim=1).cpu(), nan_rows)
 
 
+def test_weight_scale_cache_belongs_to_the_tensor_not_the_address():
+    """A new scale tensor that the allocator puts at a freed tensor's address must be repacked, an in-place write
+    must be seen, and drop_cached_weights forgets a packing that a raw write made stale."""
+    M, N, K = 64, 256, 512
+    a, a_s, b, b_s = random_problem(M, N, K, seed=11)
+    tpl, options = wb.templates.get_tagged_mxfp4_gemm((M, N, K), output_dtype=wb.bf16)
+    gemm = wb.wave_compile(options, tpl)
+    ad, asd, bd = a.to(DEV), a_s.to(DEV), b.to(DEV)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    s1 = b_s.to(DEV)
+    ptr = s1.data_ptr()
+    gemm(ad, asd, bd, s1, c)
+    check(c, a, a_s, b, b_s)
+    del s1
+    other = (b_s.to(torch.int16) + 1).clamp(max=131).to(torch.uint8)
+    s2 = other.to(DEV)  # same shape: the caching allocator hands the freed block out again
+    if s2.data_ptr() != ptr:
+        pytest.skip("the allocator did not reuse the address")
+    gemm(ad, asd, bd, s2, c)
+    check(c, a, a_s, b, other)
+    s2.copy_(b_s.to(DEV))  # in-place write: version counter moves
+    gemm(ad, asd, bd, s2, c)
+    check(c, a, a_s, b, b_s)
+    # a write the version counter does not see (here through a detached alias of the memory)
+    alias = torch.as_strided(s2.detach().view(-1).data, s2.shape, s2.stride())
+    version = s2._version
+    alias.data.copy_(other.to(DEV))
+    if s2._version == version:
+        gemm.drop_cached_weights(s2)
+    gemm(ad, asd, bd, s2, c)
+    check(c, a, a_s, b, other)
+
+
 def test_mxfp4_linear_module_matches_oracle():
     torch.manual_seed(5)
     N, K = 768, 1024

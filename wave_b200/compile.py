@@ -256,6 +256,17 @@ class ScaledGemmKernel:
             raise ValueError(f"{name} must be [{rows}, {K // ops.SCALE_GROUP_SIZE}], got {tuple(s.shape)}")
         return s
 
+    def drop_cached_weights(self, b_scale: torch.Tensor | None = None) -> None:
+        """Forget the packed copy of `b_scale` (of every weight when None). The kernel repacks a weight's scales on
+        first use and reuses the packing while the same tensor object keeps its version; after a write the version
+        counter cannot see (a raw-pointer write, a graph replay that refreshes the scales in place), call this
+        before the next GEMM. Launch plans that captured the old packing are dropped with it."""
+        if b_scale is None:
+            self._weight_scales.clear()
+        else:
+            self._weight_scales.drop(b_scale)
+        self._plans.clear()
+
     def _raster_flags(self) -> int:
         """The template's reorder_workgroups / group_size_n as the tile kernels' raster-group bits. The reference
         counts groups in workgroups of BLOCK_N columns (tagged_mxfp4_gemm.py, _reorder_mxfp4_workgroups); the

@@ -8,6 +8,7 @@ as the reference's launch shim does (wave_lang/kernel/wave/utils/run_utils.py:87
 from __future__ import annotations
 
 import ctypes
+import weakref
 from collections import OrderedDict
 
 import torch
@@ -250,8 +251,14 @@ def scaled_gemm_mxfp8_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tenso
 
 
 class WeightScaleCache:
-    """Packed copies of weight scales, keyed by the identity and version of the row-major tensor,
-    so that a weight's scales are repacked once and reused by later calls."""
+    """Packed copies of weight scales, so that a weight's scales are repacked once and reused by later calls.
+
+    An entry belongs to one tensor OBJECT at one version: it is found by address, shape, strides and version counter,
+    and used only while a weak reference shows that the very tensor it was made from is still alive. A new tensor
+    that the allocator places at a freed tensor's address therefore never meets the old packing, and an in-place
+    write (which bumps the version of every view) makes the next call repack. What the cache cannot see is a write
+    through a raw pointer (a C extension, a CUDA graph replay that rewrites the scales): call `clear()` — or
+    `ScaledGemmKernel.drop_cached_weights()` — after such a write."""
 
     def __init__(self, capacity: int = 64):
         self.capacity = capacity
@@ -261,13 +268,21 @@ class WeightScaleCache:
         key = (scale.data_ptr(), tuple(scale.shape), scale.stride(), scale.device.index, scale._version)
         hit = self._entries.get(key)
         if hit is not None:
-            self._entries.move_to_end(key)
-            return hit
+            owner, packed = hit
+            if owner() is scale:
+                self._entries.move_to_end(key)
+                return packed
+            del self._entries[key]  # same address, another (or a dead) tensor: the packing is not this tensor's
         packed = repack_scales(scale)
-        self._entries[key] = packed
+        self._entries[key] = (weakref.ref(scale), packed)
         while len(self._entries) > self.capacity:
             self._entries.popitem(last=False)
         return packed
+
+    def drop(self, scale: torch.Tensor) -> None:
+        """Forget every packing made from this tensor's memory (any version)."""
+        for key in [k for k in self._entries if k[0] == scale.data_ptr() and k[3] == scale.device.index]:
+            del self._entries[key]
 
     def clear(self) -> None:
         self._entries.clear()
