@@ -54,6 +54,12 @@ NCU_TRAFFIC = {
     "c3_m128": {"bytes": 128.9e6, "kernel": "mxfp4_skinny_whole_kernel<128,6,bf16>", "captured_at_commit": "53ffb24"},
 }
 
+# Sustained rate of a measurement build of the c2 kernel that keeps only its scale copies and MMAs (operands resident
+# in shared memory, accumulators never read): the tensor pipe's ceiling for this tile shape under the board's power
+# limit. Measured once with `python -m wave_b200.perf --sustained 8192 8192 8192` against that build; not re-measured here.
+MMA_ONLY_CEILING = {"tflops": 6881.0, "sm_mhz_median": 1665, "watts_median": 992, "measured_at_commit": "0cf7fad",
+                    "how": "library built with -DWB200_MMA_CEILING, two seconds back to back, same operands and launch protocol"}
+
 WORKLOADS = {
     "c2": dict(M=8192, N=8192, K=8192, std_b=1.0, seed_a=1002, seed_b=2002,
                desc="C2 prefill projection: MXFP4 GEMM M=N=K=8192, block 32, operands quantised from seeded N(0,1), bf16 out"),
@@ -682,6 +688,7 @@ def main():
                           "burst_kernel_ms": kernel_ms_avg, "burst_sm_mhz_median": clocks_burst["sm_mhz"],
                           "burst_clock_samples": clocks_burst["samples"],
                           "burst_ms_x_mhz": (kernel_ms_avg * clocks_burst["sm_mhz"]) if clocks_burst["sm_mhz"] else None,
+                          "mma_only_ceiling": dict(MMA_ONLY_CEILING, frac_of_it=flops / (sustained["kernel_ms"] * 1e-3) / 1e12 / MMA_ONLY_CEILING["tflops"]),
                           "what": "the c2 kernel alone, replayed from a CUDA graph over the three rotating operand sets, back to back after 0.3 s untimed"})
     # clocks of the line: the samples taken while the timed steps and the kernel-only loop ran (a few milliseconds:
     # few samples); the sustained record carries the clocks of the two-second loop

@@ -345,6 +345,9 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the loop; one elected lane issues the copies.
     uint32_t stage = 0, phase = 0;
+#ifdef WB200_MMA_CEILING
+    int stages_loaded = 0;  // measurement build: only the first ring is loaded, the MMAs then re-read it
+#endif
     pdl_wait();  // the packed activation scales may be written by the kernel launched just before this one
     for (int t = first_tile; t < num_tiles; t += tile_step) {
       int mt, nt, rows;
@@ -363,6 +366,15 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
         // With a CTA pair, every load of both CTAs reports to the leader's barrier, which
         // therefore expects the bytes of two stages; the second CTA only issues its copies.
         const uint32_t fb = (CG == 2) ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
+#ifdef WB200_MMA_CEILING
+        if (stages_loaded >= STAGES) {
+          if (leader && elect_one()) mbar_arrive(full_bar(stage));
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          continue;
+        }
+        ++stages_loaded;
+#endif
         if (elect_one()) {
           if (leader) mbar_expect_tx(full_bar(stage), Cfg::LOAD_BYTES * CG);
           tma_load_2d<CG>(sA, tm + 0, kb * 128, a_row, fb);
@@ -494,6 +506,11 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
           else mbar_arrive(acc_empty_bar(as));
         }
       };
+#ifdef WB200_MMA_CEILING
+      release();  // measurement build: the accumulator is neither read nor stored
+      ++it;
+      continue;
+#endif
       constexpr int NCHUNK = BN / 32;
 #pragma unroll 1
       for (int ci = 0; ci < NCHUNK; ++ci) {

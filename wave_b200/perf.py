@@ -363,6 +363,77 @@ def tile_variants(M: int, N: int, K: int, device="cuda:0"):
     ops.check_device_status()
 
 
+def sustained_rate(M: int, N: int, K: int, seconds: float = 2.0, device="cuda:0"):
+    """TFLOP/s of one shape launched back to back for `seconds` (after a ramp of a quarter of that), with the SM clock
+    and the board power sampled through NVML meanwhile. Operands are Gaussian data quantised on the GPU (what the
+    tensor pipe draws depends on the bits it multiplies), three rotating sets.
+
+    With the measurement build of the library (`python -m wave_b200.build --mma-ceiling`, then
+    `WAVE_B200_LIB=wave_b200/libwave_b200_mma_ceiling.so python -m wave_b200.perf --sustained 8192 8192 8192`) the
+    tile kernels load only their first ring of stages and never read the accumulators: the figure is then the ceiling
+    of the scale copies + MMAs alone, for this tile shape, under the same power limit."""
+    import statistics
+    import threading
+    import time
+    from . import _lib, ops
+    dev = torch.device(device)
+    sets = []
+    g = torch.Generator(device=dev).manual_seed(1)
+    for _ in range(3):
+        a, _, a_sf = ops.quantize_mxfp4(torch.randn(M, K, device=dev, generator=g, dtype=torch.bfloat16), want_rowmajor=False)
+        b, _, b_sf = ops.quantize_mxfp4(torch.randn(N, K, device=dev, generator=g, dtype=torch.bfloat16), want_rowmajor=False)
+        sets.append((a, a_sf, b, b_sf, torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+
+    def launch_all():
+        for a, a_sf, b, b_sf, c in sets:
+            ops.scaled_gemm_packed(a, a_sf, b, b_sf, c)
+
+    launch_all()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        launch_all()
+    samples, stop = [], [False]
+
+    def sample():
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(dev.index or 0)
+            while not stop[0]:
+                samples.append((pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM), pynvml.nvmlDeviceGetPowerUsage(h) / 1e3))
+                time.sleep(0.002)
+        except Exception:
+            pass
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    per_replay = max(e0.elapsed_time(e1), 1e-3)
+    for _ in range(max(1, int(250.0 * seconds / per_replay))):  # ramp: clocks and temperature settle under load
+        graph.replay()
+    torch.cuda.synchronize()
+    th = threading.Thread(target=sample, daemon=True)
+    th.start()
+    reps = max(3, int(1000.0 * seconds / per_replay))
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    stop[0] = True
+    th.join(timeout=1.0)
+    ms = e0.elapsed_time(e1) / (reps * len(sets))
+    out = dict(library=str(_lib.library_path()), M=M, N=N, K=K, seconds=round(e0.elapsed_time(e1) / 1e3, 2), kernel_us=round(ms * 1e3, 2),
+               tflops=round(runtime_us_to_tflops(M, N, K, ms * 1e3), 1))
+    if samples:
+        out.update(sm_mhz_median=statistics.median(s[0] for s in samples), watts_median=round(statistics.median(s[1] for s in samples), 1))
+    print(out, flush=True)
+    return out
+
+
 def skinny_timeline(M: int, N: int, K: int, launches: int = 12, save: str | None = None, device="cuda:0"):
     """Per-CTA timeline of the skinny kernel (M <= 128), from the marks of the measurement build of the library:
     build it with `python -m wave_b200.build --trace` and run
@@ -432,12 +503,17 @@ def main(argv=None):
     ap.add_argument("--timeline", nargs=3, type=int, metavar=("M", "N", "K"),
                     help="per-CTA timeline of the skinny kernel (needs the --trace build of the library, see skinny_timeline)")
     ap.add_argument("--save", default=None, help="with --timeline: write the raw marks to this .npy file")
+    ap.add_argument("--sustained", nargs=3, type=int, metavar=("M", "N", "K"),
+                    help="one shape back to back for two seconds with clock and power sampled (see sustained_rate)")
     ap.add_argument("--group-sweep", action="store_true", help="time the tile kernel over raster group sizes (WB200_GROUP_N)")
     ap.add_argument("--variants", nargs=3, type=int, action="append", metavar=("M", "N", "K"),
                     help="time one shape on every tile path (may be given several times)")
     args = ap.parse_args(argv)
     if args.timeline:
         skinny_timeline(*args.timeline, save=args.save)
+        return
+    if args.sustained:
+        sustained_rate(*args.sustained)
         return
     if args.group_sweep:
         sweep_raster_group()
