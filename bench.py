@@ -211,13 +211,16 @@ def decode_record(dev, peaks, overlap=True):
     from wave_b200 import _lib, ops
     N, K, SETS = DECODE["N"], DECODE["K"], 3
     weights = []
+    # weight scales packed once, per tile of the height that gives every SM the same number of weight tiles
+    tile_rows = ops.decode_tile_rows(N, dev)
     for i in range(SETS):
         q, s = gpu_quantised(N, K, DECODE["seed_b"] + 7 * i, DECODE["std_b"], dev)
-        weights.append((q, s, ops.repack_scales(s)))
+        weights.append((q, s, ops.repack_scales(s, tile_rows=tile_rows)))
     act_q, act_s = gpu_quantised(128, K, DECODE["seed_a"], 1.0, dev)
     flags = _lib.PATH_SKINNY | (_lib.OVERLAP_PREVIOUS if overlap else 0)
     out = {"N": N, "K": K, "weight_sets": SETS, "launch": "CUDA-graph replay of the kernel alone (activation scales packed beforehand)",
-           "overlap": "each launch is a programmatic dependent of the one before it" if overlap else "none", "per_m": {}}
+           "overlap": "each launch is a programmatic dependent of the one before it" if overlap else "none",
+           "weight_tile_rows": tile_rows, "per_m": {}}
     for M in DECODE["Ms"]:
         a, a_s = act_q[:M].contiguous(), act_s[:M].contiguous()
         a_sf = ops.repack_scales(a_s)

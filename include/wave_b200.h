@@ -74,6 +74,12 @@ extern "C" {
 #define WB200_GROUP_N_MASK 0xFF00u
 #define WB200_GROUP_N(g) (((unsigned)(g) << WB200_GROUP_N_SHIFT) & WB200_GROUP_N_MASK)
 #define WB200_GROUP_N_ALL WB200_GROUP_N(255)
+/* The weight scales (b_scale_packed) were packed per tile of h weight rows by wb200_repack_scales_tiled instead of per
+ * 128-row block: h / 8 in bits 16..20 (h = 8 .. 128 in steps of 8; 0 or 128 = the usual packing). Read by the M <= 128
+ * kernel only (WB200_PATH_AUTO with a workspace, or WB200_PATH_SKINNY); h is wb200_decode_tile_rows(N). */
+#define WB200_B_TILE_ROWS_SHIFT 16
+#define WB200_B_TILE_ROWS_MASK 0x1F0000u
+#define WB200_B_TILE_ROWS(h) ((((unsigned)(h) / 8u) << WB200_B_TILE_ROWS_SHIFT) & WB200_B_TILE_ROWS_MASK)
 
 /* Library version (major * 1000 + minor). */
 int wb200_version(void);
@@ -107,6 +113,22 @@ int wb200_debug_checks_selftest(void* stream);
 
 /* Bytes of the packed scale array for a [rows, K/32] scale matrix. */
 size_t wb200_packed_scale_bytes(int rows, int K);
+
+/* Weight-scale packing for the decode (M <= 128) kernel. That kernel deals whole tiles of weight rows to one CTA per
+ * SM; with the usual 128-row tiles the last round is partly empty whenever ceil(N / 128) is not a multiple of the SM
+ * count (N = 28672 on 148 SMs: 224 tiles, the second round runs on 76 SMs, each bounded by what one SM's ring can
+ * stream). wb200_decode_tile_rows(N) returns the tile height h <= 128 (a multiple of 8) for which every SM of the
+ * current device gets the same number of tiles, 128 when the usual packing is as good. A weight whose scales are
+ * packed with wb200_repack_scales_tiled(.., h, ..) (one 512-byte atom row per tile: rows [t h, t h + h) of the
+ * weight in atom rows 0 .. h - 1, padding byte above; wb200_packed_scale_bytes_tiled bytes) is then passed with
+ * WB200_B_TILE_ROWS(h) in flags. Weights are packed once, so this costs nothing per call; the packing depends on N
+ * and on the device's SM count, and the tile paths (M > 128) do not read it: a weight used at both ends of the M
+ * range keeps both packings. The reference prepares its weight scales per kernel variant in the same way
+ * (e8m0_shuffle for the preshuffle templates, wave_lang/kernel/wave/utils/mxfp_utils.py:113-128). */
+int wb200_decode_tile_rows(int N);
+size_t wb200_packed_scale_bytes_tiled(int rows, int K, int tile_rows);
+int wb200_repack_scales_tiled(const void* scales, long long row_stride, int rows, int K, int tile_rows, void* packed,
+                              void* stream);
 
 /* Row-major E8M0 scales -> packed layout. Replaces the host-side scale preshuffle
  * e8m0_shuffle (wave_lang/kernel/wave/utils/mxfp_utils.py:113-128) of the reference's

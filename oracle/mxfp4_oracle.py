@@ -129,6 +129,20 @@ def pack_scales(scale: torch.Tensor) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(v).reshape(-1))
 
 
+def pack_scales_tiled(scale: torch.Tensor, tile_rows: int) -> torch.Tensor:
+    """Weight-scale packing of the decode kernel: the rows are cut into tiles of `tile_rows` (a multiple of 8, at
+    most 128) and every tile gets an atom row of its own, its rows in atom rows 0 .. tile_rows - 1 and the padding byte
+    above; inside an atom the layout is `pack_scales`'s. tile_rows = 128 is `pack_scales` itself."""
+    assert tile_rows % 8 == 0 and 8 <= tile_rows <= 128
+    rows, kb = scale.shape
+    tiles = (rows + tile_rows - 1) // tile_rows
+    spread = torch.full((tiles * 128, kb), SF_PAD, dtype=torch.uint8)
+    for t in range(tiles):
+        part = scale[t * tile_rows:min(rows, (t + 1) * tile_rows)]
+        spread[t * 128:t * 128 + part.shape[0]] = part
+    return pack_scales(spread)
+
+
 # ---------------------------------------------------------------------------------------------
 # The reference's AMD pre-shuffles, stated as index maps (mxfp_utils.py:98-128). The B200 kernels do not use
 # these layouts; they are restated so that data a caller holds in them can be recognised and undone.

@@ -426,6 +426,84 @@ def test_skinny_path_with_dealt_parts(M, N, K, out_dtype, accumulate):
         assert torch.equal(outs[0].view(bits), c.view(bits))
 
 
+@pytest.mark.parametrize("rows,K,tile_rows", [(300, 768, 104), (28672 // 8, 512, 104), (97, 96, 96), (1000, 256, 8), (256, 1024, 128)])
+def test_tiled_weight_scale_packing_is_bit_exact(rows, K, tile_rows):
+    s = torch.randint(0, 255, (rows, K // 32), dtype=torch.uint8, generator=torch.Generator().manual_seed(rows + tile_rows))
+    packed = ops.repack_scales(s.to(DEV), tile_rows=tile_rows)
+    assert packed.tile_rows == tile_rows
+    assert torch.equal(packed.data.cpu(), orc.pack_scales_tiled(s, tile_rows))
+
+
+@pytest.mark.parametrize("M", [1, 16, 40, 128])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_decode_kernel_with_weight_scales_packed_per_balanced_tile(M, out_dtype):
+    """N = 28672 (the decode configuration's N): the balanced tile height is below 128 on any part whose SM count
+    does not divide 224; the GEMM on scales packed for it matches the oracle, and gives the bits of the usual packing
+    (every output column's sum over K is made in the same order either way)."""
+    N, K = 28672, 256
+    h = ops.decode_tile_rows(N)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert h % 8 == 0 and 8 <= h <= 128
+    if 224 % sms:
+        assert h < 128 and -(-N // h) <= -(-224 // sms) * sms  # every SM gets at most `rounds` tiles
+    a, a_s, b, b_s = random_problem(M, N, K, seed=500 + M)
+    ad, bd = a.to(DEV), b.to(DEV)
+    a_sf = ops.repack_scales(a_s.to(DEV))
+    usual, tiled = ops.repack_scales(b_s.to(DEV)), ops.repack_scales(b_s.to(DEV), tile_rows=h)
+    c0 = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    c1 = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_packed(ad, a_sf, bd, usual, c0, _lib.PATH_SKINNY)
+    ops.scaled_gemm_packed(ad, a_sf, bd, tiled, c1, _lib.PATH_SKINNY)
+    check(c1, a, a_s, b, b_s)
+    bits = torch.int16 if out_dtype == torch.bfloat16 else torch.int32
+    assert torch.equal(c0.view(bits), c1.view(bits))
+    # accumulate form and a ragged N on the same packing rule
+    N2 = N - 200
+    h2 = ops.decode_tile_rows(N2)
+    t2 = ops.repack_scales(b_s[:N2].to(DEV), tile_rows=h2)
+    c2 = torch.ones(M, N2, dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_packed(ad, a_sf, bd[:N2].contiguous(), t2, c2, _lib.PATH_SKINNY | _lib.ACCUMULATE)
+    check(c2, a, a_s, b[:N2], b_s[:N2], orc.scaled_gemm(a, a_s, b[:N2], b_s[:N2]) + 1.0)
+
+
+def test_tiled_weight_scales_are_refused_where_no_kernel_reads_them():
+    N, K = 28672, 256
+    h = ops.decode_tile_rows(N)
+    if h == 128:
+        pytest.skip("this part's SM count divides the tile count: no tiled packing")
+    a, a_s, b, b_s = random_problem(256, N, K, seed=9)
+    tiled = ops.repack_scales(b_s.to(DEV), tile_rows=h)
+    c = torch.empty(256, N, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):  # M > 128: the tile kernels read 128-row blocks
+        ops.scaled_gemm_packed(a.to(DEV), ops.repack_scales(a_s.to(DEV)), b.to(DEV), tiled, c)
+    lib = _lib.load()
+    small = ops.repack_scales(b_s[:1024].to(DEV), tile_rows=h)  # fewer tiles than SMs
+    c16 = torch.empty(16, 1024, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception) as err:
+        ops.scaled_gemm_packed(a[:16].to(DEV), ops.repack_scales(a_s[:16].to(DEV)), b[:1024].to(DEV), small, c16, _lib.PATH_SKINNY)
+    assert "wb200_repack_scales" in str(err.value)
+    assert lib.wb200_packed_scale_bytes_tiled(100, 256, 100) == 0  # not a multiple of 8
+    ops.check_device_status()
+
+
+def test_template_call_packs_weight_scales_for_the_decode_kernel():
+    """The reference-facing call at M <= 128 uses the balanced packing by itself and keeps the usual one for M > 128
+    of the same weight; both match the oracle."""
+    N, K = 28672, 256
+    a, a_s, b, b_s = random_problem(256, N, K, seed=77)
+    tpl, options = wb.templates.get_tagged_mxfp4_gemm((16, N, K), output_dtype=wb.bf16)
+    tpl.shape = None  # dynamic M
+    gemm = wb.wave_compile(options, tpl)
+    bd, bsd = b.to(DEV), b_s.to(DEV)
+    for M in (16, 256, 16):
+        c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        gemm(a[:M].to(DEV), a_s[:M].to(DEV), bd, bsd, c)
+        check(c, a[:M], a_s[:M], b, b_s)
+    h = ops.decode_tile_rows(N)
+    heights = sorted({k[-1] for k in gemm._weight_scales._entries})
+    assert heights == sorted({h, 128})
+
+
 def test_two_streams_run_skinny_gemms_at_the_same_time():
     """Two decode-shaped GEMMs launched on two streams with nothing ordering them: each call gets its own
     workspace (counters and partial tiles belong to one running GEMM), so both match the oracle however the

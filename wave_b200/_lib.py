@@ -37,6 +37,16 @@ GROUP_N_MASK = 0xFF00
 GROUP_N_ALL = 0xFF00
 
 
+B_TILE_ROWS_MASK = 0x1F0000
+
+
+def B_TILE_ROWS(h: int) -> int:
+    """Flag bits saying that b's scales were packed per tile of h weight rows (include/wave_b200.h, WB200_B_TILE_ROWS)."""
+    if h % 8 or not 8 <= h <= 128:
+        raise ValueError(f"{h} rows per tile: 8 .. 128 in steps of 8")
+    return 0 if h == 128 else (h // 8) << 16
+
+
 def GROUP_N(g: int) -> int:
     """Flag bits for a raster group of g N tiles (1..254); include/wave_b200.h, WB200_GROUP_N."""
     if not 1 <= int(g) <= 254:
@@ -54,6 +64,9 @@ EXPORTED_SYMBOLS = (
     "wb200_debug_checks",
     "wb200_debug_checks_selftest",
     "wb200_packed_scale_bytes",
+    "wb200_decode_tile_rows",
+    "wb200_packed_scale_bytes_tiled",
+    "wb200_repack_scales_tiled",
     "wb200_repack_scales",
     "wb200_repack_scales_broadcast",
     "wb200_repack_scales_grouped",
@@ -137,6 +150,12 @@ def load() -> ctypes.CDLL:
     lib.wb200_debug_checks_selftest.argtypes = [c_void_p]
     lib.wb200_packed_scale_bytes.restype = c_size_t
     lib.wb200_packed_scale_bytes.argtypes = [c_int, c_int]
+    lib.wb200_decode_tile_rows.restype = c_int
+    lib.wb200_decode_tile_rows.argtypes = [c_int]
+    lib.wb200_packed_scale_bytes_tiled.restype = c_size_t
+    lib.wb200_packed_scale_bytes_tiled.argtypes = [c_int, c_int, c_int]
+    lib.wb200_repack_scales_tiled.restype = c_int
+    lib.wb200_repack_scales_tiled.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_void_p]
     lib.wb200_repack_scales.restype = c_int
     lib.wb200_repack_scales.argtypes = [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p]
     lib.wb200_repack_scales_broadcast.restype = c_int

@@ -77,6 +77,9 @@ class WaveCompileOptions:
     # in the stream (weights of a layer), so the GEMM may start streaming them while that kernel drains
     # (WB200_OVERLAP_PREVIOUS: programmatic dependent launch)
     overlap_previous: bool = False
+    # wave_b200 only: for M <= 128 pack a weight's scales per tile of the height that gives every SM the same number of
+    # weight tiles (include/wave_b200.h, wb200_decode_tile_rows) instead of per 128 rows; False keeps one packing
+    decode_tiled_weight_scales: bool = True
 
 
 def get_default_arch() -> str:
@@ -119,6 +122,7 @@ class ScaledGemmKernel:
         self._a_scale_buf: dict[int, torch.Tensor] = {}
         self._workspaces = ops.WorkspacePool()  # this object's own: calls through another object may overlap with these
         self._plans: dict = {}
+        self._tile_rows: dict = {}
         self._lib = _lib.load()
         self._static = None
         if template.shape is not None and not options.dynamic_symbols:
@@ -153,7 +157,10 @@ class ScaledGemmKernel:
         M, N, K, a_buf, ws_ptr, ws_bytes, flags, dtype_code, dev_index, _ws_keepalive = plan
         if M > 128 and ws_bytes and not ops.split_k_pays() and (flags & _lib.PATH_MASK) != _lib.PATH_TILE_SPLITK:
             ws_ptr = ws_bytes = 0  # eager call: stay on the plain tile path (see ops.split_k_pays)
-        b_sf = self._weight_scales.get(b_scale)
+        tile_rows = self._weight_tile_rows(M, N, dev_index)
+        b_sf = self._weight_scales.get(b_scale, tile_rows)
+        if tile_rows != 128:
+            flags |= _lib.B_TILE_ROWS(tile_rows)
         lib = self._lib
         if dev_index == torch.cuda.current_device():
             rc = lib.wb200_mxfp4_gemm_repack_a(M, N, K, a.data_ptr(), a_scale.data_ptr(), a_scale.stride(0) if M > 1 else K // 32, a_buf.data_ptr(),
@@ -246,8 +253,12 @@ class ScaledGemmKernel:
             self._plans[sig] = plan
             return self._launch(plan, a, a_scale, b, b_scale, c)
         a_sf = self._pack_activation_scales(a_scale, M, K)
-        b_sf = b_scale if isinstance(b_scale, ops.PackedScales) else self._weight_scales.get(self._check_scale(b_scale, N, K, "b_scale"))
-        ops.scaled_gemm_packed(a, a_sf, b, b_sf, c, flags)
+        if isinstance(b_scale, ops.PackedScales):
+            b_sf = b_scale
+        else:
+            idx = a.device.index if a.device.index is not None else torch.cuda.current_device()
+            b_sf = self._weight_scales.get(self._check_scale(b_scale, N, K, "b_scale"), self._weight_tile_rows(M, N, idx))
+        ops.scaled_gemm_packed(a, a_sf, b, b_sf, c, flags)  # adds the tile-height bits a tiled packing needs
 
     @staticmethod
     def _check_scale(s, rows, K, name):
@@ -255,6 +266,18 @@ class ScaledGemmKernel:
         if tuple(s.shape) != (rows, K // ops.SCALE_GROUP_SIZE):
             raise ValueError(f"{name} must be [{rows}, {K // ops.SCALE_GROUP_SIZE}], got {tuple(s.shape)}")
         return s
+
+    def _weight_tile_rows(self, M: int, N: int, dev_index: int) -> int:
+        """Rows per tile the weight scales are packed for: the decode kernel's balanced tile height for M <= 128 (every
+        SM gets the same number of weight tiles, `ops.decode_tile_rows`), 128 otherwise. Weights are packed once per
+        (weight, height) and cached, so a weight used at both ends of the M range keeps two packings."""
+        if M > 128 or self.template.element_bits != 4 or not self.options.decode_tiled_weight_scales:
+            return 128
+        key = (N, dev_index)
+        h = self._tile_rows.get(key)
+        if h is None:
+            h = self._tile_rows[key] = ops.decode_tile_rows(N, dev_index)
+        return h
 
     def drop_cached_weights(self, b_scale: torch.Tensor | None = None) -> None:
         """Forget the packed copy of `b_scale` (of every weight when None). The kernel repacks a weight's scales on

@@ -135,6 +135,13 @@ static int group_n_from_flags(unsigned flags) {
   const unsigned g = (flags & WB200_GROUP_N_MASK) >> WB200_GROUP_N_SHIFT;
   return g == 0 ? 16 : g == 255 ? (1 << 20) : int(g);
 }
+// Weight rows per tile of the whole-tile skinny kernel for the call in progress (WB200_B_TILE_ROWS bits): 128, or the
+// height the weight scales were packed for with wb200_repack_scales_tiled.
+static thread_local int tl_b_tile_rows = 128;
+static int b_tile_rows_from_flags(unsigned flags) {
+  const unsigned h8 = (flags & WB200_B_TILE_ROWS_MASK) >> WB200_B_TILE_ROWS_SHIFT;
+  return h8 == 0 ? 128 : int(h8) * 8;
+}
 struct GroupNScope {  // restores the previous value on every return path
   int saved;
   explicit GroupNScope(unsigned flags) : saved(tl_group_n) { tl_group_n = group_n_from_flags(flags); }
@@ -625,6 +632,17 @@ bool skinny_takes_whole_tiles(int sm_count, int M, int N) {
   return rest == 0 || rest * 2 >= sm_count || tiles >= 4 * sm_count;
 }
 
+// Tile height that gives every SM the same number of tiles: with 128-row tiles the last round of the whole-tile
+// kernel is partly empty (224 tiles on 148 SMs: the second round runs on 76 of them, each bounded by what one SM's
+// ring can stream); rounds * SMs tiles of a smaller height, a multiple of 8, keep every SM streaming to the end.
+int decode_tile_rows(int sm_count, int N) {
+  const int tiles = (N + 127) / 128;
+  if (tiles < sm_count || tiles % sm_count == 0) return 128;
+  const long long slots = (long long)((tiles + sm_count - 1) / sm_count) * sm_count;
+  const int h = int(((N + slots - 1) / slots + 7) / 8 * 8);
+  return h < 128 ? h : 128;
+}
+
 template <int NP, int STAGES, typename OutT, int EB = 4>
 int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                         const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream,
@@ -633,11 +651,13 @@ int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* 
   using Cfg = wb::SkinnyWholeCfg<NP, STAGES, EB>;
   CUtensorMap tmW, tmX, tmSFW, tmSFX;
   const long long row_bytes = (long long)K * EB / 8;
-  int rc = make_operand_map(&tmW, b, N, row_bytes, 128);
+  const int tile_rows = tl_b_tile_rows;  // 128 with the usual packing of the weight scales
+  const int tiles_n = (N + tile_rows - 1) / tile_rows;
+  int rc = make_operand_map(&tmW, b, N, row_bytes, tile_rows);
   if (rc) return rc;
   rc = make_operand_map(&tmX, a, M, row_bytes, NP);
   if (rc) return rc;
-  rc = make_scale_map(&tmSFW, bs, wb::sf_row_blocks(N), wb::sf_k_atoms(K), 1, Base::SF_ATOMS);
+  rc = make_scale_map(&tmSFW, bs, tiles_n, wb::sf_k_atoms(K), 1, Base::SF_ATOMS);
   if (rc) return rc;
   rc = make_scale_map(&tmSFX, as, 1, wb::sf_k_atoms(K), 1, Base::SF_ATOMS);
   if (rc) return rc;
@@ -646,7 +666,8 @@ int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* 
   p.counters = static_cast<unsigned int*>(ws);
   p.M = M; p.N = N; p.K = K;
   p.ldc = int(ldc);
-  p.tiles_n = (N + 127) / 128;
+  p.tiles_n = tiles_n;
+  p.tile_rows = tile_rows;
   p.num_kb = (K + Base::BK - 1) / Base::BK;
   p.accumulate = accumulate;
   p.dependent = tl_dependent_launch ? 1 : 0;
@@ -676,7 +697,13 @@ template <typename OutT, int EB = 4>
 int dispatch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                     const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream,
                     int elem_format = 0) {
-  if (skinny_takes_whole_tiles(dev.sm_count, M, N)) {
+  if (tl_b_tile_rows != 128) {
+    // the weight scales are packed per tile of that height: only the whole-tile kernel reads them that way
+    if (EB != 4 || (N + tl_b_tile_rows - 1) / tl_b_tile_rows < dev.sm_count)
+      return fail(WB200_ERR_UNSUPPORTED, "weight scales packed for %d-row tiles need MXFP4 operands and at least one tile per SM (N = %d, %d SMs); "
+                  "pack them with wb200_repack_scales instead", tl_b_tile_rows, N, dev.sm_count);
+  }
+  if (tl_b_tile_rows != 128 || skinny_takes_whole_tiles(dev.sm_count, M, N)) {
     if (M <= 16) return launch_skinny_whole<16, 10, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
     if (M <= 32) return launch_skinny_whole<32, 9, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
     if (M <= 64) return launch_skinny_whole<64, 8, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
@@ -772,8 +799,22 @@ size_t wb200_packed_scale_bytes(int rows, int K) {
   return wb::sf_packed_bytes(rows, K);
 }
 
+int wb200_decode_tile_rows(int N) {
+  if (N <= 0) return 128;
+  DeviceInfo* dev;
+  if (get_device(&dev)) return 128;
+  return decode_tile_rows(dev->sm_count, N);
+}
+
+static bool tile_rows_ok(int tile_rows) { return tile_rows >= 8 && tile_rows <= 128 && tile_rows % 8 == 0; }
+
+size_t wb200_packed_scale_bytes_tiled(int rows, int K, int tile_rows) {
+  if (rows <= 0 || K <= 0 || !tile_rows_ok(tile_rows)) return 0;
+  return size_t((rows + tile_rows - 1) / tile_rows) * wb::sf_k_atoms(K) * 512;
+}
+
 static int repack_scales_impl(const void* src, long long src_row_stride, int rows, int K, void* dst, void* stream,
-                              bool broadcast) {
+                              bool broadcast, int block_rows = 128) {
   if (rows <= 0 || K <= 0 || K % 32 != 0)
     return fail(WB200_ERR_INVALID_ARG, "repack_scales: rows = %d, K = %d (K must be a positive multiple of 32)", rows, K);
   if (!src || !dst) return fail(WB200_ERR_INVALID_ARG, "repack_scales: null pointer");
@@ -784,7 +825,7 @@ static int repack_scales_impl(const void* src, long long src_row_stride, int row
   int rc = get_device(&dev);
   if (rc) return rc;
   const int k_atoms = wb::sf_k_atoms(K);
-  dim3 grid((k_atoms + 7) / 8, wb::sf_row_blocks(rows));
+  dim3 grid((k_atoms + 7) / 8, (rows + block_rows - 1) / block_rows);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(256, 1, 1);
@@ -795,8 +836,13 @@ static int repack_scales_impl(const void* src, long long src_row_stride, int row
   cfg.attrs = attr;
   cfg.numAttrs = tl_dependent_launch ? 1 : 0;
   WB_CUDA(cudaLaunchKernelEx(&cfg, wb::repack_scales_kernel, static_cast<const uint8_t*>(src), src_row_stride, rows, K / 32,
-                             k_atoms, static_cast<uint8_t*>(dst), broadcast, tl_dependent_launch));
+                             k_atoms, static_cast<uint8_t*>(dst), broadcast, tl_dependent_launch, block_rows));
   return WB200_OK;
+}
+
+int wb200_repack_scales_tiled(const void* src, long long src_row_stride, int rows, int K, int tile_rows, void* dst, void* stream) {
+  if (!tile_rows_ok(tile_rows)) return fail(WB200_ERR_INVALID_ARG, "repack_scales_tiled: %d rows per tile (8 .. 128 in steps of 8)", tile_rows);
+  return repack_scales_impl(src, src_row_stride, rows, K, dst, stream, false, tile_rows);
 }
 
 int wb200_repack_scales(const void* src, long long src_row_stride, int rows, int K, void* dst, void* stream) {
@@ -1112,9 +1158,21 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   unsigned path = flags & WB200_PATH_MASK;
-  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_TILE_N192 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS | WB200_GROUP_N_MASK)) != 0)
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_TILE_N192 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS | WB200_GROUP_N_MASK |
+                 WB200_B_TILE_ROWS_MASK)) != 0)
     return fail(WB200_ERR_INVALID_ARG, "unknown flag bits %#x", flags);
   GroupNScope group_scope(flags);
+  struct TileRowsScope {
+    int saved;
+    explicit TileRowsScope(int h) : saved(tl_b_tile_rows) { tl_b_tile_rows = h; }
+    ~TileRowsScope() { tl_b_tile_rows = saved; }
+  } tile_rows_scope(b_tile_rows_from_flags(flags));
+  if (tl_b_tile_rows != 128) {
+    if (tl_b_tile_rows > 128) return fail(WB200_ERR_INVALID_ARG, "WB200_B_TILE_ROWS: %d rows per tile (8 .. 128 in steps of 8)", tl_b_tile_rows);
+    if (M > 128 || (path != WB200_PATH_AUTO && path != WB200_PATH_SKINNY))
+      return fail(WB200_ERR_UNSUPPORTED, "weight scales packed per %d-row tile are read by the M <= 128 kernel only (M = %d, path %u)",
+                  tl_b_tile_rows, M, path);
+  }
   // restores the previous value on every return path
   struct DependentScope {
     bool saved;
@@ -1135,6 +1193,9 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
     else if (splitk_ok && slices >= 3 && !(flags & (WB200_TILE_N128 | WB200_TILE_N192))) path = WB200_PATH_TILE_SPLITK;
     else path = (M > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
   }
+  if (tl_b_tile_rows != 128 && path != WB200_PATH_SKINNY)
+    return fail(WB200_ERR_WORKSPACE, "weight scales packed per %d-row tile need the M <= 128 kernel, which needs a workspace of %zu bytes",
+                tl_b_tile_rows, skinny_workspace_bytes(dev->sm_count, M));
   if (path == WB200_PATH_TILE_SPLITK) {
     if (!splitk_ok)
       return fail(slices >= 2 ? WB200_ERR_WORKSPACE : WB200_ERR_UNSUPPORTED,

@@ -345,7 +345,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the loop; one elected lane issues the copies.
     uint32_t stage = 0, phase = 0;
-#ifdef WB200_MMA_CEILING
+#if defined(WB200_MMA_CEILING) && !defined(WB_KEEP_LOADS)
     int stages_loaded = 0;  // measurement build: only the first ring is loaded, the MMAs then re-read it
 #endif
     pdl_wait();  // the packed activation scales may be written by the kernel launched just before this one
@@ -366,7 +366,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
         // With a CTA pair, every load of both CTAs reports to the leader's barrier, which
         // therefore expects the bytes of two stages; the second CTA only issues its copies.
         const uint32_t fb = (CG == 2) ? mapa_shared(full_bar(stage), 0) : full_bar(stage);
-#ifdef WB200_MMA_CEILING
+#if defined(WB200_MMA_CEILING) && !defined(WB_KEEP_LOADS)
         if (stages_loaded >= STAGES) {
           if (leader && elect_one()) mbar_arrive(full_bar(stage));
           __syncwarp();
@@ -506,7 +506,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
           else mbar_arrive(acc_empty_bar(as));
         }
       };
-#ifdef WB200_MMA_CEILING
+#if defined(WB200_MMA_CEILING) && !defined(WB_KEEP_EPILOGUE)
       release();  // measurement build: the accumulator is neither read nor stored
       ++it;
       continue;

@@ -71,15 +71,17 @@ __device__ __forceinline__ void repack_tile(const uint8_t* __restrict__ src, lon
 // grid (ceil(k_atoms / 8), row_blocks), 256 threads.
 __global__ void __launch_bounds__(256)
 repack_scales_kernel(const uint8_t* __restrict__ src, long long src_row_stride, int rows, int kblocks,
-                     int k_atoms, uint8_t* __restrict__ dst, bool broadcast, bool dependent) {
+                     int k_atoms, uint8_t* __restrict__ dst, bool broadcast, bool dependent, int block_rows = 128) {
   // a GEMM launched behind this kernel as a programmatic dependent may start its set-up now; it waits for
   // this kernel's completion before it reads dst
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // launched as a programmatic dependent itself: the kernel before it may still be reading dst or writing src
   if (dependent) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // block_rows < 128: the tiled packing of the decode kernel, one atom row per tile of block_rows weight rows
+  // (rows block_rows..127 of every atom hold the padding byte)
   const int rb = blockIdx.y;
-  repack_tile(src, src_row_stride, rb * 128, rows, kblocks, k_atoms, blockIdx.x * 8, dst + size_t(rb) * k_atoms * 512,
-              broadcast);
+  repack_tile(src, src_row_stride, rb * block_rows, min(rows, rb * block_rows + block_rows), kblocks, k_atoms,
+              blockIdx.x * 8, dst + size_t(rb) * k_atoms * 512, broadcast);
 }
 
 // Grouped form: the rows of group g are src rows [row_start[g], row_start[g+1]) and its packed block

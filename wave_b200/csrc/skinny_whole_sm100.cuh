@@ -45,7 +45,9 @@ struct SkinnyWholeParams {
   unsigned int* counters;  // zero before the first launch; the kernel leaves them zero
   int M, N, K;
   int ldc;
-  int tiles_n;   // ceil(N / 128)
+  int tiles_n;   // ceil(N / tile_rows)
+  int tile_rows; // weight rows per tile: 128, or fewer (a multiple of 8) when the weight scales were packed per tile of
+                 // that height (wb200_repack_scales_tiled) so that every SM gets the same number of tiles
   int num_kb;    // ceil(K / BK)
   int accumulate;
   int dependent;
@@ -124,9 +126,12 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     const uint32_t sSFX = sSFW + Base::SF_BYTES;
     const uint32_t fb = full_bar(stage);
     if (elect_one()) {
-      if (part != 1) mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+      // a tile of fewer than 128 rows fills the head of the stage's weight area; the MMA still multiplies 128 rows
+      // (whatever bits the rest holds: every E2M1 code is finite, the scales of those lanes are the padding byte)
+      // and the epilogue keeps the tile's own columns
+      if (part != 1) mbar_expect_tx(fb, Cfg::STAGE_BYTES - Base::W_BYTES + uint32_t(p.tile_rows) * 128u);
       if (part != 2) {
-        tma_load_2d_hint(sW, &tmW, kb * 128, tile * 128, fb, stream_policy);
+        tma_load_2d_hint(sW, &tmW, kb * 128, tile * p.tile_rows, fb, stream_policy);
         tma_load_2d(sSFW, &tmSFW, kb * (Base::SF_ATOMS * 128), tile, fb);
       }
       if (part != 1) {
@@ -277,7 +282,8 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
       const int tile = next_tile(seq);
       if (tile < 0) break;
       const int as = seq & 1;
-      const int n = tile * 128 + pcol;  // first of this thread's eight columns
+      const int n = tile * p.tile_rows + pcol;  // first of this thread's eight columns
+      const bool keep = pcol < p.tile_rows;     // tile_rows is a multiple of 8: a piece is all inside or all outside
       mbar_wait(acc_full_bar(as), uint32_t(seq >> 1) & 1u, ctx, WB_DEV_TIMEOUT_EPILOGUE);
       tc_fence_after_sync();
 #ifdef WB200_TRACE
@@ -308,7 +314,7 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
         for (int i = 0; i < 2; ++i) {
           const int mi = prow + 8 * i;
           const int m = c0 + mi;
-          if (m >= p.M || n >= p.N) continue;
+          if (m >= p.M || n >= p.N || !keep) continue;
           const uint32_t src = buf + uint32_t(mi * 128 + pcol) * 4u;
           float4 lo, hi;
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w) : "r"(src) : "memory");

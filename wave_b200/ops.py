@@ -31,12 +31,15 @@ def _as_u8(t: torch.Tensor, what: str) -> torch.Tensor:
 
 
 class PackedScales:
-    """E8M0 scales of a [rows, K/32] matrix in the tcgen05 scale-factor layout (flat uint8)."""
+    """E8M0 scales of a [rows, K/32] matrix in the tcgen05 scale-factor layout (flat uint8). `tile_rows`: rows per
+    512-byte atom row, 128 for the layout every kernel reads; a smaller value marks a WEIGHT packing made for the
+    decode kernel's tile height (`repack_scales(..., tile_rows=decode_tile_rows(N))`), which only the M <= 128
+    path reads."""
 
-    __slots__ = ("data", "rows", "K")
+    __slots__ = ("data", "rows", "K", "tile_rows")
 
-    def __init__(self, data: torch.Tensor, rows: int, K: int):
-        self.data, self.rows, self.K = data, rows, K
+    def __init__(self, data: torch.Tensor, rows: int, K: int, tile_rows: int = 128):
+        self.data, self.rows, self.K, self.tile_rows = data, rows, K, tile_rows
 
     @property
     def device(self):
@@ -47,8 +50,19 @@ def packed_scale_bytes(rows: int, K: int) -> int:
     return int(_lib.load().wb200_packed_scale_bytes(rows, K))
 
 
-def repack_scales(scale: torch.Tensor, out: torch.Tensor | None = None) -> PackedScales:
-    """Row-major [rows, K/32] E8M0 scales -> PackedScales, on the current stream."""
+def decode_tile_rows(N: int, device=None) -> int:
+    """Tile height of the M <= 128 kernel for which every SM of `device` gets the same number of weight tiles (a multiple
+    of 8, at most 128; 128 when the usual packing is as good). Pack a weight's scales with it to use it."""
+    lib = _lib.load()
+    if device is None:
+        return int(lib.wb200_decode_tile_rows(int(N)))
+    with torch.cuda.device(device):
+        return int(lib.wb200_decode_tile_rows(int(N)))
+
+
+def repack_scales(scale: torch.Tensor, out: torch.Tensor | None = None, tile_rows: int = 128) -> PackedScales:
+    """Row-major [rows, K/32] E8M0 scales -> PackedScales, on the current stream. tile_rows < 128: the weight packing
+    of the decode kernel (one atom row per tile of that many rows, see `decode_tile_rows`)."""
     lib = _lib.load()
     _as_u8(scale, "scale")
     if scale.dim() != 2:
@@ -58,20 +72,29 @@ def repack_scales(scale: torch.Tensor, out: torch.Tensor | None = None) -> Packe
     rows, kb = scale.shape
     K = kb * SCALE_GROUP_SIZE
     row_stride = scale.stride(0) if rows > 1 else kb  # the stride of a size-1 dimension is arbitrary
-    nbytes = packed_scale_bytes(rows, K)
+    tiled = tile_rows != 128
+    nbytes = int(lib.wb200_packed_scale_bytes_tiled(rows, K, tile_rows)) if tiled else packed_scale_bytes(rows, K)
+    if tiled and nbytes == 0:
+        raise ValueError(f"repack_scales: {tile_rows} rows per tile (8 .. 128 in steps of 8)")
     if out is None:
         out = torch.empty(nbytes, dtype=torch.uint8, device=scale.device)
     elif out.numel() < nbytes or out.dtype != torch.uint8 or not out.is_contiguous():
         raise ValueError("repack_scales: `out` must be a contiguous uint8 tensor of at least packed_scale_bytes(rows, K)")
+
+    def run():
+        if tiled:
+            return lib.wb200_repack_scales_tiled(scale.data_ptr(), row_stride, rows, K, tile_rows, out.data_ptr(), _stream())
+        return lib.wb200_repack_scales(scale.data_ptr(), row_stride, rows, K, out.data_ptr(), _stream())
+
     dev_index = scale.device.index
     if dev_index is None or dev_index == torch.cuda.current_device():
-        rc = lib.wb200_repack_scales(scale.data_ptr(), row_stride, rows, K, out.data_ptr(), _stream())
+        rc = run()
     else:
         with torch.cuda.device(scale.device):
-            rc = lib.wb200_repack_scales(scale.data_ptr(), row_stride, rows, K, out.data_ptr(), _stream())
+            rc = run()
     if rc:
         _lib.check(rc)
-    return PackedScales(out, rows, K)
+    return PackedScales(out, rows, K, tile_rows)
 
 
 def repack_scales_broadcast(scale: torch.Tensor, K: int, out: torch.Tensor | None = None) -> PackedScales:
@@ -179,6 +202,12 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
         raise ValueError(f"a and b disagree on K: {K} vs {b.shape[1] * 2}")
     if (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
         raise ValueError("packed scales do not match the operand shapes")
+    if a_sf.tile_rows != 128:
+        raise ValueError("a's scales must be in the usual packing (tile_rows = 128)")
+    if b_sf.tile_rows != 128:
+        if M > 128:
+            raise ValueError(f"b's scales are packed per {b_sf.tile_rows}-row tile, which only the M <= 128 kernel reads (M = {M})")
+        flags |= _lib.B_TILE_ROWS(b_sf.tile_rows)
     ldc = c.stride(0) if M > 1 else N  # the stride of a size-1 dimension is arbitrary
     ws_ptr = ws_bytes = 0
     if M <= 128 or (flags & _lib.PATH_MASK) == _lib.PATH_TILE_SPLITK or split_k_pays():
@@ -236,6 +265,8 @@ def scaled_gemm_mxfp8_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tenso
             raise ValueError(f"{name} must be a contiguous 2-D CUDA tensor of 8-bit elements")
     M, K = a.shape
     N = b.shape[0]
+    if a_sf.tile_rows != 128 or b_sf.tile_rows != 128:
+        raise ValueError("the MXFP8 GEMM reads the usual scale packing only (tile_rows = 128)")
     if b.shape[1] != K or (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
         raise ValueError("operand and scale shapes do not agree")
     if c.dtype not in _DTYPE_CODE or tuple(c.shape) != (M, N) or c.stride(1) != 1:
@@ -264,8 +295,8 @@ class WeightScaleCache:
         self.capacity = capacity
         self._entries: OrderedDict = OrderedDict()
 
-    def get(self, scale: torch.Tensor) -> PackedScales:
-        key = (scale.data_ptr(), tuple(scale.shape), scale.stride(), scale.device.index, scale._version)
+    def get(self, scale: torch.Tensor, tile_rows: int = 128) -> PackedScales:
+        key = (scale.data_ptr(), tuple(scale.shape), scale.stride(), scale.device.index, scale._version, tile_rows)
         hit = self._entries.get(key)
         if hit is not None:
             owner, packed = hit
@@ -273,7 +304,7 @@ class WeightScaleCache:
                 self._entries.move_to_end(key)
                 return packed
             del self._entries[key]  # same address, another (or a dead) tensor: the packing is not this tensor's
-        packed = repack_scales(scale)
+        packed = repack_scales(scale, tile_rows=tile_rows)
         self._entries[key] = (weakref.ref(scale), packed)
         while len(self._entries) > self.capacity:
             self._entries.popitem(last=False)
