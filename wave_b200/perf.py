@@ -458,7 +458,8 @@ def skinny_timeline(M: int, N: int, K: int, launches: int = 12, save: str | None
         b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
         a_s = torch.randint(124, 128, (M, K // 32), dtype=torch.uint8, device=dev, generator=g)
         b_s = torch.randint(124, 128, (N, K // 32), dtype=torch.uint8, device=dev, generator=g)
-        sets.append((a, ops.repack_scales(a_s), b, ops.repack_scales(b_s), torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+        sets.append((a, ops.repack_scales(a_s), b, ops.repack_scales(b_s, tile_rows=ops.decode_tile_rows(N, dev)),
+                     torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
     ctas = torch.cuda.get_device_properties(dev).multi_processor_count
     records = []
     for it in range(launches):
