@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this folder from the reference itself.
 
-Run in the build container, where the reference tree is mounted read-only:
+Run where a checkout of the reference (iree-org/wave) is at hand, giving its path:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 It imports the reference's own module `wave_lang/kernel/wave/utils/mxfp_utils.py` and the torch
 helper `tests/kernel/moe/torch_kernels.py` (both pure torch; they run on the CPU without the
@@ -120,4 +120,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])

@@ -891,29 +891,41 @@ def test_broadcasted_scale_gemm_as_the_reference_tests_it():
 @pytest.mark.parametrize("ways", [8, 2])
 def test_config5_one_shard_of_the_sharded_gemm_bf16_sampled(ways):
     """M = 16384, N = 53248, K = 16384 sharded over `ways` GPUs by rows of b: one GPU's shard
-    (N / ways = 6656 or 26624 rows) at full size. Operands are seeded N(0, 1) matrices quantised on the GPU
-    (the quantiser is bit-exact against the oracle's, tested above); the oracle is evaluated for sampled rows of
-    a against sampled row blocks of the shard, and the whole shard is checked through the exact doubling property."""
+    (N / ways = 6656 or 26624 rows) at full size. Operands are seeded f32 N(0, 1) matrices (seeds 1005 / 2005)
+    quantised on the GPU (the quantiser is bit-exact against the oracle's, tested above); the oracle is evaluated for
+    sampled rows of a against sampled row blocks of the shard, and the whole shard is checked through the exact
+    doubling property. Bar: 1 bf16 ulp of the rounded f32 reference. An entry further away passes only where the f32
+    bound holds (a sum that cancels far below its terms, so that the accumulation order moves it across more than one
+    bf16 step); such entries are counted and reported, and there may be at most one in ten thousand."""
     M, N, K = 16384, 53248, 16384
     n_shard = N // ways
     assert n_shard % 256 == 0
     g = torch.Generator(device=DEV).manual_seed(1005)
-    a, a_s, _ = ops.quantize_mxfp4(torch.randn(M, K, device=DEV, generator=g, dtype=torch.bfloat16), want_packed=False)
+    a, a_s, _ = ops.quantize_mxfp4(torch.randn(M, K, device=DEV, generator=g, dtype=torch.float32), want_packed=False)
     g.manual_seed(2005)
-    b, b_s, _ = ops.quantize_mxfp4(torch.randn(n_shard, K, device=DEV, generator=g, dtype=torch.bfloat16), want_packed=False)
+    b, b_s, _ = ops.quantize_mxfp4(torch.randn(n_shard, K, device=DEV, generator=g, dtype=torch.float32), want_packed=False)
     kernel, options = wb.get_tagged_mxfp4_gemm((M, n_shard, K), output_dtype=wb.bf16)
     gemm = wb.wave_compile(options, kernel)
     c = torch.empty(M, n_shard, dtype=torch.bfloat16, device=DEV)
     gemm(a, a_s, b, b_s, c)
     rows = torch.arange(0, M, 683, device=DEV)
+    escaped = checked = 0
     for n0 in (0, (n_shard // 2) // 256 * 256 + 128, n_shard - 1024):
         ref = orc.scaled_gemm(a[rows].cpu(), a_s[rows].cpu(), b[n0:n0 + 1024].cpu(), b_s[n0:n0 + 1024].cpu())
         got = c[rows][:, n0:n0 + 1024].contiguous()
         ulp = orc.bf16_ulp_distance(got, ref)
         tol = orc.f32_tolerance(orc.dequant_mxfp4(a[rows].cpu(), a_s[rows].cpu()),
                                 orc.dequant_mxfp4(b[n0:n0 + 1024].cpu(), b_s[n0:n0 + 1024].cpu()), ref, K)
-        bad = (ulp > 1) & ~((got.float().cpu() - ref).abs() <= tol + ref.abs() * 2.0 ** -8)
-        assert not bool(bad.any()) and float((ulp > 1).float().mean()) < 1e-3
+        within_f32 = (got.float().cpu() - ref).abs() <= tol
+        failed = (ulp > 1) & ~within_f32
+        assert not bool(failed.any()), f"{int(failed.sum())} entries beyond 1 bf16 ulp and beyond the f32 bound (max {int(ulp.max())} ulp)"
+        escaped += int(((ulp > 1) & within_f32).sum())
+        checked += ulp.numel()
+    if escaped:
+        import warnings
+        warnings.warn(f"config 5, {ways}-way shard: {escaped} of {checked} sampled entries are more than 1 bf16 ulp from the "
+                      "rounded reference and pass by the f32 bound")
+    assert escaped * 10000 <= checked
     c2 = torch.empty_like(c)
     gemm(a, a_s + 1, b, b_s, c2)
     assert torch.equal((c.float() * 2).to(torch.bfloat16), c2)

@@ -385,11 +385,11 @@ int launch_grouped(const DeviceInfo& dev, int num_groups, const int* row_offsets
 }
 
 // Grouped GEMM over a block-aligned row layout described by DEVICE arrays (see GroupedMaps::aligned).
-template <typename OutT>
+template <typename OutT, int BN = 256>
 int launch_aligned(const DeviceInfo& dev, int num_groups, int max_rows, const int* expert_ids, const int* num_rows, int N, int K,
                    const void* a, const void* a_sf, const void* const* b_ptrs, const void* const* b_sf_ptrs, void* c,
                    long long ldc, cudaStream_t stream) {
-  constexpr int CG = 2, BN = 256;
+  constexpr int CG = 2;
   using Cfg = wb::GemmCfg<CG, BN, int(sizeof(OutT))>;
   static wb::GroupedMaps maps;
   static std::mutex mu;
@@ -412,7 +412,7 @@ int launch_aligned(const DeviceInfo& dev, int num_groups, int max_rows, const in
     if ((rc = make_operand_map(m + 0, a, max_rows, K / 2, Cfg::BM))) return rc;
     if ((rc = make_operand_map(m + 1, b_ptrs[g], N, K / 2, Cfg::B_ROWS))) return rc;
     if ((rc = make_scale_map(m + 2, a_sf, wb::sf_row_blocks(max_rows), k_atoms, 1))) return rc;
-    if ((rc = make_scale_map(m + 3, b_sf_ptrs[g], wb::sf_row_blocks(N), k_atoms, BN / 128))) return rc;
+    if ((rc = make_scale_map(m + 3, b_sf_ptrs[g], wb::sf_row_blocks(N), k_atoms, Cfg::SFB_BLOCKS))) return rc;
     if ((rc = make_output_map(m + 4, c, max_rows, N, ldc, esz))) return rc;
   }
   wb::GemmParams p = {};
@@ -1357,6 +1357,14 @@ int wb200_mxfp4_moe_gemm(int num_experts, int max_rows, const int* expert_ids, c
   DeviceInfo* dev;
   int rc = get_device(&dev);
   if (rc) return rc;
+  static const bool narrow = getenv("WB200_MOE_BN192") != nullptr;  // EXPERIMENT
+  if (narrow) {
+    if (c_dtype == WB200_F32)
+      return launch_aligned<float, 192>(*dev, num_experts, max_rows, expert_ids, num_rows, N, K, a, a_scale_packed, b_ptrs, b_scale_ptrs,
+                                        c, ldc, static_cast<cudaStream_t>(stream));
+    return launch_aligned<__nv_bfloat16, 192>(*dev, num_experts, max_rows, expert_ids, num_rows, N, K, a, a_scale_packed, b_ptrs,
+                                              b_scale_ptrs, c, ldc, static_cast<cudaStream_t>(stream));
+  }
   if (c_dtype == WB200_F32)
     return launch_aligned<float>(*dev, num_experts, max_rows, expert_ids, num_rows, N, K, a, a_scale_packed, b_ptrs, b_scale_ptrs,
                                  c, ldc, static_cast<cudaStream_t>(stream));
