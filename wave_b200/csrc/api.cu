@@ -1357,14 +1357,6 @@ int wb200_mxfp4_moe_gemm(int num_experts, int max_rows, const int* expert_ids, c
   DeviceInfo* dev;
   int rc = get_device(&dev);
   if (rc) return rc;
-  static const bool narrow = getenv("WB200_MOE_BN192") != nullptr;  // EXPERIMENT
-  if (narrow) {
-    if (c_dtype == WB200_F32)
-      return launch_aligned<float, 192>(*dev, num_experts, max_rows, expert_ids, num_rows, N, K, a, a_scale_packed, b_ptrs, b_scale_ptrs,
-                                        c, ldc, static_cast<cudaStream_t>(stream));
-    return launch_aligned<__nv_bfloat16, 192>(*dev, num_experts, max_rows, expert_ids, num_rows, N, K, a, a_scale_packed, b_ptrs,
-                                              b_scale_ptrs, c, ldc, static_cast<cudaStream_t>(stream));
-  }
   if (c_dtype == WB200_F32)
     return launch_aligned<float>(*dev, num_experts, max_rows, expert_ids, num_rows, N, K, a, a_scale_packed, b_ptrs, b_scale_ptrs,
                                  c, ldc, static_cast<cudaStream_t>(stream));
