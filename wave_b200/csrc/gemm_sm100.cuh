@@ -512,6 +512,10 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
       continue;
 #endif
       constexpr int NCHUNK = BN / 32;
+      // Overlapping accumulators: the MMA warp cannot start the next tile before the shared columns are read. Both
+      // shared chunks are therefore fetched at once, ahead of any staging, and the accumulator is handed back as soon
+      // as they are in registers; `held` keeps the second chunk until its turn.
+      [[maybe_unused]] uint32_t held[32];
 #pragma unroll 1
       for (int ci = 0; ci < NCHUNK; ++ci) {
         // With overlapping accumulators the columns shared with the other accumulator go first:
@@ -522,10 +526,23 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
             chunk = (ci < Cfg::OVERLAP_CHUNKS) ? (NCHUNK - Cfg::OVERLAP_CHUNKS + ci) : (ci - Cfg::OVERLAP_CHUNKS);
         }
         uint32_t r[32];
-        tmem_ld_32x32(t_acc + chunk * 32, r);
-        tmem_ld_wait();
         if constexpr (Cfg::OVERLAP) {
-          if (ci == Cfg::OVERLAP_CHUNKS - 1) release();
+          static_assert(Cfg::OVERLAP_CHUNKS == 2, "the early hand-back below fetches exactly two shared chunks");
+          if (ci == 0) {
+            tmem_ld_32x32(t_acc + chunk * 32, r);
+            tmem_ld_32x32(t_acc + (chunk + 1) * 32, held);
+            tmem_ld_wait();
+            release();
+          } else if (ci == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = held[j];
+          } else {
+            tmem_ld_32x32(t_acc + chunk * 32, r);
+            tmem_ld_wait();
+          }
+        } else {
+          tmem_ld_32x32(t_acc + chunk * 32, r);
+          tmem_ld_wait();
         }
         const int col = col0 + chunk * 32;
         if (p.tma_store) {
