@@ -75,8 +75,11 @@ extern "C" {
 #define WB200_GROUP_N(g) (((unsigned)(g) << WB200_GROUP_N_SHIFT) & WB200_GROUP_N_MASK)
 #define WB200_GROUP_N_ALL WB200_GROUP_N(255)
 /* The weight scales (b_scale_packed) were packed per tile of h weight rows by wb200_repack_scales_tiled instead of per
- * 128-row block: h / 8 in bits 16..20 (h = 8 .. 128 in steps of 8; 0 or 128 = the usual packing). Read by the M <= 128
- * kernel only (WB200_PATH_AUTO with a workspace, or WB200_PATH_SKINNY); h is wb200_decode_tile_rows(N). */
+ * 128-row block: h / 8 in bits 16..20 (h = 8 .. 128 in steps of 8; 0 or 128 = the usual packing). Heights up to 128 are read by
+ * the M <= 128 kernel only (WB200_PATH_AUTO with a workspace, or WB200_PATH_SKINNY); h is wb200_decode_tile_rows(N). */
+/* h = 224 is the one height above 128: it selects the CTA-pair tile kernel with 224-column tiles (M > 128, WB200_PATH_AUTO
+ * or WB200_PATH_TILE_2CTA), whose two accumulators sit side by side in tensor memory; its scales are packed two atom rows
+ * per 224-row tile. Same results as the 256-wide tiles; measured no faster, kept as an option. */
 #define WB200_B_TILE_ROWS_SHIFT 16
 #define WB200_B_TILE_ROWS_MASK 0x1F0000u
 #define WB200_B_TILE_ROWS(h) ((((unsigned)(h) / 8u) << WB200_B_TILE_ROWS_SHIFT) & WB200_B_TILE_ROWS_MASK)

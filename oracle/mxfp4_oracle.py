@@ -130,16 +130,18 @@ def pack_scales(scale: torch.Tensor) -> torch.Tensor:
 
 
 def pack_scales_tiled(scale: torch.Tensor, tile_rows: int) -> torch.Tensor:
-    """Weight-scale packing of the decode kernel: the rows are cut into tiles of `tile_rows` (a multiple of 8, at
-    most 128) and every tile gets an atom row of its own, its rows in atom rows 0 .. tile_rows - 1 and the padding byte
-    above; inside an atom the layout is `pack_scales`'s. tile_rows = 128 is `pack_scales` itself."""
-    assert tile_rows % 8 == 0 and 8 <= tile_rows <= 128
+    """Weight-scale packing per tile of `tile_rows` rows. Up to 128 (a multiple of 8; the decode kernel's tiles): every
+    tile gets an atom row of its own, its rows in atom rows 0 .. tile_rows - 1 and the padding byte above. 224 (the
+    tile kernel's 224-column tiles): two atom rows per tile, rows 0..127 and 128..223 of the tile. Inside an atom the
+    layout is `pack_scales`'s; tile_rows = 128 is `pack_scales` itself."""
+    assert tile_rows == 224 or (tile_rows % 8 == 0 and 8 <= tile_rows <= 128)
     rows, kb = scale.shape
     tiles = (rows + tile_rows - 1) // tile_rows
-    spread = torch.full((tiles * 128, kb), SF_PAD, dtype=torch.uint8)
+    span = (tile_rows + 127) // 128 * 128  # rows of packed storage per tile
+    spread = torch.full((tiles * span, kb), SF_PAD, dtype=torch.uint8)
     for t in range(tiles):
         part = scale[t * tile_rows:min(rows, (t + 1) * tile_rows)]
-        spread[t * 128:t * 128 + part.shape[0]] = part
+        spread[t * span:t * span + part.shape[0]] = part
     return pack_scales(spread)
 
 

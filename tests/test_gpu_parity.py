@@ -426,7 +426,8 @@ def test_skinny_path_with_dealt_parts(M, N, K, out_dtype, accumulate):
         assert torch.equal(outs[0].view(bits), c.view(bits))
 
 
-@pytest.mark.parametrize("rows,K,tile_rows", [(300, 768, 104), (28672 // 8, 512, 104), (97, 96, 96), (1000, 256, 8), (256, 1024, 128)])
+@pytest.mark.parametrize("rows,K,tile_rows", [(300, 768, 104), (28672 // 8, 512, 104), (97, 96, 96), (1000, 256, 8), (256, 1024, 128),
+                                              (224, 256, 224), (1000, 288, 224), (8192, 512, 224)])
 def test_tiled_weight_scale_packing_is_bit_exact(rows, K, tile_rows):
     s = torch.randint(0, 255, (rows, K // 32), dtype=torch.uint8, generator=torch.Generator().manual_seed(rows + tile_rows))
     packed = ops.repack_scales(s.to(DEV), tile_rows=tile_rows)
@@ -464,6 +465,27 @@ def test_decode_kernel_with_weight_scales_packed_per_balanced_tile(M, out_dtype)
     c2 = torch.ones(M, N2, dtype=out_dtype, device=DEV)
     ops.scaled_gemm_packed(ad, a_sf, bd[:N2].contiguous(), t2, c2, _lib.PATH_SKINNY | _lib.ACCUMULATE)
     check(c2, a, a_s, b[:N2], b_s[:N2], orc.scaled_gemm(a, a_s, b[:N2], b_s[:N2]) + 1.0)
+
+
+@pytest.mark.parametrize("shape", [(256, 224, 256), (300, 1000, 288), (1024, 2304, 1024), (2048, 4096, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_224_wide_tiles_on_weight_scales_packed_for_them(shape, out_dtype):
+    """CTA-pair tiles of 224 columns: two accumulators side by side in tensor memory (no hand-over between tiles), read
+    from weight scales packed two atom rows per 224-row tile. Same bits as the 256-wide kernel (each output's sum over
+    K is made in the same order)."""
+    M, N, K = shape
+    a, a_s, b, b_s = random_problem(M, N, K, seed=M + N)
+    ad, bd, a_sf = a.to(DEV), b.to(DEV), ops.repack_scales(a_s.to(DEV))
+    c224 = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_packed(ad, a_sf, bd, ops.repack_scales(b_s.to(DEV), tile_rows=224), c224)
+    check(c224, a, a_s, b, b_s)
+    c256 = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_packed(ad, a_sf, bd, ops.repack_scales(b_s.to(DEV)), c256, _lib.PATH_TILE_2CTA)
+    bits = torch.int16 if out_dtype == torch.bfloat16 else torch.int32
+    assert torch.equal(c224.view(bits), c256.view(bits))
+    with pytest.raises(Exception):  # forcing another width on scales packed for 224 is refused
+        ops.scaled_gemm_packed(ad, a_sf, bd, ops.repack_scales(b_s.to(DEV), tile_rows=224), c224, _lib.PATH_TILE_2CTA | _lib.TILE_N128)
+    ops.check_device_status()
 
 
 def test_tiled_weight_scales_are_refused_where_no_kernel_reads_them():

@@ -42,8 +42,8 @@ B_TILE_ROWS_MASK = 0x1F0000
 
 def B_TILE_ROWS(h: int) -> int:
     """Flag bits saying that b's scales were packed per tile of h weight rows (include/wave_b200.h, WB200_B_TILE_ROWS)."""
-    if h % 8 or not 8 <= h <= 128:
-        raise ValueError(f"{h} rows per tile: 8 .. 128 in steps of 8")
+    if h != 224 and (h % 8 or not 8 <= h <= 128):
+        raise ValueError(f"{h} rows per tile: 8 .. 128 in steps of 8, or 224")
     return 0 if h == 128 else (h // 8) << 16
 
 

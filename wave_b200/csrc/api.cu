@@ -302,6 +302,7 @@ int dispatch_tile(unsigned path, int bn, int c_dtype, const DeviceInfo& dev, int
   if (path == WB200_PATH_TILE_2CTA) {
     if (bn == 128) return launch_tile_dtype<2, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
     if (bn == 192) return launch_tile_dtype<2, 192>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
+    if (bn == 224) return launch_tile_dtype<2, 224>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, (N + 223) / 224 * 2, accumulate, stream);
     return launch_tile_dtype<2, 256>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
   }
   if (bn == 128) return launch_tile_dtype<1, 128>(c_dtype, dev, M, N, K, a, as, b, bs, c, ldc, sfa_rb, sfb_rb, accumulate, stream);
@@ -806,11 +807,12 @@ int wb200_decode_tile_rows(int N) {
   return decode_tile_rows(dev->sm_count, N);
 }
 
-static bool tile_rows_ok(int tile_rows) { return tile_rows >= 8 && tile_rows <= 128 && tile_rows % 8 == 0; }
+static bool tile_rows_ok(int tile_rows) { return (tile_rows >= 8 && tile_rows <= 128 && tile_rows % 8 == 0) || tile_rows == 224; }
+static int tiled_row_blocks(int rows, int tile_rows) { return (rows + tile_rows - 1) / tile_rows * ((tile_rows + 127) / 128); }
 
 size_t wb200_packed_scale_bytes_tiled(int rows, int K, int tile_rows) {
   if (rows <= 0 || K <= 0 || !tile_rows_ok(tile_rows)) return 0;
-  return size_t((rows + tile_rows - 1) / tile_rows) * wb::sf_k_atoms(K) * 512;
+  return size_t(tiled_row_blocks(rows, tile_rows)) * wb::sf_k_atoms(K) * 512;
 }
 
 static int repack_scales_impl(const void* src, long long src_row_stride, int rows, int K, void* dst, void* stream,
@@ -825,7 +827,7 @@ static int repack_scales_impl(const void* src, long long src_row_stride, int row
   int rc = get_device(&dev);
   if (rc) return rc;
   const int k_atoms = wb::sf_k_atoms(K);
-  dim3 grid((k_atoms + 7) / 8, (rows + block_rows - 1) / block_rows);
+  dim3 grid((k_atoms + 7) / 8, tiled_row_blocks(rows, block_rows));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(256, 1, 1);
@@ -841,7 +843,8 @@ static int repack_scales_impl(const void* src, long long src_row_stride, int row
 }
 
 int wb200_repack_scales_tiled(const void* src, long long src_row_stride, int rows, int K, int tile_rows, void* dst, void* stream) {
-  if (!tile_rows_ok(tile_rows)) return fail(WB200_ERR_INVALID_ARG, "repack_scales_tiled: %d rows per tile (8 .. 128 in steps of 8)", tile_rows);
+  if (!tile_rows_ok(tile_rows))
+    return fail(WB200_ERR_INVALID_ARG, "repack_scales_tiled: %d rows per tile (8 .. 128 in steps of 8, or 224)", tile_rows);
   return repack_scales_impl(src, src_row_stride, rows, K, dst, stream, false, tile_rows);
 }
 
@@ -1167,8 +1170,14 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
     explicit TileRowsScope(int h) : saved(tl_b_tile_rows) { tl_b_tile_rows = h; }
     ~TileRowsScope() { tl_b_tile_rows = saved; }
   } tile_rows_scope(b_tile_rows_from_flags(flags));
-  if (tl_b_tile_rows != 128) {
-    if (tl_b_tile_rows > 128) return fail(WB200_ERR_INVALID_ARG, "WB200_B_TILE_ROWS: %d rows per tile (8 .. 128 in steps of 8)", tl_b_tile_rows);
+  const bool wide224 = tl_b_tile_rows == 224;  // weight scales packed for the tile kernel's 224-column tiles
+  if (wide224) {
+    if (M <= 128 || (path != WB200_PATH_AUTO && path != WB200_PATH_TILE_2CTA) || (flags & (WB200_TILE_N128 | WB200_TILE_N192)))
+      return fail(WB200_ERR_UNSUPPORTED, "weight scales packed per 224-row tile are read by the CTA-pair tile kernel only (M > 128, "
+                  "WB200_PATH_AUTO or WB200_PATH_TILE_2CTA, no other tile width forced; M = %d, flags %#x)", M, flags);
+    path = WB200_PATH_TILE_2CTA;
+  } else if (tl_b_tile_rows != 128) {
+    if (tl_b_tile_rows > 128) return fail(WB200_ERR_INVALID_ARG, "WB200_B_TILE_ROWS: %d rows per tile (8 .. 128 in steps of 8, or 224)", tl_b_tile_rows);
     if (M > 128 || (path != WB200_PATH_AUTO && path != WB200_PATH_SKINNY))
       return fail(WB200_ERR_UNSUPPORTED, "weight scales packed per %d-row tile are read by the M <= 128 kernel only (M = %d, path %u)",
                   tl_b_tile_rows, M, path);
@@ -1193,7 +1202,7 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
     else if (splitk_ok && slices >= 3 && !(flags & (WB200_TILE_N128 | WB200_TILE_N192))) path = WB200_PATH_TILE_SPLITK;
     else path = (M > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
   }
-  if (tl_b_tile_rows != 128 && path != WB200_PATH_SKINNY)
+  if (tl_b_tile_rows != 128 && !wide224 && path != WB200_PATH_SKINNY)
     return fail(WB200_ERR_WORKSPACE, "weight scales packed per %d-row tile need the M <= 128 kernel, which needs a workspace of %zu bytes",
                 tl_b_tile_rows, skinny_workspace_bytes(dev->sm_count, M));
   if (path == WB200_PATH_TILE_SPLITK) {
@@ -1236,6 +1245,7 @@ int wb200_mxfp4_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
       if (w192 * 1045 < w256 * 1000) bn = 192;
     }
   }
+  if (wide224) bn = 224;
   return dispatch_tile(path, bn, c_dtype, *dev, M, N, K, a, a_scale_packed, b, b_scale_packed, c, ldc,
                        wb::sf_row_blocks(M), wb::sf_row_blocks(N), accumulate, s);
 }

@@ -47,7 +47,10 @@ struct GemmCfg {
   // tile starts at column 0 or 2 of a block and ends inside the next one: the kernel loads both
   // blocks and points the MMA at the column the tile starts with. (The MMA takes even column
   // offsets only: an odd one, as a 224-row tile would need, raises a misaligned-address fault.)
-  static constexpr int SFB_BLOCKS = (BN % 128 == 0) ? BN / 128 : (BN + 64 + 127) / 128;
+  // A 224-row tile would start on odd columns too, so it reads a packing of the weight scales made for it: two
+  // blocks per tile (rows 0..127 and 128..223 of the tile), the tile always at column 0 (wb200_repack_scales_tiled).
+  static constexpr bool TILED_SFB = (BN == 224);
+  static constexpr int SFB_BLOCKS = (BN % 128 == 0) ? BN / 128 : TILED_SFB ? 2 : (BN + 64 + 127) / 128;
   static constexpr int SFB_BYTES = SFB_BLOCKS * SF_ATOMS * 512;
   static constexpr int LOAD_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;  // what the loads of a stage deliver
   static constexpr int STAGE_BYTES = (LOAD_BYTES + 1023) / 1024 * 1024;
@@ -71,7 +74,8 @@ struct GemmCfg {
   // not have to wait for the MMAs of the previous block to finish reading theirs.
   // (sized for two atoms per 128 rows also when a stage has one, so that the accumulators sit at the same columns)
   static constexpr int SF_SET_COLS = 8 + SFB_BLOCKS * 8;  // A: 2 atoms x 4 columns, B: blocks x 2 atoms x 4
-  static constexpr int SF_SETS = OVERLAP ? 2 : 4;
+  static constexpr int SF_SETS = OVERLAP ? 2 : ((512 - 2 * BN) / SF_SET_COLS >= 4 ? 4 : (512 - 2 * BN) / SF_SET_COLS);
+  static_assert(SF_SETS >= 2, "the scale-factor ring needs two column sets");
   static constexpr int SF_COL = OVERLAP ? 512 - SF_SETS * SF_SET_COLS : 2 * BN;
   // 32-column chunks shared by the two accumulators: accumulator 1 ends where the scale factors begin
   static constexpr int OVERLAP_CHUNKS = (2 * 256 - SF_COL + 31) / 32;
@@ -79,8 +83,8 @@ struct GemmCfg {
   static_assert(SF_COL + SF_SETS * SF_SET_COLS <= 512, "scale-factor ring does not fit in tensor memory");
   static_assert(!OVERLAP || OVERLAP_CHUNKS % 2 == 0, "bf16 stores pair neighbouring chunks; the shared columns must be whole pairs");
   static constexpr int THREADS = 192;
-  static_assert(BN == 128 || BN == 192 || BN == 256, "BN must be 128, 192 or 256");
-  static_assert(BN % 64 == 0, "tiles start on even scale columns and are stored as whole pairs of 32-column chunks");
+  static_assert(BN == 128 || BN == 192 || BN == 224 || BN == 256, "BN must be 128, 192, 224 or 256");
+  static_assert(BN % 64 == 0 || TILED_SFB, "tiles start on even scale columns unless the scales are packed per tile");
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 };
 
@@ -356,7 +360,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
       const int a_row = (mt * CG + int(rank)) * Cfg::BM;
       const int b_row = nt * BN + int(rank) * Cfg::B_ROWS;
       const int sfa_rb = mt * CG + int(rank);
-      const int sfb_rb = (nt * BN) / 128;
+      const int sfb_rb = Cfg::TILED_SFB ? nt * Cfg::SFB_BLOCKS : (nt * BN) / 128;
       for (int kb = 0; kb < num_kb; ++kb) {
         mbar_wait(empty_bar(stage), phase ^ 1u, ctx, WB_DEV_TIMEOUT_PRODUCER);
         const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
@@ -399,7 +403,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
       for (int t = first_tile; t < num_tiles; t += tile_step) {
         // first 32-row group of this tile inside its first 128-row scale block = first scale column (0 or 2)
         uint32_t sfb_group = 0;
-        if constexpr (BN % 128 != 0 || Maps::kGrouped) {
+        if constexpr ((BN % 128 != 0 && !Cfg::TILED_SFB) || Maps::kGrouped) {
           int mt, nt, rows;
           if (decode_tile(maps, p, t, mt, nt, rows) == nullptr) continue;
           sfb_group = uint32_t((nt * BN) % 128) / 32u;
@@ -545,7 +549,11 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
           tmem_ld_wait();
         }
         const int col = col0 + chunk * 32;
-        if (p.tma_store) {
+        // bf16 stores go out as pairs of chunks (whole 128-byte lines); with an odd number of chunks (224 columns)
+        // the last one has no partner and is written with direct 16-byte stores instead
+        constexpr bool kOddChunks = (sizeof(OutT) == 2) && (NCHUNK % 2 == 1);
+        const bool lone = kOddChunks && ci == NCHUNK - 1;
+        if (p.tma_store && !lone) {
           // Two staging buffers per warp; a store covers one f32 chunk or a pair of bf16 chunks (the
           // chunk order above keeps pairs together). Before a buffer is refilled, the store issued
           // two stores ago must have read it.

@@ -77,11 +77,16 @@ repack_scales_kernel(const uint8_t* __restrict__ src, long long src_row_stride, 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // launched as a programmatic dependent itself: the kernel before it may still be reading dst or writing src
   if (dependent) asm volatile("griddepcontrol.wait;" ::: "memory");
-  // block_rows < 128: the tiled packing of the decode kernel, one atom row per tile of block_rows weight rows
-  // (rows block_rows..127 of every atom hold the padding byte)
+  // block_rows != 128: a packing per tile of block_rows weight rows. Up to 128: one atom row per tile (the decode
+  // kernel's tiles; rows block_rows..127 of every atom hold the padding byte). Above 128 (224: the tile kernel's
+  // 224-column tiles): two atom rows per tile, rows 0..127 and 128..block_rows-1 of the tile.
   const int rb = blockIdx.y;
-  repack_tile(src, src_row_stride, rb * block_rows, min(rows, rb * block_rows + block_rows), kblocks, k_atoms,
-              blockIdx.x * 8, dst + size_t(rb) * k_atoms * 512, broadcast);
+  const int per_tile = (block_rows + 127) / 128;
+  const int tile = rb / per_tile, part = rb - tile * per_tile;
+  const int row_base = tile * block_rows + part * 128;
+  const int row_end = tile * block_rows + min(block_rows, (part + 1) * 128);
+  repack_tile(src, src_row_stride, row_base, min(rows, row_end), kblocks, k_atoms, blockIdx.x * 8,
+              dst + size_t(rb) * k_atoms * 512, broadcast);
 }
 
 // Grouped form: the rows of group g are src rows [row_start[g], row_start[g+1]) and its packed block

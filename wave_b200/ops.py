@@ -205,8 +205,9 @@ def scaled_gemm_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_s
     if a_sf.tile_rows != 128:
         raise ValueError("a's scales must be in the usual packing (tile_rows = 128)")
     if b_sf.tile_rows != 128:
-        if M > 128:
-            raise ValueError(f"b's scales are packed per {b_sf.tile_rows}-row tile, which only the M <= 128 kernel reads (M = {M})")
+        if (M > 128) != (b_sf.tile_rows == 224):
+            raise ValueError(f"b's scales are packed per {b_sf.tile_rows}-row tile: 224 is read by the M > 128 tile kernel, "
+                             f"smaller heights by the M <= 128 kernel (M = {M})")
         flags |= _lib.B_TILE_ROWS(b_sf.tile_rows)
     ldc = c.stride(0) if M > 1 else N  # the stride of a size-1 dimension is arbitrary
     ws_ptr = ws_bytes = 0

@@ -331,9 +331,13 @@ def _interleaved_times(launchers, rounds=10, launches_per_replay=8):
     return [statistics.median(t[2:]) for t in times]
 
 
+_rowmajor_scales = {}  # the row-major weight scales of the last _packed_problem, for other packings of them
+
+
 def _packed_problem(M, N, K, device):
     from . import generate_gemm_afp4wfp4_inputs, ops
     x, w, xs, ws = generate_gemm_afp4wfp4_inputs((M, N, K), device=torch.device(device))
+    _rowmajor_scales["b"] = ws
     w_t = w.T.contiguous()
     return x, ops.repack_scales(xs), w_t, ops.repack_scales(ws), torch.empty(M, N, dtype=torch.bfloat16, device=device)
 
@@ -358,7 +362,12 @@ def tile_variants(M: int, N: int, K: int, device="cuda:0"):
     names = {"auto": _lib.PATH_AUTO, "2cta-256": _lib.PATH_TILE_2CTA, "2cta-192": _lib.PATH_TILE_2CTA | _lib.TILE_N192,
              "2cta-128": _lib.PATH_TILE_2CTA | _lib.TILE_N128, "1cta-256": _lib.PATH_TILE_1CTA,
              "1cta-128": _lib.PATH_TILE_1CTA | _lib.TILE_N128}
-    us = _interleaved_times([lambda f=f: ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c, f) for f in names.values()])
+    launchers = [lambda f=f: ops.scaled_gemm_packed(x, a_sf, w_t, b_sf, c, f) for f in names.values()]
+    if M > 128:  # 224-wide tiles read weight scales packed for them
+        b_224 = ops.repack_scales(_rowmajor_scales["b"], tile_rows=224)
+        names["2cta-224"] = None
+        launchers.append(lambda: ops.scaled_gemm_packed(x, a_sf, w_t, b_224, c))
+    us = _interleaved_times(launchers)
     print((M, N, K), " | ".join(f"{n}: {t:7.1f} us ({runtime_us_to_tflops(M, N, K, t):6.0f} TF)" for n, t in zip(names, us)), flush=True)
     ops.check_device_status()
 
