@@ -351,7 +351,7 @@ def sharded_record(dev, rank, world, dist):
     # MultiDeviceLaunchable): rank 0 drives all the GPUs of the job while the other ranks wait at a barrier; its
     # result must equal the per-rank launcher's bit for bit.
     native = None
-    if torch.cuda.device_count() >= world:
+    if world > 1 and torch.cuda.device_count() >= world:  # with one device the call is the plain kernel object
         # The other ranks wait on the HOST (a key in the job's store), with nothing of theirs queued on their GPU: a
         # collective's kernel spinning on GPU g while rank 0's GEMM runs there from another process would time-slice
         # against it.
