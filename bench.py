@@ -49,8 +49,8 @@ FALLBACK_HBM_GBS = 6650.0
 # benchmark's workload each (scaled to the full workload where the capture ran a smaller case), with the commit whose
 # kernel was captured: the figure describes that kernel, not necessarily the one timed now.
 NCU_TRAFFIC = {
-    "c2": {"bytes": 201.6e6, "kernel": "mxfp4_gemm_kernel<2,256,bf16>", "captured_at_commit": "42ea90d"},
-    "c3": {"bytes": 128.6e6, "kernel": "mxfp4_skinny_whole_kernel<16,10,bf16>", "captured_at_commit": "53ffb24"},
+    "c2": {"bytes": 200.0e6, "kernel": "mxfp4_gemm_kernel<2,256,bf16>", "captured_at_commit": "49071a8"},
+    "c3": {"bytes": 131.1e6, "kernel": "mxfp4_skinny_whole_kernel<16,10,bf16>, 104-row tiles", "captured_at_commit": "49071a8"},
     "c3_m128": {"bytes": 128.9e6, "kernel": "mxfp4_skinny_whole_kernel<128,6,bf16>", "captured_at_commit": "53ffb24"},
 }
 
