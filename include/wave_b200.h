@@ -254,6 +254,13 @@ int wb200_mxfp4_gemm_repack_a(int M, int N, int K, const void* a, const void* a_
  * AUTO when a workspace is passed) takes the workspace of wb200_mxfp4_gemm_workspace_bytes(M, N, K). */
 #define WB200_E4M3 0
 #define WB200_E5M2 1
+/* Mixed operand pair: or WB200_B_FP4 into elem_format and pass b as packed E2M1, [N, K/2] bytes (the MXFP4 weight
+ * layout), with its E8M0 block scales as usual: a stays 8-bit (E4M3 or E5M2). The MMA is kind::mxf8f6f4 with the two
+ * operand formats set independently; the copy engine expands the 4-bit values into the instruction's 8-bit container
+ * layout on their way into shared memory, so the weights cross HBM at 4 bits each. K must be a multiple of 128 and b
+ * 32-byte aligned. The reference reaches this pair through the same scaled MMA with different bitcasts of its i8
+ * operands (F32_16x16x128_F8F6F4, wave_lang/kernel/wave/constraints.py:79-86); it has no test of it. */
+#define WB200_B_FP4 0x10
 int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_packed, const void* b,
                      const void* b_scale_packed, void* c, int c_dtype, long long ldc, int elem_format, void* workspace,
                      size_t workspace_bytes, unsigned flags, void* stream);

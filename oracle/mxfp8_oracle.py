@@ -43,6 +43,16 @@ def torch_scaled_gemm_mxfp8(x, w, x_scales, w_scales) -> torch.Tensor:
     return torch.mm(x_f32, w_f32)                                                   # :91
 
 
+def torch_scaled_gemm_mxfp8_mxfp4(x, w_codes, x_scales, w_scales) -> torch.Tensor:
+    """The mixed pair of the same scaled MMA: 8-bit activations x [M, K] against packed E2M1 weights w_codes [N, K/2]
+    (the kernel's layout), each with E8M0 block scales: dequantise both as the reference's two oracles do
+    (tests/kernel/wave_gemm_mxfp_test.py:80-91 for the 8-bit side, wave_lang/kernel/wave/utils/mxfp_utils.py:131-143 for
+    the 4-bit side), then one f32 torch.mm. The reference has no test of this pair; its scaled MMA takes it
+    (wave_lang/kernel/wave/constraints.py:79-86)."""
+    from .mxfp4_oracle import dequant_mxfp4
+    return torch.mm(dequant_mxfp8(x, x_scales), dequant_mxfp4(w_codes, w_scales).T)
+
+
 def quantize_mxfp8(x: torch.Tensor, dtype=torch.float8_e5m2):
     """f32 [R, K] -> (f8 [R, K], scales [R, K/32] uint8). Not in the reference (its MXFP8 test feeds random values,
     tests/kernel/wave_gemm_mxfp_test.py:64-77); the block rule of the MXFP4 harness quantiser carried over:

@@ -208,3 +208,110 @@ def test_overlapped_chain_of_mxfp8_decode_calls_gives_the_same_bits():
     for c, r in zip(outs, ref):
         assert torch.equal(c.view(torch.int16), r.view(torch.int16))
     ops.check_device_status()
+
+
+# ---------------------------------------------------------------------------------------------
+# the mixed pair: 8-bit activations, packed E2M1 weights (kind::mxf8f6f4 with two operand formats)
+# ---------------------------------------------------------------------------------------------
+def mixed_problem(M, N, K, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    a = (torch.randn(M, K, generator=g) * 2).to(dtype)
+    b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)  # every E2M1 code, both signs of zero included
+    a_s = torch.randint(123, 131, (M, K // 32), dtype=torch.uint8, generator=g)
+    b_s = torch.randint(123, 131, (N, K // 32), dtype=torch.uint8, generator=g)
+    return a, a_s, b, b_s
+
+
+def check_mixed(c, a, a_s, b, b_s):
+    ad, bd = orc8.dequant_mxfp8(a, a_s), orc.dequant_mxfp4(b, b_s)
+    ref = orc8.torch_scaled_gemm_mxfp8_mxfp4(a, b, a_s, b_s)
+    tol = orc.f32_tolerance(ad, bd, ref, a.shape[1])
+    if c.dtype == torch.float32:
+        err = (c.cpu() - ref).abs()
+        assert bool((err <= tol).all()), f"{int((err > tol).sum())} outside tolerance, max err {float(err.max())}"
+    else:
+        ulp = orc.bf16_ulp_distance(c, ref)
+        bad = (ulp > 1) & ~((c.float().cpu() - ref).abs() <= tol)
+        assert not bool(bad.any()), f"{int(bad.sum())} entries beyond 1 bf16 ulp and beyond the f32 bound"
+        assert float((ulp > 1).float().mean()) < 1e-3
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("elem", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("flags,shape", [
+    (_lib.PATH_TILE_1CTA, (256, 256, 512)), (_lib.PATH_TILE_1CTA | _lib.TILE_N128, (130, 520, 128)),
+    (_lib.PATH_TILE_2CTA, (512, 512, 1024)), (_lib.PATH_TILE_2CTA | _lib.TILE_N128, (300, 1000, 384)),
+    (_lib.PATH_SKINNY, (1, 1024, 2048)), (_lib.PATH_SKINNY, (16, 1000, 384)), (_lib.PATH_SKINNY, (100, 4096, 256)),
+    (_lib.PATH_SKINNY, (40, 128 * 230, 128)), (_lib.PATH_AUTO, (2048, 2304, 1024))])
+def test_fp8_activations_against_fp4_weights(flags, shape, out_dtype, elem):
+    """The weights cross HBM as packed E2M1 and are expanded into the MMA's 8-bit containers by the copy engine; the
+    result equals dequantised activations times dequantised weights, on every path the 8-bit GEMM has."""
+    M, N, K = shape
+    a, a_s, b, b_s = mixed_problem(M, N, K, M + N + K, elem)
+    c = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_mxfp8_packed(a.to(DEV), ops.repack_scales(a_s.to(DEV)), b.to(DEV), ops.repack_scales(b_s.to(DEV)), c,
+                                 flags=flags, b_fp4=True)
+    check_mixed(c, a, a_s, b, b_s)
+
+
+def test_mixed_pair_equals_the_mxfp8_gemm_on_expanded_weights():
+    """Every E2M1 value is an E4M3 value: converting the weights to E4M3 bytes and running the plain MXFP8 GEMM must give
+    the same bits as the mixed pair on the packed weights (same scales, same instruction, same order of sums)."""
+    M, N, K = 384, 768, 512
+    a, a_s, b, b_s = mixed_problem(M, N, K, 3, torch.float8_e4m3fn)
+    expanded = orc.mxfp4_to_f32(b).to(torch.float8_e4m3fn)
+    assert torch.equal(expanded.float(), orc.mxfp4_to_f32(b))
+    a_sf, b_sf = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
+    for out_dtype in (torch.float32, torch.bfloat16):
+        c_mixed = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        c_plain = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        ops.scaled_gemm_mxfp8_packed(a.to(DEV), a_sf, b.to(DEV), b_sf, c_mixed, b_fp4=True)
+        ops.scaled_gemm_mxfp8_packed(a.to(DEV), a_sf, expanded.to(DEV), b_sf, c_plain)
+        bits = torch.int32 if out_dtype == torch.float32 else torch.int16
+        assert torch.equal(c_mixed.view(bits), c_plain.view(bits))
+    ops.check_device_status()
+
+
+def test_mixed_pair_through_the_template_and_its_argument_errors():
+    M, N, K = 200, 384, 256
+    a, a_s, b, b_s = mixed_problem(M, N, K, 21, torch.float8_e5m2)
+    kernel, hyper = wb.get_scaled_gemm_mxfp8_kernel((M, N, K), wb.ScaledMMAType.F32_16x16x128_F8F6F4, weight_format="f4e2m1fn")
+    gemm = wb.wave_compile(wb.WaveCompileOptions(subs=hyper), kernel)
+    c = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    gemm(a.to(DEV).view(torch.int8), a_s.to(DEV), b.to(DEV).view(torch.int8), b_s.to(DEV), c)
+    check_mixed(c, a, a_s, b, b_s)
+    with pytest.raises(ValueError):  # K must be a multiple of 128
+        wb.get_scaled_gemm_mxfp8_kernel((M, N, 160), wb.ScaledMMAType.F32_16x16x128_F8F6F4, weight_format="f4e2m1fn")
+    with pytest.raises(ValueError):  # b in the 8-bit layout [N, K] where packed [N, K/2] is expected
+        gemm(a.to(DEV), a_s.to(DEV), torch.zeros(N, K, dtype=torch.uint8, device=DEV), b_s.to(DEV), c)
+    lib = _lib.load()
+    a_sf, b_sf = ops.repack_scales(a_s.to(DEV)), ops.repack_scales(b_s.to(DEV))
+    rc = lib.wb200_mxfp8_gemm(M, N, 160, a.to(DEV).data_ptr(), a_sf.data.data_ptr(), b.to(DEV).data_ptr(), b_sf.data.data_ptr(),
+                              c.data_ptr(), 0, N, _lib.E5M2 | _lib.B_FP4, None, 0, 0, None)
+    assert rc == _lib.WB200_ERR_UNSUPPORTED and b"128" in lib.wb200_last_error()
+
+
+@pytest.mark.parametrize("M", [1, 16, 100])
+@pytest.mark.parametrize("b_fp4", [False, True])
+def test_8bit_decode_kernel_on_weight_scales_packed_per_balanced_tile(M, b_fp4):
+    """N = 28672 with the balanced tile height (as for MXFP4), 8-bit and mixed operands: matches the oracle, and gives the
+    bits of the usual packing wherever both run the whole-tile kernel."""
+    N, K = 28672, 256
+    h = ops.decode_tile_rows(N)
+    if h == 128:
+        pytest.skip("this part's SM count divides the tile count")
+    if b_fp4:
+        a, a_s, b, b_s = mixed_problem(M, N, K, 70 + M, torch.float8_e4m3fn)
+    else:
+        a, a_s, b, b_s = problem(M, N, K, 70 + M, torch.float8_e4m3fn)
+    ad, bd, a_sf = a.to(DEV), b.to(DEV), ops.repack_scales(a_s.to(DEV))
+    outs = []
+    for b_sf in (ops.repack_scales(b_s.to(DEV)), ops.repack_scales(b_s.to(DEV), tile_rows=h)):
+        c = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+        ops.scaled_gemm_mxfp8_packed(ad, a_sf, bd, b_sf, c, flags=_lib.PATH_SKINNY, b_fp4=b_fp4)
+        outs.append(c)
+    for c in outs:
+        (check_mixed if b_fp4 else check)(c, a, a_s, b, b_s)
+    if M > 16:  # up to 16 rows the usual packing takes the K-split kernel, whose partial sums are added in another order
+        assert torch.equal(outs[0].view(torch.int32), outs[1].view(torch.int32))

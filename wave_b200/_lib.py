@@ -54,6 +54,7 @@ def GROUP_N(g: int) -> int:
     return int(g) << 8
 E4M3 = 0
 E5M2 = 1
+B_FP4 = 0x10  # or into elem_format: b is packed E2M1 (include/wave_b200.h, WB200_B_FP4)
 
 # Every symbol include/wave_b200.h declares; tests check that the built library exports them all.
 EXPORTED_SYMBOLS = (

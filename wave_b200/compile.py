@@ -185,13 +185,22 @@ class ScaledGemmKernel:
         a, b = a.contiguous(), b.contiguous()  # non-contiguous inputs are copied, as the reference does (run_utils.py:106-109)
         M, K = a.shape
         N = b.shape[0]
+        b_fp4 = t.weight_bits == 4
+        if b_fp4:
+            b = ops._as_u8(b, "b")
+            if b.shape[1] * 2 != K:
+                raise ValueError(f"b must be packed E2M1 [N, K/2] = [{N}, {K // 2}], got {tuple(b.shape)}")
         if self._static is not None and self._static != (M, N, K):
             raise ValueError(f"kernel was built for (M, N, K) = {self._static}, called with {(M, N, K)}")
         a_sf = a_scale if isinstance(a_scale, ops.PackedScales) else self._pack_activation_scales(a_scale, M, K)
-        b_sf = b_scale if isinstance(b_scale, ops.PackedScales) else self._weight_scales.get(self._check_scale(b_scale, N, K, "b_scale"))
+        if isinstance(b_scale, ops.PackedScales):
+            b_sf = b_scale
+        else:
+            idx = a.device.index if a.device.index is not None else torch.cuda.current_device()
+            b_sf = self._weight_scales.get(self._check_scale(b_scale, N, K, "b_scale"), self._weight_tile_rows(M, N, idx))
         fmt = _lib.E5M2 if t.element_format == "f8e5m2" else _lib.E4M3
         flags = self.options.kernel_path | self._raster_flags() | (_lib.ACCUMULATE if t.accumulate else 0)
-        ops.scaled_gemm_mxfp8_packed(a, a_sf, b, b_sf, c, fmt, flags)
+        ops.scaled_gemm_mxfp8_packed(a, a_sf, b, b_sf, c, fmt, flags, b_fp4=b_fp4)
 
     def _invoke_checked(self, a, a_scale, b, b_scale, c) -> None:
         t = self.template
@@ -271,7 +280,7 @@ class ScaledGemmKernel:
         """Rows per tile the weight scales are packed for: the decode kernel's balanced tile height for M <= 128 (every
         SM gets the same number of weight tiles, `ops.decode_tile_rows`), 128 otherwise. Weights are packed once per
         (weight, height) and cached, so a weight used at both ends of the M range keeps two packings."""
-        if M > 128 or self.template.element_bits != 4 or not self.options.decode_tiled_weight_scales:
+        if M > 128 or not self.options.decode_tiled_weight_scales:
             return 128
         key = (N, dev_index)
         h = self._tile_rows.get(key)

@@ -162,6 +162,22 @@ int make_operand_map(CUtensorMap* map, const void* base, long long rows, long lo
   return WB200_OK;
 }
 
+// Packed E2M1 weights ([rows, K/2] bytes) for the 8-bit kernels (kind::mxf8f6f4): the copy engine expands every 16
+// values (8 bytes) into a 16-byte slot of shared memory, 8 bytes of values and 8 of padding, which is the 8-bit
+// container layout the MMA reads 4-bit operands in. One box = 128 values x box_rows = 128 bytes x box_rows of shared
+// memory, the footprint of an 8-bit operand tile. K a multiple of 128, base 32-byte aligned (driver rules of this type).
+int make_operand_map_u4(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+  if (K % 128 != 0) return fail(WB200_ERR_UNSUPPORTED, "4-bit weights in the 8-bit GEMM need K %% 128 == 0 (K = %lld)", K);
+  if (reinterpret_cast<uintptr_t>(base) & 31) return fail(WB200_ERR_ALIGNMENT, "4-bit weights in the 8-bit GEMM must be 32-byte aligned");
+  const MapKey k{base, (unsigned long long)K, (unsigned long long)rows, (unsigned long long)(K / 2), 128u, unsigned(box_rows),
+                 int(CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B), int(CU_TENSOR_MAP_SWIZZLE_128B), int(CU_TENSOR_MAP_L2_PROMOTION_L2_256B)};
+  CUresult r = encode_2d(map, k);
+  if (r != CUDA_SUCCESS)
+    return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled (4-bit weights) failed with CUresult %d (rows %lld, K %lld)", int(r), rows, K);
+  return WB200_OK;
+}
+static bool weights_are_fp4(int EB, int elem_format) { return EB == 8 && (elem_format & 0x10) != 0; }
+
 // Packed scale array ([row_blocks][k_atoms][512 bytes]) as a 2-D tensor of 32-bit words, one
 // row per 128-row block; a box is box_atoms atoms of 512 bytes (those of one pipeline stage) x box_rows.
 // pitch_atoms: atoms between consecutive row blocks when the map covers a K slice of a wider packed array (0 = k_atoms).
@@ -237,7 +253,8 @@ int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const
   const long long row_bytes = (long long)K * EB / 8;
   int rc = make_operand_map(&maps.m[0], a, M, row_bytes, Cfg::BM);
   if (rc) return rc;
-  rc = make_operand_map(&maps.m[1], b, N, row_bytes, Cfg::B_ROWS);
+  rc = weights_are_fp4(EB, elem_format) ? make_operand_map_u4(&maps.m[1], b, N, K, Cfg::B_ROWS)
+                                        : make_operand_map(&maps.m[1], b, N, row_bytes, Cfg::B_ROWS);
   if (rc) return rc;
   rc = make_scale_map(&maps.m[2], as, sfa_row_blocks, wb::sf_k_atoms(K), 1, Cfg::SF_ATOMS);
   if (rc) return rc;
@@ -579,7 +596,7 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
   using Cfg = wb::SkinnyCfg<NP, STAGES, EB>;
   CUtensorMap tmW, tmX, tmSFW, tmSFX;
   const long long row_bytes = (long long)K * EB / 8;
-  int rc = make_operand_map(&tmW, b, N, row_bytes, 128);
+  int rc = weights_are_fp4(EB, elem_format) ? make_operand_map_u4(&tmW, b, N, K, 128) : make_operand_map(&tmW, b, N, row_bytes, 128);
   if (rc) return rc;
   rc = make_operand_map(&tmX, a, M, row_bytes, NP);
   if (rc) return rc;
@@ -626,10 +643,13 @@ int launch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, con
 // only when the tiles left over after the full rounds are none, or at least half a round, or a small part of the whole:
 // a few stragglers alone run at one SM's bandwidth (150 tiles: 21.9 us whole against 19.2 us K-split; 185 tiles: 22.5
 // against 19.9; 224 tiles: 23.3 against 24.9; 148 tiles: 15.7 against 16.4).
-bool skinny_takes_whole_tiles(int sm_count, int M, int N) {
+bool skinny_takes_whole_tiles(int sm_count, int M, int N, int elem_bits = 4) {
   const int tiles = (N + 127) / 128, rest = tiles % sm_count;
   if (tiles < sm_count) return false;
   if (M > 16) return true;
+  // 8-bit operands stream twice the bytes per tile, so a partly empty last round costs twice as much: measured at
+  // N = 28672, K = 8192, M = 16: 50.8 us with whole 128-row tiles against 42.5 us with the K split
+  if (elem_bits == 8) return rest == 0;
   return rest == 0 || rest * 2 >= sm_count || tiles >= 4 * sm_count;
 }
 
@@ -654,7 +674,7 @@ int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* 
   const long long row_bytes = (long long)K * EB / 8;
   const int tile_rows = tl_b_tile_rows;  // 128 with the usual packing of the weight scales
   const int tiles_n = (N + tile_rows - 1) / tile_rows;
-  int rc = make_operand_map(&tmW, b, N, row_bytes, tile_rows);
+  int rc = weights_are_fp4(EB, elem_format) ? make_operand_map_u4(&tmW, b, N, K, tile_rows) : make_operand_map(&tmW, b, N, row_bytes, tile_rows);
   if (rc) return rc;
   rc = make_operand_map(&tmX, a, M, row_bytes, NP);
   if (rc) return rc;
@@ -700,11 +720,11 @@ int dispatch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, c
                     int elem_format = 0) {
   if (tl_b_tile_rows != 128) {
     // the weight scales are packed per tile of that height: only the whole-tile kernel reads them that way
-    if (EB != 4 || (N + tl_b_tile_rows - 1) / tl_b_tile_rows < dev.sm_count)
-      return fail(WB200_ERR_UNSUPPORTED, "weight scales packed for %d-row tiles need MXFP4 operands and at least one tile per SM (N = %d, %d SMs); "
+    if ((N + tl_b_tile_rows - 1) / tl_b_tile_rows < dev.sm_count)
+      return fail(WB200_ERR_UNSUPPORTED, "weight scales packed for %d-row tiles need at least one tile per SM (N = %d, %d SMs); "
                   "pack them with wb200_repack_scales instead", tl_b_tile_rows, N, dev.sm_count);
   }
-  if (tl_b_tile_rows != 128 || skinny_takes_whole_tiles(dev.sm_count, M, N)) {
+  if (tl_b_tile_rows != 128 || skinny_takes_whole_tiles(dev.sm_count, M, N, EB)) {
     if (M <= 16) return launch_skinny_whole<16, 10, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
     if (M <= 32) return launch_skinny_whole<32, 9, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
     if (M <= 64) return launch_skinny_whole<64, 8, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
@@ -1281,11 +1301,20 @@ int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
                      size_t workspace_bytes, unsigned flags, void* stream) {
   int rc = check_common(M, N, K, a, a_scale_packed, b, b_scale_packed, c, c_dtype, ldc);
   if (rc) return rc;
-  if (elem_format != WB200_E4M3 && elem_format != WB200_E5M2)
-    return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown element format %d", elem_format);
-  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS | WB200_GROUP_N_MASK)) != 0)
+  if ((elem_format & ~(1 | WB200_B_FP4)) != 0)
+    return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown element format %#x (WB200_E4M3 or WB200_E5M2, optionally | WB200_B_FP4)", elem_format);
+  if ((elem_format & WB200_B_FP4) && K % 128 != 0)
+    return fail(WB200_ERR_UNSUPPORTED, "mxfp8_gemm with 4-bit weights needs K %% 128 == 0 (K = %d)", K);
+  if ((flags & ~(WB200_PATH_MASK | WB200_TILE_N128 | WB200_ACCUMULATE | WB200_OVERLAP_PREVIOUS | WB200_GROUP_N_MASK | WB200_B_TILE_ROWS_MASK)) != 0)
     return fail(WB200_ERR_INVALID_ARG, "mxfp8_gemm: unknown flag bits %#x", flags);
   GroupNScope group_scope(flags);
+  struct TileRowsScope {
+    int saved;
+    explicit TileRowsScope(int h) : saved(tl_b_tile_rows) { tl_b_tile_rows = h; }
+    ~TileRowsScope() { tl_b_tile_rows = saved; }
+  } tile_rows_scope(b_tile_rows_from_flags(flags));
+  if (tl_b_tile_rows > 128)
+    return fail(WB200_ERR_UNSUPPORTED, "mxfp8_gemm: weight scales packed per %d-row tile (the 8-bit GEMM reads heights of 8 .. 128 on its M <= 128 path)", tl_b_tile_rows);
   struct DependentScope {  // restores the previous value on every return path
     bool saved;
     explicit DependentScope(bool on) : saved(tl_dependent_launch) { if (on) tl_dependent_launch = true; }
@@ -1302,6 +1331,9 @@ int wb200_mxfp8_gemm(int M, int N, int K, const void* a, const void* a_scale_pac
   const bool ws_ok = workspace && workspace_bytes >= skinny_workspace_bytes(dev->sm_count, M) &&
                      (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
   if (path == WB200_PATH_AUTO) path = (M <= 128 && ws_ok) ? WB200_PATH_SKINNY : (M > 128) ? WB200_PATH_TILE_2CTA : WB200_PATH_TILE_1CTA;
+  if (tl_b_tile_rows != 128 && path != WB200_PATH_SKINNY)
+    return fail(WB200_ERR_UNSUPPORTED, "mxfp8_gemm: weight scales packed per %d-row tile are read by the M <= 128 kernel only, which needs "
+                "a workspace (M = %d, path %u)", tl_b_tile_rows, M, path);
   if (path == WB200_PATH_SKINNY) {
     if (M > 128) return fail(WB200_ERR_UNSUPPORTED, "the skinny path handles M <= 128 (got %d)", M);
     if (N > 4096 * 128) return fail(WB200_ERR_UNSUPPORTED, "the skinny path handles N <= 524288 (got %d)", N);

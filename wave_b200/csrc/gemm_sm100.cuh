@@ -380,7 +380,8 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
         ++stages_loaded;
 #endif
         if (elect_one()) {
-          if (leader) mbar_expect_tx(full_bar(stage), Cfg::LOAD_BYTES * CG);
+          // 4-bit weights expanded by the copy engine (EB == 8 kernels only): the transaction count is the packed size
+          if (leader) mbar_expect_tx(full_bar(stage), (Cfg::LOAD_BYTES - ((EB == 8 && (p.elem_format & 0x10)) ? Cfg::B_BYTES / 2 : 0)) * CG);
           tma_load_2d<CG>(sA, tm + 0, kb * 128, a_row, fb);
           tma_load_2d<CG>(sB, tm + 1, kb * 128, b_row, fb);
           // scale factors: SF_ATOMS atoms of 512 bytes (128 32-bit words) per 128-row block and stage
@@ -395,7 +396,7 @@ mxfp4_gemm_kernel(const __grid_constant__ Maps maps, const GemmParams p) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader) {
       const uint32_t idesc = (EB == 4) ? make_idesc_mxf4(Cfg::BM * CG, BN)
-                                       : make_idesc_mxf8(Cfg::BM * CG, BN, uint32_t(p.elem_format));
+                                       : make_idesc_mxf8(Cfg::BM * CG, BN, act_format_of(p.elem_format), weight_format_of(p.elem_format));
       const uint32_t peer_empty0 = (CG == 2) ? mapa_shared(empty_bar(0), 1) : 0u;
       const uint32_t peer_acc_full0 = (CG == 2) ? mapa_shared(acc_full_bar(0), 1) : 0u;
       uint32_t stage = 0, phase = 0, sf_set = 0;

@@ -317,11 +317,20 @@ __device__ __forceinline__ uint32_t idesc_with_sf_id(uint32_t idesc, uint32_t sf
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// Instruction descriptor of kind::mxf8f6f4 block-scaled with 8-bit operands: fmt 0 = E4M3, 1 = E5M2 (both
-// operands the same), K-major, UE8M0 scales, K = 32 per instruction; the scale-factor id (0..3) picks
-// the byte of the 32-bit scale column that this K = 32 step reads.
-__host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n, uint32_t fmt) {
-  return (fmt << 7) | (fmt << 10) | (uint32_t(n >> 3) << 17) | (1u << 23) | (uint32_t(m >> 4) << 24);
+// Instruction descriptor of kind::mxf8f6f4 block-scaled: operand formats 0 = E4M3, 1 = E5M2, 5 = E2M1 (4-bit values in
+// the 8-bit container layout: 16 values in 8 bytes, then 8 bytes of padding), chosen per operand; K-major, UE8M0
+// scales, K = 32 per instruction; the scale-factor id (0..3) picks the byte of the 32-bit scale column that this
+// K = 32 step reads.
+constexpr uint32_t kFmtE2M1 = 5;
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n, uint32_t a_fmt, uint32_t b_fmt) {
+  return (a_fmt << 7) | (b_fmt << 10) | (uint32_t(n >> 3) << 17) | (1u << 23) | (uint32_t(m >> 4) << 24);
+}
+// The `elem_format` word of the 8-bit kernels: bit 0 = format of the activations (and of the weights unless bit 4 is
+// set), bit 4 = the weights are packed E2M1 ([N, K/2] bytes in global memory, expanded into 8-bit containers by the
+// copy engine on their way to shared memory).
+__host__ __device__ constexpr uint32_t act_format_of(int elem_format) { return uint32_t(elem_format) & 1u; }
+__host__ __device__ constexpr uint32_t weight_format_of(int elem_format) {
+  return (elem_format & 0x10) ? kFmtE2M1 : (uint32_t(elem_format) & 1u);
 }
 
 template <int CTA_GROUP>

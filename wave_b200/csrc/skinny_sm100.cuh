@@ -178,7 +178,8 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       const uint32_t sSFX = sSFW + Cfg::SF_BYTES;
       const uint32_t fb = full_bar(p_stage);
       if (elect_one()) {
-        if (part != 1) mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+        // 4-bit weights expanded by the copy engine (EB == 8 only) count with their packed size
+        if (part != 1) mbar_expect_tx(fb, Cfg::STAGE_BYTES - ((EB == 8 && (p.elem_format & 0x10)) ? Cfg::W_BYTES / 2 : 0));
         if (part != 2) {
           tma_load_2d_hint(sW, &tmW, p_kb * 128, p_tile * 128, fb, stream_policy);
           tma_load_2d(sSFW, &tmSFW, p_kb * (Cfg::SF_ATOMS * 128), p_tile, fb);
@@ -233,7 +234,7 @@ mxfp4_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     produce(0x7fffffff, true, 0);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = (EB == 4) ? make_idesc_mxf4(128, NP) : make_idesc_mxf8(128, NP, uint32_t(p.elem_format));
+    const uint32_t idesc = (EB == 4) ? make_idesc_mxf4(128, NP) : make_idesc_mxf8(128, NP, weight_format_of(p.elem_format), act_format_of(p.elem_format));
     uint32_t stage = 0, phase = 0, sf_set = 0;
     for (int seg = 0; seg < nseg; ++seg) {
       int tile, kbs, kbe;

@@ -129,7 +129,9 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
       // a tile of fewer than 128 rows fills the head of the stage's weight area; the MMA still multiplies 128 rows
       // (whatever bits the rest holds: every E2M1 code is finite, the scales of those lanes are the padding byte)
       // and the epilogue keeps the tile's own columns
-      if (part != 1) mbar_expect_tx(fb, Cfg::STAGE_BYTES - Base::W_BYTES + uint32_t(p.tile_rows) * 128u);
+      // (4-bit weights expanded by the copy engine, EB == 8 only, count with their packed size: 64 bytes per row)
+      if (part != 1)
+        mbar_expect_tx(fb, Cfg::STAGE_BYTES - Base::W_BYTES + uint32_t(p.tile_rows) * ((EB == 8 && (p.elem_format & 0x10)) ? 64u : 128u));
       if (part != 2) {
         tma_load_2d_hint(sW, &tmW, kb * 128, tile * p.tile_rows, fb, stream_policy);
         tma_load_2d(sSFW, &tmSFW, kb * (Base::SF_ATOMS * 128), tile, fb);
@@ -214,7 +216,7 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     emit(-1);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = (EB == 4) ? make_idesc_mxf4(128, NP) : make_idesc_mxf8(128, NP, uint32_t(p.elem_format));
+    const uint32_t idesc = (EB == 4) ? make_idesc_mxf4(128, NP) : make_idesc_mxf8(128, NP, weight_format_of(p.elem_format), act_format_of(p.elem_format));
     uint32_t stage = 0, phase = 0, sf_set = 0;
     for (int seq = 0;; ++seq) {
       const int tile = next_tile(seq);

@@ -253,9 +253,10 @@ def quantize_mxfp8(x: torch.Tensor, dtype: torch.dtype = torch.float8_e5m2, want
 
 
 def scaled_gemm_mxfp8_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tensor, b_sf: PackedScales, c: torch.Tensor,
-                             elem_format: int | None = None, flags: int = 0) -> None:
+                             elem_format: int | None = None, flags: int = 0, b_fp4: bool = False) -> None:
     """c [M, N] = dequant(a) @ dequant(b)^T for 8-bit operands a [M, K], b [N, K] (torch float8 tensors, or
-    int8 / uint8 bytes with `elem_format` given) and packed E8M0 scales, on the current stream."""
+    int8 / uint8 bytes with `elem_format` given) and packed E8M0 scales, on the current stream.
+    b_fp4: the mixed pair — b is packed E2M1, [N, K/2] uint8 as for the MXFP4 GEMM, a stays 8-bit (K % 128 == 0)."""
     lib = _lib.load()
     if elem_format is None:
         if a.dtype not in _FP8_FORMATS:
@@ -266,9 +267,15 @@ def scaled_gemm_mxfp8_packed(a: torch.Tensor, a_sf: PackedScales, b: torch.Tenso
             raise ValueError(f"{name} must be a contiguous 2-D CUDA tensor of 8-bit elements")
     M, K = a.shape
     N = b.shape[0]
-    if a_sf.tile_rows != 128 or b_sf.tile_rows != 128:
-        raise ValueError("the MXFP8 GEMM reads the usual scale packing only (tile_rows = 128)")
-    if b.shape[1] != K or (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
+    if a_sf.tile_rows != 128 or b_sf.tile_rows > 128 or (b_sf.tile_rows != 128 and M > 128):
+        raise ValueError("the 8-bit GEMM reads per-tile weight scales (tile_rows < 128) on its M <= 128 path only")
+    if b_sf.tile_rows != 128:
+        flags |= _lib.B_TILE_ROWS(b_sf.tile_rows)
+    if b_fp4:
+        if b.dtype not in (torch.uint8, torch.int8) or K % 128:
+            raise ValueError("4-bit weights: b must be uint8 [N, K/2] (packed E2M1) and K a multiple of 128")
+        elem_format |= _lib.B_FP4
+    if b.shape[1] * (2 if b_fp4 else 1) != K or (a_sf.rows, a_sf.K) != (M, K) or (b_sf.rows, b_sf.K) != (N, K):
         raise ValueError("operand and scale shapes do not agree")
     if c.dtype not in _DTYPE_CODE or tuple(c.shape) != (M, N) or c.stride(1) != 1:
         raise ValueError(f"c must be f32 or bf16 [{M}, {N}] with unit column stride")

@@ -145,28 +145,35 @@ def time_moe(tokens=4096, experts=8, top_k=2, K=4096, inter=7168, iters=10, devi
     return rows
 
 
-def time_mxfp8(iters=20, device="cuda:0"):
+def time_mxfp8(iters=20, device="cuda:0", b_fp4: bool = False):
     """MXFP8 (E4M3 operands, E8M0 block scales, bf16 output): large tile shapes and the decode shapes, three rotating
-    operand sets (> L2 for the decode shapes), launches replayed from a CUDA graph."""
+    operand sets (> L2 for the decode shapes), launches replayed from a CUDA graph. b_fp4: the mixed pair, E4M3
+    activations against packed E2M1 weights (K rounded to a multiple of 128)."""
     from . import ops
     rows = []
     shapes = [(8192, 8192, 8192), (4096, 4096, 4096), (8192, 8192, 16000)] + [(M, 28672, 8192) for M in (1, 16, 64, 128)]
     for M, N, K in shapes:
+        if b_fp4:
+            K = K // 128 * 128
         g = torch.Generator(device=device).manual_seed(1)
         sets = []
         for _ in range(3):
             a = torch.randn(M, K, device=device, generator=g).to(torch.float8_e4m3fn)
-            b = torch.randn(N, K, device=device, generator=g).to(torch.float8_e4m3fn)
+            if b_fp4:
+                b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=g)
+            else:
+                b = torch.randn(N, K, device=device, generator=g).to(torch.float8_e4m3fn)
             a_sf = ops.repack_scales(torch.randint(124, 128, (M, K // 32), dtype=torch.uint8, device=device, generator=g))
-            b_sf = ops.repack_scales(torch.randint(124, 128, (N, K // 32), dtype=torch.uint8, device=device, generator=g))
+            b_sf = ops.repack_scales(torch.randint(124, 128, (N, K // 32), dtype=torch.uint8, device=device, generator=g),
+                                     tile_rows=ops.decode_tile_rows(N, device) if M <= 128 else 128)  # weights: packed once, per balanced tile
             sets.append((a, a_sf, b, b_sf, torch.empty(M, N, dtype=torch.bfloat16, device=device)))
         for st in sets:
-            ops.scaled_gemm_mxfp8_packed(*st)
+            ops.scaled_gemm_mxfp8_packed(*st, b_fp4=b_fp4)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for st in sets:
-                ops.scaled_gemm_mxfp8_packed(*st)
+                ops.scaled_gemm_mxfp8_packed(*st, b_fp4=b_fp4)
         graph.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -182,7 +189,7 @@ def time_mxfp8(iters=20, device="cuda:0"):
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (3 * reps)
-        nbytes = M * K + M * K // 32 + N * K + N * K // 32 + M * N * 2
+        nbytes = M * K + M * K // 32 + N * K // (2 if b_fp4 else 1) + N * K // 32 + M * N * 2
         rows.append({"M": M, "N": N, "K": K, "runtime_us": round(us, 1), "tflops": round(runtime_us_to_tflops(M, N, K, us), 1),
                      "gbytes_per_s": round(nbytes / us / 1e3, 1)})
         print(rows[-1], flush=True)
@@ -507,6 +514,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--csv", default=None)
     ap.add_argument("--mxfp8", action="store_true", help="time the MXFP8 GEMM (tile shapes and decode shapes)")
+    ap.add_argument("--mxfp8-fp4-weights", action="store_true", help="time the mixed pair: E4M3 activations, packed E2M1 weights")
     ap.add_argument("--compare-cublaslt", action="store_true", help="context: time cuBLASLt's block-scaled FP4 GEMM on the same operands")
     ap.add_argument("--k-sharded", action="store_true", help="under torchrun: time the K-sharded GEMM against GEMM + NCCL reduce-scatter")
     ap.add_argument("--moe", action="store_true", help="time the steps of the MXFP4 expert MLP instead of the shape sweep")
@@ -535,8 +543,8 @@ def main(argv=None):
     if args.moe:
         time_moe(iters=args.iters)
         return
-    if args.mxfp8:
-        time_mxfp8(iters=args.iters)
+    if args.mxfp8 or args.mxfp8_fp4_weights:
+        time_mxfp8(iters=args.iters, b_fp4=args.mxfp8_fp4_weights)
         return
     if args.compare_cublaslt:
         compare_cublaslt(iters=args.iters)

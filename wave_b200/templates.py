@@ -34,6 +34,7 @@ class ScaledGemmTemplate:
     broadcast_a_scale: bool = False        # a_scale is [M]: one scale per row for all of K
     element_bits: int = 4                  # 4: packed E2M1 (MXFP4); 8: one byte per element (MXFP8)
     element_format: str = "f4e2m1fn"       # MXFP8: "f8e5m2" or "f8e4m3fn"
+    weight_bits: int = 0                   # 8-bit kernels only: 4 = b is packed E2M1 (the mixed f8 x f4 pair); 0 = as a
     hints: dict = field(default_factory=dict)
 
 
@@ -73,17 +74,28 @@ def get_broadcasted_scale_gemm_mxfp4(shape, mfma_variant: ScaledMMAType):
     return tpl, _hyperparams(shape, (32, 32, 256), {"ADDRESS_SPACE": SHARED_ADDRESS_SPACE})
 
 
-def get_scaled_gemm_mxfp8_kernel(shape, mfma_variant: ScaledMMAType, element_format: str = "f8e5m2", output_dtype=f32):
+def get_scaled_gemm_mxfp8_kernel(shape, mfma_variant: ScaledMMAType, element_format: str = "f8e5m2", output_dtype=f32,
+                                 weight_format: str | None = None):
     """(kernel, hyperparams) for the MXFP8 scaled GEMM: a [M, K], b [N, K] bytes of f8e5m2 (or f8e4m3fn),
     E8M0 scales [rows, K/32], c [M, N]. The reference has this kernel only inside its test
     (tests/kernel/wave_gemm_mxfp_test.py:416-501: same signature as the MXFP4 kernel with K instead of K/2
-    columns and a bitcast to f8e5m2); this function gives it the template form of get_scaled_gemm_kernel."""
+    columns and a bitcast to f8e5m2); this function gives it the template form of get_scaled_gemm_kernel.
+
+    weight_format = "f4e2m1fn": the mixed pair of the same scaled MMA (F32_16x16x128_F8F6F4 takes f8, f6 and f4
+    operands; in the reference's DSL it is the same kernel with b bitcast to f4e2m1fn): a stays 8-bit, b is packed E2M1
+    [N, K/2] exactly as for the MXFP4 GEMM; K must be a multiple of 128."""
     if not isinstance(mfma_variant, ScaledMMAType):
         raise TypeError("mfma_variant must be a ScaledMMAType")
     if element_format not in ("f8e5m2", "f8e4m3fn"):
         raise ValueError(f"unknown 8-bit element format {element_format}")
-    tpl = ScaledGemmTemplate("scaled_gemm_mxfp8", tuple(shape), as_output_dtype(output_dtype), element_bits=8,
-                             element_format=element_format, hints={"mfma_variant": mfma_variant, "block_shape": (32, 32, 256)})
+    if weight_format not in (None, element_format, "f4e2m1fn"):
+        raise ValueError(f"weights are {element_format} like the activations, or f4e2m1fn (got {weight_format})")
+    if weight_format == "f4e2m1fn" and shape[2] % 128:
+        raise ValueError(f"4-bit weights under 8-bit activations need K % 128 == 0 (K = {shape[2]})")
+    tpl = ScaledGemmTemplate("scaled_gemm_mxfp8" if weight_format != "f4e2m1fn" else "scaled_gemm_mxfp8_mxfp4", tuple(shape),
+                             as_output_dtype(output_dtype), element_bits=8, element_format=element_format,
+                             weight_bits=4 if weight_format == "f4e2m1fn" else 8,
+                             hints={"mfma_variant": mfma_variant, "block_shape": (32, 32, 256)})
     return tpl, _hyperparams(shape, (32, 32, 256), {"ADDRESS_SPACE": SHARED_ADDRESS_SPACE})
 
 
