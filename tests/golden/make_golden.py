@@ -20,9 +20,13 @@ import torch
 HERE = Path(__file__).resolve().parent
 
 
-def main(ref_root: str) -> None:
+def main(ref_root: str, only_mixed: bool = False) -> None:
     sys.path.insert(0, ref_root)
     from wave_lang.kernel.wave.utils import mxfp_utils as ref  # noqa: E402
+
+    if only_mixed:  # adds the newest fixture without rewriting the others (their archives carry timestamps)
+        mixed_pair(ref, reference_mxfp8_functions(ref_root, ref))
+        return
 
     torch.set_num_threads(1)  # fixed summation order inside torch.mm for the stored GEMM outputs
 
@@ -101,6 +105,19 @@ def main(ref_root: str) -> None:
     #    (tests/kernel/wave_gemm_mxfp_test.py:64-91) whose other imports need the compiler stack, so the
     #    two function definitions are taken out of that file's syntax tree and executed as they are, with
     #    the CPU forms of the helpers they call.
+    ns = reference_mxfp8_functions(ref_root, ref)
+    torch.set_num_threads(1)
+    x, w, xs, ws = ns["generate_gemm_afp8wfp8_inputs"]((64, 96, 128))
+    out = ns["torchScaledGemmMXFP8"](x, w, xs, ws)
+    np.savez_compressed(HERE / "gemm_mxfp8_seed5_64x96x128.npz", x=x.view(torch.uint8).numpy(),
+                        w=np.ascontiguousarray(w.T.contiguous().view(torch.uint8).numpy()),  # stored as [N, K] bytes
+                        x_scales=np.ascontiguousarray(xs.numpy()), w_scales=np.ascontiguousarray(ws.numpy()),
+                        out=out.numpy())
+    mixed_pair(ref, ns)
+    print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
+
+
+def reference_mxfp8_functions(ref_root: str, ref) -> dict:
     import ast
     test_src = (Path(ref_root) / "tests/kernel/wave_gemm_mxfp_test.py").read_text()
     wanted = [n for n in ast.parse(test_src).body
@@ -109,17 +126,25 @@ def main(ref_root: str) -> None:
     ns = {"torch": torch, "SCALE_GROUP_SIZE": ref.SCALE_GROUP_SIZE, "e8m0_to_f32": ref.e8m0_to_f32,
           "device_randn": torch.randn, "device_randint": torch.randint}
     exec(compile(ast.Module(body=wanted, type_ignores=[]), "wave_gemm_mxfp_test.py", "exec"), ns)
+    return ns
+
+
+def mixed_pair(ref, ns) -> None:
+    """8. The mixed pair of the same scaled MMA: the reference's 8-bit activations (its MXFP8 generator) against its packed
+    E2M1 weights (its MXFP4 generator), each dequantised by the reference's own functions, then its f32 torch.mm."""
     torch.set_num_threads(1)
-    x, w, xs, ws = ns["generate_gemm_afp8wfp8_inputs"]((64, 96, 128))
-    out = ns["torchScaledGemmMXFP8"](x, w, xs, ws)
-    np.savez_compressed(HERE / "gemm_mxfp8_seed5_64x96x128.npz", x=x.view(torch.uint8).numpy(),
-                        w=np.ascontiguousarray(w.T.contiguous().view(torch.uint8).numpy()),  # stored as [N, K] bytes
-                        x_scales=np.ascontiguousarray(xs.numpy()), w_scales=np.ascontiguousarray(ws.numpy()),
-                        out=out.numpy())
-    print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
+    shape = (64, 96, 128)
+    x, _, xs, _ = ns["generate_gemm_afp8wfp8_inputs"](shape)
+    _, w, _, ws = ref.generate_gemm_afp4wfp4_inputs(shape)  # w: [K/2, N] view, ws: [N, K/32]
+    x_f32 = x.to(torch.float32) * ref.e8m0_to_f32(xs.repeat_interleave(ref.SCALE_GROUP_SIZE, dim=1).to(torch.float32))
+    w_f32 = ref.mxfp4_to_f32(w.T).T * ref.e8m0_to_f32(ws.repeat_interleave(ref.SCALE_GROUP_SIZE, dim=1).to(torch.float32)).T
+    out = torch.mm(x_f32, w_f32)
+    np.savez_compressed(HERE / "gemm_mxfp8_mxfp4_seed5_64x96x128.npz", x=x.view(torch.uint8).numpy(),
+                        w=np.ascontiguousarray(w.T.contiguous().numpy()),  # stored as [N, K/2] packed bytes
+                        x_scales=np.ascontiguousarray(xs.numpy()), w_scales=np.ascontiguousarray(ws.numpy()), out=out.numpy())
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: make_golden.py <path to the reference checkout>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        sys.exit("usage: make_golden.py <path to the reference checkout> [--only-mixed]")
+    main(sys.argv[1], only_mixed="--only-mixed" in sys.argv[2:])

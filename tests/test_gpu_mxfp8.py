@@ -315,3 +315,17 @@ def test_8bit_decode_kernel_on_weight_scales_packed_per_balanced_tile(M, b_fp4):
         (check_mixed if b_fp4 else check)(c, a, a_s, b, b_s)
     if M > 16:  # up to 16 rows the usual packing takes the K-split kernel, whose partial sums are added in another order
         assert torch.equal(outs[0].view(torch.int32), outs[1].view(torch.int32))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_mixed_pair_golden_small(out_dtype):
+    """Against the output stored from the reference's own functions (its f8e5m2 activations, its packed E2M1 weights)."""
+    g = np.load(GOLDEN / "gemm_mxfp8_mxfp4_seed5_64x96x128.npz")
+    x = torch.from_numpy(g["x"]).view(torch.float8_e5m2)
+    w, xs, ws = torch.from_numpy(g["w"]), torch.from_numpy(g["x_scales"]), torch.from_numpy(g["w_scales"])
+    ref = torch.from_numpy(g["out"])
+    c = torch.full((64, 96), float("nan"), dtype=out_dtype, device=DEV)
+    ops.scaled_gemm_mxfp8_packed(x.to(DEV), ops.repack_scales(xs.to(DEV)), w.to(DEV), ops.repack_scales(ws.to(DEV)), c, b_fp4=True)
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(c.cpu(), ref, atol=2e-3, rtol=1e-3)  # the reference's tolerance for its 8-bit test
+    check_mixed(c, x, xs, w, ws)

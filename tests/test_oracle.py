@@ -167,3 +167,16 @@ def test_amd_preshuffle_index_maps_match_reference_outputs():
     # on aligned shapes the scale shuffle is a permutation
     s2 = torch.randint(0, 255, (512, 64), dtype=torch.uint8, generator=torch.Generator().manual_seed(3))
     assert sorted(orc.amd_e8m0_shuffle(s2).reshape(-1).tolist()) == sorted(s2.reshape(-1).tolist())
+
+
+def test_mixed_pair_oracle_matches_reference_output():
+    """8-bit activations x packed E2M1 weights: the oracle against the output stored from the reference's own
+    generators and dequantisation functions (tests/golden/make_golden.py, step 8)."""
+    import numpy as np
+    from conftest import GOLDEN
+    from oracle import mxfp8_oracle as orc8
+    g = np.load(GOLDEN / "gemm_mxfp8_mxfp4_seed5_64x96x128.npz")
+    x = torch.from_numpy(g["x"]).view(torch.float8_e5m2)
+    w = torch.from_numpy(g["w"])  # [N, K/2] packed E2M1
+    out = orc8.torch_scaled_gemm_mxfp8_mxfp4(x, w, torch.from_numpy(g["x_scales"]), torch.from_numpy(g["w_scales"]))
+    torch.testing.assert_close(out, torch.from_numpy(g["out"]), rtol=1e-6, atol=1e-6 * float(np.abs(g["out"]).max()))
