@@ -751,6 +751,23 @@ def test_mxfp4_linear_module_matches_oracle():
     check_bf16(y.reshape(-1, N), orc.scaled_gemm(xq, xs, wq, ws))
 
 
+def test_mxfp4_linear_decode_batch_uses_the_balanced_packing():
+    """A layer wide enough for the whole-tile decode kernel: small batches read the per-tile packing, large ones the usual
+    one, both match the oracle."""
+    torch.manual_seed(6)
+    N, K = 28672, 256
+    w = torch.randn(N, K) * 0.02
+    layer = wb.MXFP4Linear.from_float(w.to(DEV), output_dtype=torch.bfloat16)
+    wq, ws = orc.quantize_mxfp4(w)
+    for rows in (4, 200, 4):
+        x = torch.randn(rows, K)
+        y = layer(x.to(DEV))
+        xq, xs = orc.quantize_mxfp4(x)
+        check_bf16(y, orc.scaled_gemm(xq, xs, wq, ws))
+    assert layer._packed_decode.tile_rows == ops.decode_tile_rows(N) and layer._packed.tile_rows == 128
+    ops.check_device_status()
+
+
 def test_host_pipelined_gemm_on_pinned_buffers():
     """Five calls through the three-stream host pipeline with three device buffer sets: every result
     must belong to its own call's operands (no buffer reused before its result left the device)."""

@@ -25,6 +25,9 @@ class MXFP4Linear(torch.nn.Module):
         self.register_buffer("weight_codes", weight_codes.contiguous())
         self.register_buffer("weight_scales", weight_scales.contiguous())
         self._packed = ops.repack_scales(self.weight_scales)  # once
+        # decode calls (at most 128 rows) read a second packing, per tile of the height that gives every SM the same number
+        # of weight tiles; made on first use, and only where that height differs from 128
+        self._packed_decode = None
 
     @classmethod
     def from_float(cls, weight: torch.Tensor, output_dtype=torch.bfloat16) -> "MXFP4Linear":
@@ -37,5 +40,11 @@ class MXFP4Linear(torch.nn.Module):
         x2 = x.reshape(-1, self.in_features)
         q, _, sf = ops.quantize_mxfp4(x2, want_rowmajor=False, want_packed=True)
         out = torch.empty(x2.shape[0], self.out_features, dtype=self.output_dtype, device=x.device)
-        ops.scaled_gemm_packed(q, sf, self.weight_codes, self._packed, out)
+        packed = self._packed
+        if x2.shape[0] <= 128:
+            if self._packed_decode is None:
+                h = ops.decode_tile_rows(self.out_features, x.device)
+                self._packed_decode = self._packed if h == 128 else ops.repack_scales(self.weight_scales, tile_rows=h)
+            packed = self._packed_decode
+        ops.scaled_gemm_packed(q, sf, self.weight_codes, packed, out)
         return out.reshape(*lead, self.out_features)
