@@ -667,12 +667,12 @@ int decode_tile_rows(int sm_count, int N) {
   return (h >= 88 && h < 128) ? h : 128;
 }
 
-template <int NP, int STAGES, typename OutT, int EB = 4>
+template <int NP, int STAGES, typename OutT, int EB = 4, int WR = 128, int SBUFS = 2>
 int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
                         const void* bs, void* c, long long ldc, void* ws, int accumulate, cudaStream_t stream,
                         int elem_format = 0) {
-  using Base = wb::SkinnyCfg<NP, STAGES, EB>;
-  using Cfg = wb::SkinnyWholeCfg<NP, STAGES, EB>;
+  using Base = wb::SkinnyCfg<NP, STAGES, EB, WR>;
+  using Cfg = wb::SkinnyWholeCfg<NP, STAGES, EB, WR, SBUFS>;
   CUtensorMap tmW, tmX, tmSFW, tmSFX;
   const long long row_bytes = (long long)K * EB / 8;
   const int tile_rows = tl_b_tile_rows;  // 128 with the usual packing of the weight scales
@@ -698,7 +698,7 @@ int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* 
   p.elem_format = elem_format;
   p.c_vec = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * (long long)sizeof(OutT)) % 16 == 0) ? 1 : 0;
   p.status = dev.status_ptr;
-  auto kernel = wb::mxfp4_skinny_whole_kernel<NP, STAGES, OutT, EB>;
+  auto kernel = wb::mxfp4_skinny_whole_kernel<NP, STAGES, OutT, EB, WR, SBUFS>;
   static bool smem_set[kMaxDevices] = {};
   rc = set_smem(kernel, Cfg::SMEM_BYTES, smem_set);
   if (rc) return rc;
@@ -726,6 +726,13 @@ int dispatch_skinny(const DeviceInfo& dev, int M, int N, int K, const void* a, c
     if ((N + tl_b_tile_rows - 1) / tl_b_tile_rows < dev.sm_count)
       return fail(WB200_ERR_UNSUPPORTED, "weight scales packed for %d-row tiles need at least one tile per SM (N = %d, %d SMs); "
                   "pack them with wb200_repack_scales instead", tl_b_tile_rows, N, dev.sm_count);
+  }
+  if (tl_b_tile_rows <= 104) {
+    // tiles of at most 104 rows: stages with room for 104 weight rows, so that the ring holds more of them
+    if (M <= 16) return launch_skinny_whole<16, 12, OutT, EB, 104>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+    if (M <= 32) return launch_skinny_whole<32, 11, OutT, EB, 104>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+    if (M <= 64) return launch_skinny_whole<64, 9, OutT, EB, 104>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
+    return launch_skinny_whole<128, 7, OutT, EB, 104, 1>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);
   }
   if (tl_b_tile_rows != 128 || skinny_takes_whole_tiles(dev.sm_count, M, N, EB)) {
     if (M <= 16) return launch_skinny_whole<16, 10, OutT, EB>(dev, M, N, K, a, as, b, bs, c, ldc, ws, accumulate, stream, elem_format);

@@ -47,14 +47,18 @@ __device__ __forceinline__ unsigned long long trace_now() {
 
 // EB: bits per operand element, 4 (MXFP4) or 8 (MXFP8); a stage is one 128-byte swizzle row of every operand row
 // either way: 256 or 128 K elements, 2 or 1 scale-factor atoms per 128 rows.
-template <int NP_, int STAGES_, int EB = 4>
+// WR: weight rows a stage has room for. 128 = a whole MMA tile; the whole-tile kernel also runs with 104 when its tiles
+// are at most 104 rows high (the MMA then reads the rows above from the bytes that follow in the stage, which it never
+// keeps), so that the ring holds more stages.
+template <int NP_, int STAGES_, int EB = 4, int WR = 128>
 struct SkinnyCfg {
   static_assert(EB == 4 || EB == 8, "operand elements are 4 or 8 bits");
+  static_assert(WR % 8 == 0 && WR >= 64 && WR <= 128, "weight rows per stage: whole 8-row swizzle groups");
   static constexpr int NP = NP_;  // padded M = MMA N
   static constexpr int STAGES = STAGES_;
   static constexpr int BK = 1024 / EB;
   static constexpr int SF_ATOMS = BK / 128;
-  static constexpr int W_BYTES = 128 * 128;
+  static constexpr int W_BYTES = WR * 128;
   static constexpr int X_BYTES = NP * 128;
   static constexpr int SF_BYTES = SF_ATOMS * 512;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;

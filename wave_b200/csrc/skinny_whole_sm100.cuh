@@ -28,12 +28,15 @@ namespace wb {
 constexpr int kWholeWorkCounter = 1023;  // counters[1023]: the tile dispenser (the K-split kernel uses counters[tile], tile < SMs)
 constexpr int kWholeItemQueue = 8;       // depth of the in-CTA queue of tile numbers
 
-template <int NP_, int STAGES_, int EB = 4>
+// SBUFS: staging buffers of the epilogue (2: a chunk is staged while the one before is still being stored; 1 where the
+// ring needs the room).
+template <int NP_, int STAGES_, int EB = 4, int WR = 128, int SBUFS = 2>
 struct SkinnyWholeCfg {
-  using Base = SkinnyCfg<NP_, STAGES_, EB>;
+  using Base = SkinnyCfg<NP_, STAGES_, EB, WR>;
+  static_assert(SBUFS == 1 || SBUFS == 2, "one or two staging buffers");
   static constexpr int STAGE_BYTES = Base::STAGE_BYTES;
   static constexpr int STAGING_BUF_BYTES = 16 * 128 * 4;  // 16 output rows x 128 columns of f32
-  static constexpr int STAGING_BYTES = 2 * STAGING_BUF_BYTES;
+  static constexpr int STAGING_BYTES = SBUFS * STAGING_BUF_BYTES;
   static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4 + 2 * kWholeItemQueue;
   static constexpr int MISC_BYTES = 64 + kWholeItemQueue * 4;
   static constexpr int SMEM_BYTES = 1024 + STAGES_ * STAGE_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + MISC_BYTES;
@@ -56,13 +59,13 @@ struct SkinnyWholeParams {
   int* status;
 };
 
-template <int NP, int STAGES, typename OutT, int EB = 4>
+template <int NP, int STAGES, typename OutT, int EB = 4, int WR = 128, int SBUFS = 2>
 __global__ void __launch_bounds__(192, 1)
 mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                           const __grid_constant__ CUtensorMap tmSFW, const __grid_constant__ CUtensorMap tmSFX,
                           const SkinnyWholeParams p) {
-  using Base = SkinnyCfg<NP, STAGES, EB>;
-  using Cfg = SkinnyWholeCfg<NP, STAGES, EB>;
+  using Base = SkinnyCfg<NP, STAGES, EB, WR>;
+  using Cfg = SkinnyWholeCfg<NP, STAGES, EB, WR, SBUFS>;
   constexpr int IQ = kWholeItemQueue;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -304,7 +307,7 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
           if (lane == 0) mbar_arrive(acc_empty_bar(as));
         }
         // transpose through shared memory: staging[m][n], one 512-byte row per output row of the chunk
-        const uint32_t buf = staging_base + (chunk_ctr & 1u) * uint32_t(Cfg::STAGING_BUF_BYTES);
+        const uint32_t buf = staging_base + (SBUFS == 2 ? (chunk_ctr & 1u) : 0u) * uint32_t(Cfg::STAGING_BUF_BYTES);
         ++chunk_ctr;
 #pragma unroll
         for (int j = 0; j < 16; ++j)
@@ -353,6 +356,8 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             }
           }
         }
+        // one staging buffer: every thread has read its pieces before the next chunk is staged
+        if constexpr (SBUFS == 1) asm volatile("bar.sync 1, 128;" ::: "memory");
       }
 #ifdef WB200_TRACE
       if (t == 0) WB_TRACE_SEG(seq, 3, trace_now() | (1ull << 63));
