@@ -241,6 +241,17 @@ int make_output_map(CUtensorMap* map, void* c, int M, int N, long long ldc, int 
   return WB200_OK;
 }
 
+// C as a 2-D tensor for dense (unswizzled) boxes of box_cols x box_rows elements: the whole-tile decode kernel's stores.
+int make_output_map_dense(CUtensorMap* map, void* c, int M, int N, long long ldc, int esz, int box_cols, int box_rows) {
+  const MapKey k{c, (unsigned long long)N, (unsigned long long)M, (unsigned long long)ldc * esz, unsigned(box_cols), unsigned(box_rows),
+                 int(esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16),
+                 int(CU_TENSOR_MAP_SWIZZLE_NONE), int(CU_TENSOR_MAP_L2_PROMOTION_NONE)};
+  CUresult r = encode_2d(map, k);
+  if (r != CUDA_SUCCESS)
+    return fail(WB200_ERR_CUDA, "cuTensorMapEncodeTiled (dense output) failed with CUresult %d (M %d, N %d, ldc %lld)", int(r), M, N, ldc);
+  return WB200_OK;
+}
+
 // EB: bits per operand element (4: MXFP4, 8: MXFP8 with elem_format 0 = E4M3 / 1 = E5M2).
 template <int CG, int BN, typename OutT, int EB = 4>
 int launch_tile(const DeviceInfo& dev, int M, int N, int K, const void* a, const void* as, const void* b,
@@ -697,6 +708,14 @@ int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* 
   p.dependent = tl_dependent_launch ? 1 : 0;
   p.elem_format = elem_format;
   p.c_vec = ((reinterpret_cast<uintptr_t>(c) & 15) == 0 && (ldc * (long long)sizeof(OutT)) % 16 == 0) ? 1 : 0;
+  // TMA stores of the staged chunks: 16-byte aligned C, no accumulation, and two staging halves that each hold a chunk
+  // in the output type (the single-buffer variant has room for bf16 chunks only)
+  p.tma_store = (p.c_vec && !accumulate && (sizeof(OutT) == 2 || SBUFS == 2)) ? 1 : 0;
+  CUtensorMap tmC = {};
+  if (p.tma_store) {
+    rc = make_output_map_dense(&tmC, c, M, N, ldc, int(sizeof(OutT)), tile_rows, 16);
+    if (rc) return rc;
+  }
   p.status = dev.status_ptr;
   auto kernel = wb::mxfp4_skinny_whole_kernel<NP, STAGES, OutT, EB, WR, SBUFS>;
   static bool smem_set[kMaxDevices] = {};
@@ -712,7 +731,7 @@ int launch_skinny_whole(const DeviceInfo& dev, int M, int N, int K, const void* 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = tl_dependent_launch ? 1 : 0;
-  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmW, tmX, tmSFW, tmSFX, p));
+  WB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tmW, tmX, tmSFW, tmSFX, tmC, p));
   WB_CUDA(cudaGetLastError());
   return WB200_OK;
 }

@@ -14,8 +14,8 @@
 //     runs on the SMs that came back first, each of them pulls well over its 1/148 share of HBM, so the
 //     total stays bandwidth-bound (measured: M = 128, N = 28672, K = 8192 in 28.6 us against 36 us for the
 //     K-split kernel, whose 64 KB partial tiles cost it 5-15 us of epilogue; M <= 16: the same 24 us);
-//   * the epilogue transposes 16-row chunks of the accumulator through shared memory and stores 16 bytes
-//     per thread along n.
+//   * the epilogue transposes 16-row chunks of the accumulator through shared memory; a chunk leaves through one
+//     TMA store, or, where C is accumulated into or not 16-byte aligned, as 16 bytes per thread along n.
 // The producer hands the tile numbers to the MMA and epilogue warps through a small queue in shared
 // memory (mbarrier-guarded), since only it talks to the counter.
 #pragma once
@@ -56,6 +56,8 @@ struct SkinnyWholeParams {
   int dependent;
   int elem_format;
   int c_vec;     // C's base and row pitch allow 16-byte accesses
+  int tma_store; // write C with TMA stores from the staged chunk (needs c_vec, no accumulate, a staging buffer pair that
+                 // holds two chunks in the output type)
   int* status;
 };
 
@@ -63,7 +65,7 @@ template <int NP, int STAGES, typename OutT, int EB = 4, int WR = 128, int SBUFS
 __global__ void __launch_bounds__(192, 1)
 mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                           const __grid_constant__ CUtensorMap tmSFW, const __grid_constant__ CUtensorMap tmSFX,
-                          const SkinnyWholeParams p) {
+                          const __grid_constant__ CUtensorMap tmC, const SkinnyWholeParams p) {
   using Base = SkinnyCfg<NP, STAGES, EB, WR>;
   using Cfg = SkinnyWholeCfg<NP, STAGES, EB, WR, SBUFS>;
   constexpr int IQ = kWholeItemQueue;
@@ -78,6 +80,7 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
 #endif
   if (warp == 0 && lane < 4)  // the copy engine fetches a descriptor on first use: start that now
     prefetch_tensormap(lane == 0 ? &tmW : lane == 1 ? &tmSFW : lane == 2 ? &tmX : &tmSFX);
+  if (warp == 2 && lane == 0 && p.tma_store) prefetch_tensormap(&tmC);
 
   const uint32_t staging_base = smem_base + STAGES * Cfg::STAGE_BYTES;
   const uint32_t bar_base = staging_base + Cfg::STAGING_BYTES;
@@ -295,6 +298,50 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
       if (t == 0) WB_TRACE_SEG(seq, 2, trace_now());
 #endif
       const uint32_t t_acc = tmem_base + (uint32_t(quad * 32) << 16) + (as ? Base::ACC_COL1 : 0);
+      if (p.tma_store) {
+        // Every 16-row chunk is transposed into a dense [16][tile_rows] block of the output type in one of two
+        // staging buffers and leaves through one TMA store (clipped at M and N by the copy engine). The stores are
+        // asynchronous: no thread waits for global memory, only, before a buffer is staged again, for the store
+        // that last read it to have read it (checked by the issuing thread ahead of the chunk's barrier).
+        constexpr uint32_t kHalf = uint32_t(Cfg::STAGING_BYTES) / 2;
+        const uint32_t pitch = uint32_t(p.tile_rows) * uint32_t(sizeof(OutT));
+#pragma unroll 1
+        for (int ch = 0; ch < nchunks; ++ch) {
+          uint32_t r[16];
+          tmem_ld_32x16(t_acc + ch * 16, r);
+          tmem_ld_wait();
+          if (ch == nchunks - 1) {  // accumulator fully read: hand it back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(as));
+          }
+          const uint32_t buf = staging_base + (chunk_ctr & 1u) * kHalf;
+          ++chunk_ctr;
+          if (nl < p.tile_rows) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t dst = buf + uint32_t(j) * pitch + uint32_t(nl) * uint32_t(sizeof(OutT));
+              if constexpr (sizeof(OutT) == 4) {
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst), "r"(r[j]) : "memory");
+              } else {
+                const uint16_t h = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[j])));
+                asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"(h) : "memory");
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          if (t == 0) bulk_wait_group_read<0>();  // the previous chunk's store has read the other buffer
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (t == 0) {
+            tma_store_2d(&tmC, buf, tile * p.tile_rows, ch * 16);
+            bulk_commit_group();
+          }
+        }
+#ifdef WB200_TRACE
+        if (t == 0) WB_TRACE_SEG(seq, 3, trace_now() | (1ull << 63));
+#endif
+        continue;
+      }
 #pragma unroll 1
       for (int ch = 0; ch < nchunks; ++ch) {
         const int c0 = ch * 16;
@@ -365,6 +412,7 @@ mxfp4_skinny_whole_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     }
   }
 
+  if (threadIdx.x == 64 && p.tma_store) bulk_wait_group<0>();  // this thread's stores have left shared memory and landed
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
